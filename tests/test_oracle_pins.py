@@ -1,0 +1,92 @@
+"""Pins the numpy oracle: bit-for-bit against golden vectors produced by the reference's own host ops
+(tests/golden/make_golden.py) and against the official gguf package's dequantiser."""
+import numpy as np
+import pytest
+
+from conftest import load_golden
+from oracle import kquant as kq
+from quactlize_b200 import synth
+
+
+def _eq(a, b):
+    a, b = np.asarray(a), np.asarray(b)
+    assert a.shape == b.shape, (a.shape, b.shape)
+    if a.dtype == np.float16:
+        a, b = a.view(np.uint16), b.view(np.uint16)
+    assert np.array_equal(a, b)
+
+
+def test_dequantize_bit_exact(qtype):
+    g = load_golden(qtype)
+    _eq(kq.dequantize(g["blocks"], qtype), g["dequant"])
+
+
+def test_unpack_bit_exact(qtype):
+    g = load_golden(qtype)
+    c, s, z = kq.unpack(g["blocks"], qtype)
+    _eq(c, g["codes"]); _eq(s, g["scale_rows"]); _eq(z, g["zero_rows"])
+
+
+def test_prepare_gemv_bit_exact(qtype):
+    g = load_golden(qtype)
+    low, high, scale, zero = kq.prepare_gemv(g["blocks"], int(g["n"]), int(g["k"]), qtype)
+    _eq(low, g["low"]); _eq(high, g["high"]); _eq(scale, g["scale"]); _eq(zero, g["zero"])
+    _eq(kq.gemv_artifact_dequantize(low, high, scale, zero, qtype), g["artifact_dequant"])
+
+
+def test_units_bit_exact(qtype):
+    g = load_golden(qtype)
+    n, k = int(g["n"]), int(g["k"])
+    units = kq.pack_units(g["blocks"], n, k, qtype)[0]
+    _eq(units, g["units"])
+    for zm in (-32, -24, -4, 0, 8):
+        s, z = kq.units_decode(units, qtype, zm)
+        _eq(s, g[f"unit_scale_z{zm}"]); _eq(z, g[f"unit_zero_z{zm}"])
+
+
+def test_scale_prepass_bit_exact(qtype):
+    g = load_golden(qtype)
+    f = kq.fmt(qtype)
+    b = g["blocks"]
+    d, dmin = kq.d_dmin(b, qtype)
+    for zm in (0, 8):
+        s, z = kq.scale_prepass(b[:, f.scale_off:f.scale_off + f.scale_bytes], d, dmin, qtype, zm)
+        _eq(s, g[f"prepass_scale_z{zm}"]); _eq(z, g[f"prepass_zero_z{zm}"])
+
+
+def test_recover_round_trip(qtype):
+    g = load_golden(qtype)
+    n, k = int(g["n"]), int(g["k"])
+    low, high, units = kq.prepare_fully_quantized(g["blocks"], n, k, qtype)
+    _eq(kq.recover_blocks(low, high, units, n, k, qtype), g["blocks"])
+
+
+def test_vecdot_dense_matches_reference_cpu_arm(qtype):
+    g = load_golden(qtype)
+    got = kq.vecdot_dense(g["blocks"], g["x"], int(g["n"]), int(g["k"]), qtype)
+    assert kq.max_rel(got, g["vecdot_dense"]) < 2e-6
+    # the merged artifact (planes + units) describes the same weight
+    low, high, units = kq.prepare_fully_quantized(g["blocks"], int(g["n"]), int(g["k"]), qtype)
+    assert kq.max_rel(kq.bc_matmul(g["x"], low, high, units, qtype), g["vecdot_dense"]) < 2e-6
+
+
+def test_official_gguf_dequantizer(qtype):
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    blocks = synth.kquant_blocks(qtype, 257, seed=5 + qtype)
+    ref = quants.dequantize(blocks.reshape(-1), gguf.GGMLQuantizationType(qtype)).reshape(-1, 256)
+    got = kq.dequantize(blocks, qtype)
+    _eq(got, ref.astype(np.float16))
+    assert np.allclose(kq.dequantize_f32(blocks, qtype), ref, rtol=1e-6, atol=1e-9)
+
+
+def test_planes_matmul_matches_dequant(qtype):
+    g = load_golden(qtype)
+    f = kq.fmt(qtype)
+    n, k = int(g["n"]), int(g["k"])
+    low, high, scale, zero = g["low"], g["high"], g["scale"], g["zero"]
+    a = synth.activations(3, k, seed=9)
+    w = kq.gemv_artifact_dequantize(low, high, scale, zero, qtype)[0].astype(np.float64)
+    ref = a.astype(np.float64) @ w.T
+    got = kq.planes_matmul(a, low, high, scale, zero, f.lo_bits, f.hi_bits, f.group_size)
+    assert kq.max_rel(got, ref) < 2e-3
