@@ -1,0 +1,174 @@
+/* C ABI of libquactlize_b200.so -- the B200 (sm_100a) device library behind quactlize's raw-pointer boundary.
+ *
+ * The library is a drop-in for the reference's device library: every `quactlize_ppu_*` entry below has the name,
+ * argument list, argument meaning and return-code behaviour of the reference symbol it replaces (cited per entry as
+ * file:line inside the reference project), so the reference's own host extension can dlopen this file through
+ * QUACTLIZE_PPU_LIB (quactlize/csrc/preprocess/thop/ppu_backend.cpp:58-134 resolves exactly these names).
+ * `quactlize_b200_*` entries are additive: they cover what the reference reaches only through C++ templates
+ * (generic per-group W4/W2/W1 planes, bf16 activations, multi-row raw-block GEMV, device-pointer MoE forms).
+ *
+ * Conventions (quactlize/csrc/preprocess/thop/ppu_backend.h:23-104, quactlize/include/quactlize_ppu_device.h:12-51):
+ *   - raw pointers and ints only; fp16/bf16 cross as uint16_t*; qtype is the ggml number (Q2_K=10 .. Q6_K=14);
+ *   - host-pointer entries take HOST memory: they allocate device temporaries, copy in, launch, synchronise, copy out;
+ *   - `_dev_` entries take DEVICE memory and a native stream cast to void* (NULL = default stream); a zero return
+ *     means ENQUEUED, not completed; they neither allocate nor synchronise; the caller owns every buffer;
+ *   - every entry returns an int: 0 ok, small distinct codes for refused arguments, 41 for a latched runtime failure
+ *     (allocation / copy / launch / synchronise / bounded device wait), never an exception or abort; host outputs are
+ *     untouched on failure;
+ *   - weights: raw GGUF k-quant blocks [E][N][K/256][block bytes] row-major by output row, or the offline artifact:
+ *     Native code planes low [E][N][K*lo/8], high [E][N][K*hi/8] (element k of a row at bit k*bits, LSB first;
+ *     Q3_K/Q6_K offset-binary) plus either fp16 planes scale/zero [E][K/gs][N] or packed units
+ *     [E][K/256/P][N][P*sb_bytes];  grouped activations/outputs are concatenated in expert order with cumulative
+ *     int offsets[E+1].
+ */
+#ifndef QUACTLIZE_B200_H_
+#define QUACTLIZE_B200_H_
+
+#include <stdbool.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- config inventory records: quactlize/include/quactlize_ppu_config.h:12-40 ----------------------------------- */
+typedef struct quactlize_ppu_config_v1 {
+  bool enable_cuda_kernel;
+  char const* name;
+  int32_t tile_m, tile_n, warp_m, warp_n, stages;
+} quactlize_ppu_config_v1;
+
+typedef struct quactlize_ppu_config_v2 {
+  bool enable_cuda_kernel;
+  char const* name;
+  int32_t tile_m, tile_n, tile_k, warp_m, warp_n, stages;
+} quactlize_ppu_config_v2;
+
+/* ================================ raw GGUF block consumers (CUDA-core family) =================================== */
+
+/* Independent block rows, each with its own activation slice: blocks [rows*bpr][block_bytes], x fp16
+ * [rows*bpr*256], out fp32 [rows].  Replaces quactlize/csrc/device/ppu_backend.cu:297-304. */
+int quactlize_ppu_vecdot(uint8_t const* blocks, int64_t block_bytes, uint16_t const* x, float* out,
+                         int rows, int blocks_per_row, int qtype);
+/* Dense decode GEMV, one shared activation x fp16 [bpr*256], out fp32 [rows].  ppu_backend.cu:306-313. */
+int quactlize_ppu_vecdot_dense(uint8_t const* blocks, int64_t block_bytes, uint16_t const* x, float* out,
+                               int rows, int blocks_per_row, int qtype);
+/* Device-pointer form.  ppu_backend.cu:315-326, quactlize/include/quactlize_ppu_device.h:15-17. */
+int quactlize_ppu_vecdot_dense_dev_v1(uint8_t const* blocks, int64_t block_bytes, uint16_t const* x, float* out,
+                                      int rows, int blocks_per_row, int qtype, void* stream);
+/* Ragged MoE decode: blocks [E][n][bpr][bytes], gathered x [total_rows][bpr*256], offsets [E+1], out fp32
+ * [total_rows][n].  ppu_backend.cu:373-396. */
+int quactlize_ppu_vecdot_moe(uint8_t const* blocks, int64_t block_bytes, uint16_t const* x, int const* row_offsets,
+                             float* out, int n, int blocks_per_row, int experts, int total_rows, int max_rows, int qtype);
+int quactlize_ppu_vecdot_moe_config_v1(uint8_t const* blocks, int64_t block_bytes, uint16_t const* x, int const* offsets,
+                                       float* out, int n, int blocks_per_row, int experts, int total_rows, int max_rows,
+                                       int qtype, char const* config_name);
+/* ppu_backend.cu:348-371 */
+int32_t quactlize_ppu_vecdot_moe_config_valid_v1(int total_rows, int n, int k, int group_size, int experts, int max_rows,
+                                                 int qtype, char const* config_name);
+int32_t quactlize_ppu_list_valid_vecdot_moe_configs_v2(quactlize_ppu_config_v2* configs, int32_t capacity, int total_rows,
+                                                       int n, int k, int group_size, int experts, int max_rows, int qtype);
+/* Raw blocks [n_blocks][bytes] -> fp16 [n_blocks][256], bit-exact half(dl*q - ml).  ppu_backend.cu:433-439. */
+int quactlize_ppu_dequantize(uint8_t const* blocks, int64_t block_bytes, uint16_t* out, int n_blocks, int qtype);
+/* Scale blocks + fp16 headers -> fp16 (scale, zero) [n][groups]; zmul in {0, 8}.  ppu_backend.cu:441-452. */
+int quactlize_ppu_prepass(uint8_t const* blocks, int64_t block_bytes, uint16_t const* d, uint16_t const* dmin, int n,
+                          uint16_t* scale, uint16_t* zero, int groups, int qtype, int zmul);
+/* Packed units [E][unit][N][bytes] -> fp16 planes [E][K/gs][N]; zmul in {-32,-24,-4,0,8}.  ppu_backend.cu:454-467. */
+int quactlize_ppu_prepass_unit(uint8_t const* units, uint16_t* scale, uint16_t* zero, int n, int k, int experts,
+                               int qtype, int zmul);
+
+/* additive: m >= 1 shared activation rows x fp16 [m][k], out fp32 [m][rows]; force_generic selects the simple
+ * warp-per-row kernel.  No counterpart entry in the reference (its dense entry is m = 1, ppu_backend.cu:93-106). */
+int quactlize_b200_vecdot_rows_dev_v1(uint8_t const* blocks, int64_t block_bytes, uint16_t const* x, float* out, int m,
+                                      int rows, int blocks_per_row, int qtype, int force_generic, void* stream);
+/* additive device-pointer forms of the entries above */
+int quactlize_b200_vecdot_dev_v1(uint8_t const* blocks, int64_t block_bytes, uint16_t const* x, float* out, int rows,
+                                 int blocks_per_row, int qtype, void* stream);
+int quactlize_b200_vecdot_moe_dev_v1(uint8_t const* blocks, int64_t block_bytes, uint16_t const* x, int const* offsets,
+                                     float* out, int n, int blocks_per_row, int experts, int total_rows, int max_rows,
+                                     int qtype, void* stream);
+int quactlize_b200_dequantize_dev_v1(uint8_t const* blocks, int64_t block_bytes, uint16_t* out, int n_blocks, int qtype,
+                                     void* stream);
+int quactlize_b200_prepass_unit_dev_v1(uint8_t const* units, uint16_t* scale, uint16_t* zero, int n, int k, int experts,
+                                       int qtype, int zmul, void* stream);
+
+/* ================================ bit-plane GEMV (scale-first and merged artifact) ============================== */
+
+/* Scale-first GEMV over (low, high, scale, zero): out fp16 [total_rows][n]; experts == 0 is dense, otherwise offsets
+ * is [E+1].  W = u*scale + zero with u the offset-binary plane code.  ppu_backend.cu:462-474. */
+int quactlize_ppu_gemv_lowbit(uint16_t const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale,
+                              uint16_t const* zero, uint16_t* out, int total_rows, int n, int k, int group_size,
+                              int qtype, int experts, int const* row_offsets, int max_rows);
+/* ppu_backend.cu:476-489 */
+int quactlize_ppu_gemv_lowbit_config_v1(uint16_t const* act, uint8_t const* low, uint8_t const* high,
+                                        uint16_t const* scale, uint16_t const* zero, uint16_t* out, int m, int n, int k,
+                                        int group_size, int qtype, char const* config_name);
+/* ppu_backend.cu:328-346 */
+int32_t quactlize_ppu_gemv_lowbit_config_valid_v1(int m, int n, int k, int group_size, int qtype, char const* config_name);
+/* ppu_backend.cu:491-509, quactlize_ppu_device.h:21-24 */
+int quactlize_ppu_gemv_lowbit_dev_v1(uint16_t const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale,
+                                     uint16_t const* zero, uint16_t* out, int m, int n, int k, int group_size, int qtype,
+                                     void* stream, char const* config_name);
+/* Merged artifact (planes + packed units) GEMV, out fp32; experts == 0 requires total_rows == 1.
+ * ppu_backend.cu:398-431, quactlize_ppu_device.h:28-32. */
+int quactlize_ppu_bc_gemv(uint16_t const* act, uint8_t const* low, uint8_t const* high, uint8_t const* units,
+                          int const* row_offsets, float* out, int total_rows, int n, int k, int experts, int max_rows,
+                          int qtype);
+int quactlize_ppu_bc_gemv_dev_v1(uint16_t const* x, uint8_t const* low, uint8_t const* high, uint8_t const* units,
+                                 int const* offsets, float* out, int total_rows, int n, int k, int experts, int max_rows,
+                                 int qtype, void* stream);
+
+/* additive: ragged MoE scale-first GEMV on device pointers (the reference reaches it only through its host entry). */
+int quactlize_b200_gemv_lowbit_moe_dev_v1(uint16_t const* act, uint8_t const* low, uint8_t const* high,
+                                          uint16_t const* scale, uint16_t const* zero, uint16_t* out, int total_rows,
+                                          int n, int k, int group_size, int qtype, int experts, int const* offsets,
+                                          int max_rows, void* stream);
+/* additive: generic per-group plane GEMV.  W = (lo + 2^bits_lo*hi + code_offset)*scale + zero (zero may be NULL);
+ * bits_lo in {1,2,4}, bits_hi in {0,1,2}; act_dtype 0 = fp16, 1 = bf16; out_dtype 0 = fp16, 1 = fp32, 2 = bf16;
+ * experts == 0 is dense over total_rows activation rows.  The reference instantiates these shapes only as C++
+ * templates (tests/test_gemv_lowbit.cu:454-461, quactlize/include/gemv_lowbit/gemv_launcher.hpp:116-208). */
+int quactlize_b200_gemv_plane_dev_v1(void const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale,
+                                     uint16_t const* zero, void* out, int total_rows, int n, int k, int bits_lo,
+                                     int bits_hi, int group_size, int code_offset, int act_dtype, int out_dtype,
+                                     int experts, int const* offsets, int max_rows, void* stream);
+
+/* ================================ host-only artifact producers ================================================== */
+
+/* quactlize/include/quactlize_ppu_packed.h:12-33, quactlize/csrc/device/ppu_unit_pack.cpp:186-233 */
+int64_t quactlize_ppu_units_bytes(int n, int k, int qtype);
+int quactlize_ppu_prepare_units(uint8_t const* blocks, uint8_t* units, int n, int k, int qtype);
+int quactlize_ppu_prepare_units_grouped(uint8_t const* blocks, uint8_t* units, int n, int k, int experts, int qtype);
+int quactlize_ppu_prepare_fully_quantized_v1(uint8_t const* blocks, uint8_t* low, uint8_t* high, uint8_t* units, int n,
+                                             int k, int experts, int qtype);
+int quactlize_ppu_recover_fully_quantized_v1(uint8_t const* low, uint8_t const* high, uint8_t const* units,
+                                             uint8_t* recovered, int n, int k, int experts, int qtype);
+/* Plane placement for the tensor-core consumers.  This library's placement is the Native order, so these are
+ * byte-identical copies.  quactlize/csrc/device/ppu_dense_layout.cu:108-208, ppu_backend.h:62-78. */
+int quactlize_ppu_prepare_dense(uint8_t const* low_native, uint8_t const* high_native, uint8_t* low_layout,
+                                uint8_t* high_layout, int n, int k, int qtype);
+int quactlize_ppu_recover_dense(uint8_t const* low_layout, uint8_t const* high_layout, uint8_t* low_native,
+                                uint8_t* high_native, int n, int k, int qtype);
+int quactlize_ppu_prepare_dense_for_tile(uint8_t const* low_native, uint8_t const* high_native, uint8_t* low_layout,
+                                         uint8_t* high_layout, int n, int k, int qtype, int tile_k);
+int quactlize_ppu_recover_dense_for_tile(uint8_t const* low_layout, uint8_t const* high_layout, uint8_t* low_native,
+                                         uint8_t* high_native, int n, int k, int qtype, int tile_k);
+/* additive: the scale-first artifact producer (raw -> low, high, fp16 scale, fp16 zero), which the reference keeps in
+ * its torch extension (quactlize/csrc/preprocess/thop/gguf_prepass_ops.cpp:809-878); any n > 0. */
+int quactlize_b200_prepare_gemv(uint8_t const* blocks, uint8_t* low, uint8_t* high, uint16_t* scale, uint16_t* zero,
+                                int n, int k, int experts, int qtype);
+/* additive: packed-unit producer without the n % 256 restriction of the GEMM-facing entries. */
+int quactlize_b200_pack_units(uint8_t const* blocks, uint8_t* units, int n, int k, int experts, int qtype);
+
+/* ================================ runtime ======================================================================= */
+
+/* additive: make the NEXT runtime call of the given kind fail on the host (1 alloc, 2 H2D, 3 D2H, 4 sync, 6 launch);
+ * the thread's latched status; read-and-clear of the device wait-status word (0 ok, 41 a bounded wait gave up).
+ * Mirrors the reference's injectable fake runtime, quactlize/include/gemv_lowbit/gemv_rt.hpp:50-91. */
+void quactlize_b200_rt_fail_next(int kind);
+int quactlize_b200_rt_last_status(void);
+int quactlize_b200_device_wait_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QUACTLIZE_B200_H_ */

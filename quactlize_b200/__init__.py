@@ -1,0 +1,476 @@
+"""quactlize_b200 -- weight-only low-bit matmul for B200 (sm_100a) behind quactlize's Python surface.
+
+The op names, argument order, shapes and error behaviour follow the reference's `quactlize/__init__.py` wrappers
+(one function per `torch.ops.quactlize.*` op).  Underneath, every op calls the C-ABI device library
+`libquactlize_b200.so` through ctypes:
+
+  * CPU tensors go through the host-pointer entries (the library copies to the device, runs, copies back), exactly
+    what the reference's host extension does through its dlopen seam;
+  * CUDA tensors go through the `_dev` entries on torch's current stream: nothing is allocated or synchronised by the
+    library, the result tensor is allocated by torch.
+
+There is no CPU arm here: a missing library or CUDA device is an error, never a silent fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from .formats import QuantType, kquant_geometry  # noqa: F401
+
+__all__ = [
+    "gguf_vecdot", "gguf_vecdot_dense", "gguf_vecdot_rows", "gguf_vecdot_moe", "gguf_dequantize", "gguf_scale_prepass",
+    "gguf_packed_scale_prepass", "gguf_prepare_gemv", "gguf_prepare_fully_quantized_dense",
+    "gguf_prepare_fully_quantized_grouped", "gguf_recover_fully_quantized", "gguf_gemv_scale_first",
+    "gguf_gemv_scale_first_moe", "gguf_gemv_bc", "gguf_gemv_bc_moe", "gemv_plane", "gguf_backend", "gguf_pack_unit",
+]
+
+
+def _check(cond, msg):
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _rc(rc, what):
+    if rc != 0:
+        raise RuntimeError(f"{what} failed in libquactlize_b200 (rc={rc}"
+                           f"{'; runtime failure, see stderr' if rc == 41 else ''})")
+
+
+def _p(t):
+    return None if t is None or t.numel() == 0 else C.c_void_p(t.data_ptr())
+
+
+def _stream(t):
+    return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _same_device(*ts):
+    devs = {t.device for t in ts if t is not None and t.numel() > 0}
+    _check(len(devs) == 1, f"all tensors must be on one device, got {sorted(str(d) for d in devs)}")
+    return next(iter(devs))
+
+
+def _u8(t, name, dim=None):
+    _check(t.dtype == torch.uint8 and t.is_contiguous(), f"{name} must be contiguous uint8")
+    if dim is not None:
+        _check(t.dim() == dim, f"{name} must be {dim}-D, got {tuple(t.shape)}")
+
+
+def _f16(x):
+    _check(x.dtype in (torch.float16, torch.float32), "activations must be float16 or float32")
+    return (x if x.dtype == torch.float16 else x.to(torch.float16)).contiguous()
+
+
+def _geom(qtype):
+    g = kquant_geometry(qtype)
+    _check(g is not None, f"unsupported ggml type {qtype} -- expected one of Q2_K=10, Q3_K=11, Q4_K=12, Q5_K=13, Q6_K=14")
+    return g
+
+
+def gguf_backend() -> str:
+    """Which backend serves the ops, as the reference reports it ("ppu (...)" / "cpu (...)"); here always the device
+    library, or an ImportError from loading it."""
+    _lib.lib()
+    return f"b200 ({_lib.LIB_PATH})"
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# raw GGUF block consumers
+
+def gguf_vecdot(blocks, x, qtype: int):
+    """One dot product per raw block: blocks uint8 [rows,type_size], x fp16/fp32 [rows,256] -> fp32 [rows]."""
+    g = _geom(qtype)
+    _u8(blocks, "blocks", 2)
+    _check(blocks.shape[1] == g.block_bytes, f"this format's raw GGUF block is {g.block_bytes} bytes, got {blocks.shape[1]}")
+    _check(x.dim() == 2 and x.shape[1] == 256 and x.shape[0] == blocks.shape[0], "x must be [rows,256] matching blocks")
+    dev = _same_device(blocks, x)
+    x16 = _f16(x)
+    rows = blocks.shape[0]
+    out = torch.empty(rows, dtype=torch.float32, device=dev)
+    if rows == 0:
+        return out
+    L = _lib.lib()
+    if dev.type == "cpu":
+        _rc(L.quactlize_ppu_vecdot(_p(blocks), g.block_bytes, _p(x16), _p(out), rows, 1, int(qtype)), "gguf_vecdot")
+    else:
+        with torch.cuda.device(dev):
+            _rc(L.quactlize_b200_vecdot_dev_v1(_p(blocks), g.block_bytes, _p(x16), _p(out), rows, 1, int(qtype),
+                                               _stream(blocks)), "gguf_vecdot")
+    return out
+
+
+def gguf_vecdot_rows(blocks, x, n: int, k: int, qtype: int, force_generic: bool = False):
+    """Raw-block GEMV with m >= 1 shared activation rows: x [m,k] -> fp32 [m,n] (CUDA tensors)."""
+    g = _geom(qtype)
+    _u8(blocks, "blocks", 2)
+    _check(n > 0 and k > 0 and k % 256 == 0, "n must be positive and k a positive multiple of 256")
+    _check(blocks.shape == (n * (k // 256), g.block_bytes), f"blocks must be [{n * (k // 256)},{g.block_bytes}], got {tuple(blocks.shape)}")
+    _check(x.dim() == 2 and x.shape[1] == k, "x must be [m,k]")
+    dev = _same_device(blocks, x)
+    _check(dev.type == "cuda", "gguf_vecdot_rows takes CUDA tensors")
+    x16 = _f16(x)
+    m = x.shape[0]
+    out = torch.empty((m, n), dtype=torch.float32, device=dev)
+    if m == 0:
+        return out
+    with torch.cuda.device(dev):
+        _rc(_lib.lib().quactlize_b200_vecdot_rows_dev_v1(_p(blocks), g.block_bytes, _p(x16), _p(out), m, n, k // 256,
+                                                         int(qtype), int(force_generic), _stream(blocks)), "gguf_vecdot_rows")
+    return out
+
+
+def gguf_vecdot_dense(blocks, x, n: int, k: int, qtype: int):
+    """Dense decode GEMV: blocks [n*k/256,type_size], one activation x fp16/fp32 [1,k] -> fp32 [1,n]."""
+    g = _geom(qtype)
+    _u8(blocks, "blocks", 2)
+    _check(x.dim() == 2 and x.shape[0] == 1 and x.shape[1] == k, "x must be fp16/fp32 [1,k]")
+    _check(n > 0 and k > 0 and k % 256 == 0, "n must be positive and k a positive multiple of 256")
+    bpr = k // 256
+    _check(blocks.shape[0] == n * bpr, f"blocks need n*k/256 rows; got {blocks.shape[0]}")
+    _check(blocks.shape[1] == g.block_bytes, f"this format's raw GGUF block is {g.block_bytes} bytes, got {blocks.shape[1]}")
+    dev = _same_device(blocks, x)
+    x16 = _f16(x)
+    out = torch.empty((1, n), dtype=torch.float32, device=dev)
+    L = _lib.lib()
+    if dev.type == "cpu":
+        _rc(L.quactlize_ppu_vecdot_dense(_p(blocks), g.block_bytes, _p(x16), _p(out), n, bpr, int(qtype)), "gguf_vecdot_dense")
+    else:
+        with torch.cuda.device(dev):
+            _rc(L.quactlize_ppu_vecdot_dense_dev_v1(_p(blocks), g.block_bytes, _p(x16), _p(out), n, bpr, int(qtype),
+                                                    _stream(blocks)), "gguf_vecdot_dense")
+    return out
+
+
+def _offsets_info(row_offsets, experts, total_rows):
+    _check(row_offsets.dtype == torch.int32 and row_offsets.dim() == 1 and row_offsets.numel() == experts + 1,
+           "row_offsets must be int32 [experts+1]")
+    off = row_offsets.detach().cpu()
+    _check(int(off[0]) == 0, "row_offsets must start at zero")
+    d = off[1:] - off[:-1]
+    _check(bool((d >= 0).all()), "row_offsets must be nondecreasing")
+    _check(int(off[-1]) == total_rows, f"row_offsets end at {int(off[-1])} but x has {total_rows} rows")
+    return int(d.max()) if experts > 0 else 0
+
+
+def gguf_vecdot_moe(blocks, x, row_offsets, qtype: int):
+    """Ragged MoE decode over raw blocks: blocks [E,n*k/256,type_size], gathered x [rows,k], offsets int32 [E+1]
+    -> fp32 [rows,n]."""
+    g = _geom(qtype)
+    _u8(blocks, "blocks", 3)
+    _check(x.dim() == 2, "x must be fp16/fp32 [total_rows,k]")
+    experts, k = blocks.shape[0], x.shape[1]
+    _check(k > 0 and k % 256 == 0, "x's k must be a positive multiple of 256")
+    bpr = k // 256
+    _check(blocks.shape[1] % bpr == 0, "expert block count must be divisible by k/256")
+    n = blocks.shape[1] // bpr
+    _check(blocks.shape[2] == g.block_bytes, f"this format's raw GGUF block is {g.block_bytes} bytes, got {blocks.shape[2]}")
+    total = x.shape[0]
+    max_rows = _offsets_info(row_offsets, experts, total)
+    dev = _same_device(blocks, x)
+    x16 = _f16(x)
+    out = torch.empty((total, n), dtype=torch.float32, device=dev)
+    if total == 0:
+        return out
+    L = _lib.lib()
+    off = row_offsets.to(dev).contiguous()
+    if dev.type == "cpu":
+        _rc(L.quactlize_ppu_vecdot_moe(_p(blocks), g.block_bytes, _p(x16), _p(off), _p(out), n, bpr, experts, total,
+                                       max_rows, int(qtype)), "gguf_vecdot_moe")
+    else:
+        with torch.cuda.device(dev):
+            _rc(L.quactlize_b200_vecdot_moe_dev_v1(_p(blocks), g.block_bytes, _p(x16), _p(off), _p(out), n, bpr, experts,
+                                                   total, max_rows, int(qtype), _stream(blocks)), "gguf_vecdot_moe")
+    return out
+
+
+def gguf_dequantize(blocks, qtype: int):
+    """Raw blocks [rows,type_size] -> fp16 [rows,256], bit-exact half(dl*q - ml)."""
+    g = _geom(qtype)
+    _u8(blocks, "blocks", 2)
+    _check(blocks.shape[1] == g.block_bytes, f"this format's raw GGUF block is {g.block_bytes} bytes, got {blocks.shape[1]}")
+    rows = blocks.shape[0]
+    out = torch.empty((rows, 256), dtype=torch.float16, device=blocks.device)
+    if rows == 0:
+        return out
+    L = _lib.lib()
+    if blocks.device.type == "cpu":
+        _rc(L.quactlize_ppu_dequantize(_p(blocks), g.block_bytes, _p(out), rows, int(qtype)), "gguf_dequantize")
+    else:
+        with torch.cuda.device(blocks.device):
+            _rc(L.quactlize_b200_dequantize_dev_v1(_p(blocks), g.block_bytes, _p(out), rows, int(qtype), _stream(blocks)),
+                "gguf_dequantize")
+    return out
+
+
+def gguf_scale_prepass(scale_blocks, d, dmin, qtype: int, zmul: int):
+    """The format's scale blocks [rows,scale_bytes] + fp16 headers -> fp16 (scale, zero) [rows,groups]; zmul in {0,8}."""
+    g = _geom(qtype)
+    _u8(scale_blocks, "scale_blocks", 2)
+    _check(scale_blocks.shape[1] == g.scale_bytes, f"scale_blocks second dim is {scale_blocks.shape[1]} but this format's scale block is {g.scale_bytes} bytes")
+    _check(d.dtype == torch.float16 and d.dim() == 1 and d.shape[0] == scale_blocks.shape[0], "d must be float16 [rows]")
+    has = dmin is not None and dmin.numel() > 0
+    _check(not g.has_min or has, "this format has a min channel, so dmin is required")
+    _check(zmul in (0, 8), f"zmul must be 0 or 8; got {zmul}")
+    rows = scale_blocks.shape[0]
+    sb, dd = scale_blocks.cpu(), d.cpu().contiguous()
+    dm = dmin.cpu().contiguous() if has else None
+    scale = torch.empty((rows, g.groups), dtype=torch.float16)
+    zero = torch.empty_like(scale)
+    _rc(_lib.lib().quactlize_ppu_prepass(_p(sb), g.scale_bytes, _p(dd), _p(dm), rows, _p(scale), _p(zero), g.groups,
+                                         int(qtype), int(zmul)), "gguf_scale_prepass")
+    return scale.to(scale_blocks.device), zero.to(scale_blocks.device)
+
+
+def gguf_packed_scale_prepass(units, qtype: int, zmul: int = 0):
+    """Packed units (dense [U,n,bytes] or grouped [E,U,n,bytes]) -> fp16 planes (scale, zero) [E, k/group_size, n]."""
+    g = _geom(qtype)
+    _u8(units, "units")
+    _check(units.dim() in (3, 4), "packed units must be dense [unit,n,bytes] or grouped [experts,unit,n,bytes]")
+    _check(zmul in (-32, -24, -4, 0, 8), f"zmul must be one of -32, -24, -4, 0, 8; got {zmul}")
+    u4 = units if units.dim() == 4 else units.unsqueeze(0)
+    experts, nu, n, ub = u4.shape
+    _check(ub == g.unit_total, f"this format's copyable unit is {g.unit_total} bytes; got {ub}")
+    _check(experts > 0 and nu > 0 and n > 0, "packed unit axes must be nonempty")
+    k = nu * g.sb_per_unit * 256
+    scale = torch.empty((experts, k // g.group_size, n), dtype=torch.float16, device=units.device)
+    zero = torch.empty_like(scale)
+    L = _lib.lib()
+    if units.device.type == "cpu":
+        _rc(L.quactlize_ppu_prepass_unit(_p(u4), _p(scale), _p(zero), n, k, experts, int(qtype), int(zmul)),
+            "gguf_packed_scale_prepass")
+    else:
+        with torch.cuda.device(units.device):
+            _rc(L.quactlize_b200_prepass_unit_dev_v1(_p(u4), _p(scale), _p(zero), n, k, experts, int(qtype), int(zmul),
+                                                     _stream(units)), "gguf_packed_scale_prepass")
+    return scale, zero
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# offline artifact producers (host work; the result follows the input's device)
+
+def _blocks_cpu(blocks, n, k, g, experts=None):
+    _u8(blocks, "blocks")
+    _check(blocks.dim() in (2, 3), "blocks must be uint8 [N*K/256,type_size] or [E,N*K/256,type_size]")
+    _check(n > 0 and k > 0 and k % 256 == 0, "n must be positive and k a positive multiple of 256")
+    e = blocks.shape[0] if blocks.dim() == 3 else 1
+    per = blocks.shape[1] if blocks.dim() == 3 else blocks.shape[0]
+    if experts is not None:
+        _check(blocks.dim() == 2 and blocks.shape[0] == experts * n * (k // 256),
+               f"blocks should be [{experts * n * (k // 256)}, type_size] for {experts} experts of an ({n}, {k}) weight, got {tuple(blocks.shape)}")
+        e, per = experts, n * (k // 256)
+    _check(per == n * (k // 256), f"each expert needs {n * (k // 256)} raw blocks for n={n} k={k}; got {per}")
+    _check(blocks.shape[-1] == g.block_bytes, f"this format's raw GGUF block is {g.block_bytes} bytes, got {blocks.shape[-1]}")
+    return blocks.cpu().contiguous(), e
+
+
+def gguf_prepare_gemv(blocks, n: int, k: int, qtype: int):
+    """Raw blocks -> the resident scale-first artifact (low, high, scale, zero): Native code planes [E,n,...] and fp16
+    planes [E,k/group_size,n]; `high` is empty for single-plane formats."""
+    g = _geom(qtype)
+    b, e = _blocks_cpu(blocks, n, k, g)
+    low = torch.empty((e, n, k * g.lo_bits // 8), dtype=torch.uint8)
+    high = torch.empty((e, n, k * g.hi_bits // 8), dtype=torch.uint8) if g.hi_bits else torch.empty((0,), dtype=torch.uint8)
+    scale = torch.empty((e, k // g.group_size, n), dtype=torch.float16)
+    zero = torch.empty_like(scale)
+    _rc(_lib.lib().quactlize_b200_prepare_gemv(_p(b), _p(low), _p(high), _p(scale), _p(zero), n, k, e, int(qtype)),
+        "gguf_prepare_gemv")
+    dev = blocks.device
+    return low.to(dev), high.to(dev), scale.to(dev), zero.to(dev)
+
+
+def _prepare_fq(blocks, n, k, qtype, experts, dense):
+    g = _geom(qtype)
+    _check(n % 256 == 0 and k % 256 == 0, "fully-quantized preparation needs n and k multiples of 256")
+    _check((k // 256) % g.sb_per_unit == 0, f"this format needs {g.sb_per_unit} superblocks per copyable unit")
+    b, e = _blocks_cpu(blocks, n, k, g, experts)
+    low = torch.empty((e, n, k * g.lo_bits // 8), dtype=torch.uint8)
+    high = torch.empty((e, n, k * g.hi_bits // 8), dtype=torch.uint8) if g.hi_bits else torch.empty((0,), dtype=torch.uint8)
+    nu = k // 256 // g.sb_per_unit
+    units = torch.empty((e, nu, n, g.unit_total), dtype=torch.uint8)
+    _rc(_lib.lib().quactlize_ppu_prepare_fully_quantized_v1(_p(b), _p(low), _p(high), _p(units), n, k, e, int(qtype)),
+        "gguf_prepare_fully_quantized")
+    if dense:
+        units = units[0]
+    dev = blocks.device
+    return low.to(dev), high.to(dev), units.to(dev)
+
+
+def gguf_prepare_fully_quantized_dense(blocks, n: int, k: int, qtype: int):
+    """Raw blocks [n*k/256,type_size] -> (low [1,n,..], high, units [U,n,bytes]); nothing is expanded."""
+    _check(blocks.dim() == 2, "dense preparation takes one [n*k/256,type_size] weight")
+    return _prepare_fq(blocks, n, k, qtype, 1, True)
+
+
+def gguf_prepare_fully_quantized_grouped(blocks, n: int, k: int, qtype: int, experts: int):
+    """Raw blocks [E*n*k/256,type_size] (expert-major) -> (low [E,n,..], high, units [E,U,n,bytes])."""
+    return _prepare_fq(blocks, n, k, qtype, int(experts), False)
+
+
+def gguf_recover_fully_quantized(low, high, units, n: int, k: int, qtype: int):
+    """Byte-exact inverse of the fully-quantized producers: (low, high, units) -> raw blocks [E*n*k/256,type_size]."""
+    g = _geom(qtype)
+    e = low.shape[0]
+    lo, hi, un = low.cpu().contiguous(), high.cpu().contiguous(), units.cpu().contiguous()
+    out = torch.empty((e * n * (k // 256), g.block_bytes), dtype=torch.uint8)
+    _rc(_lib.lib().quactlize_ppu_recover_fully_quantized_v1(_p(lo), _p(hi), _p(un), _p(out), n, k, e, int(qtype)),
+        "gguf_recover_fully_quantized")
+    return out.to(low.device)
+
+
+def gguf_pack_unit(blocks, n: int, k: int, qtype: int, experts: int = 1):
+    """Raw blocks -> packed scale units [E,U,n,bytes] only (any n)."""
+    g = _geom(qtype)
+    b, e = _blocks_cpu(blocks, n, k, g, experts)
+    _check((k // 256) % g.sb_per_unit == 0, f"this format needs {g.sb_per_unit} superblocks per copyable unit")
+    units = torch.empty((e, k // 256 // g.sb_per_unit, n, g.unit_total), dtype=torch.uint8)
+    _rc(_lib.lib().quactlize_b200_pack_units(_p(b), _p(units), n, k, e, int(qtype)), "gguf_pack_unit")
+    return units.to(blocks.device)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# bit-plane GEMV
+
+def _planes_check(a, low, high, g, k):
+    _check(a.dim() == 2, "a must be fp16/fp32 [rows,k]")
+    _u8(low, "low", 3)
+    _check(k > 0 and k % 256 == 0, "a's k must be a positive multiple of 256")
+    _check(low.shape[2] == k * g.lo_bits // 8, "low plane byte count disagrees with k/qtype")
+    if g.hi_bits:
+        _u8(high, "high", 3)
+        _check(high.shape == (low.shape[0], low.shape[1], k * g.hi_bits // 8), "high plane shape disagrees with qtype")
+    else:
+        _check(high is None or high.numel() == 0, "single-plane format must have an empty high plane")
+
+
+def _scale_first(a, low, high, scale, zero, row_offsets, qtype, grouped):
+    g = _geom(qtype)
+    k = a.shape[1] if a.dim() == 2 else 0
+    _planes_check(a, low, high, g, k)
+    e, n = low.shape[0], low.shape[1]
+    _check(scale.dtype == torch.float16 and zero.dtype == torch.float16 and scale.shape == zero.shape and
+           scale.shape == (e, k // g.group_size, n), "scale and zero must be fp16 [experts,k/group_size,n]")
+    rows = a.shape[0]
+    dev = _same_device(a, low, scale, zero)
+    a16 = _f16(a)
+    out = torch.empty((rows, n), dtype=torch.float16, device=dev)
+    experts, max_rows, off = 0, rows, None
+    if grouped:
+        experts = e
+        max_rows = _offsets_info(row_offsets, experts, rows)
+        off = row_offsets.to(dev).contiguous()
+    else:
+        _check(e == 1, "dense artifact must have one expert dimension")
+    if rows == 0:
+        return out
+    L = _lib.lib()
+    scale, zero = scale.contiguous(), zero.contiguous()
+    if dev.type == "cpu":
+        _rc(L.quactlize_ppu_gemv_lowbit(_p(a16), _p(low), _p(high), _p(scale), _p(zero), _p(out), rows, n, k,
+                                        g.group_size, int(qtype), experts, _p(off), max_rows), "scale-first GEMV")
+    else:
+        with torch.cuda.device(dev):
+            if grouped:
+                _rc(L.quactlize_b200_gemv_lowbit_moe_dev_v1(_p(a16), _p(low), _p(high), _p(scale), _p(zero), _p(out), rows,
+                                                            n, k, g.group_size, int(qtype), experts, _p(off), max_rows,
+                                                            _stream(a16)), "scale-first MoE GEMV")
+            else:
+                _check(n % 256 == 0, "the device-pointer scale-first entry needs n a multiple of 256")
+                _rc(L.quactlize_ppu_gemv_lowbit_dev_v1(_p(a16), _p(low), _p(high), _p(scale), _p(zero), _p(out), rows, n, k,
+                                                       g.group_size, int(qtype), _stream(a16), None), "scale-first GEMV")
+    return out
+
+
+def gguf_gemv_scale_first(a, low, high, scale, zero, qtype: int):
+    """Dense GEMV over a resident `gguf_prepare_gemv` artifact -> fp16 [rows,n]."""
+    return _scale_first(a, low, high, scale, zero, None, qtype, False)
+
+
+def gguf_gemv_scale_first_moe(a, low, high, scale, zero, row_offsets, qtype: int):
+    """Ragged MoE GEMV over a resident `gguf_prepare_gemv` artifact -> fp16 [rows,n]."""
+    return _scale_first(a, low, high, scale, zero, row_offsets, qtype, True)
+
+
+def _bc(a, low, high, units, row_offsets, qtype, grouped):
+    g = _geom(qtype)
+    k = a.shape[1] if a.dim() == 2 else 0
+    _planes_check(a, low, high, g, k)
+    e, n = low.shape[0], low.shape[1]
+    _check(n > 0 and n % 256 == 0 and k % (256 * g.sb_per_unit) == 0, f"BC GEMV needs n multiple 256 and k multiple {256 * g.sb_per_unit}")
+    _u8(units, "units")
+    nu = k // 256 // g.sb_per_unit
+    rows = a.shape[0]
+    dev = _same_device(a, low, units)
+    a16 = _f16(a)
+    out = torch.empty((rows, n), dtype=torch.float32, device=dev)
+    experts, max_rows, off = 0, 1, None
+    if grouped:
+        _check(units.shape == (e, nu, n, g.unit_total), f"grouped packed units must be [experts,copyable_unit,n,{g.unit_total}]")
+        experts = e
+        max_rows = _offsets_info(row_offsets, experts, rows)
+        off = row_offsets.to(dev).contiguous()
+    else:
+        _check(rows == 1, "dense BC decode is GEMV and requires exactly one activation row")
+        _check(e == 1, "dense BC artifact must have one expert dimension")
+        _check(units.shape == (nu, n, g.unit_total), f"dense packed units must be [copyable_unit,n,{g.unit_total}]")
+    if rows == 0:
+        return out
+    L = _lib.lib()
+    if dev.type == "cpu":
+        _rc(L.quactlize_ppu_bc_gemv(_p(a16), _p(low), _p(high), _p(units), _p(off), _p(out), rows, n, k, experts, max_rows,
+                                    int(qtype)), "BC GEMV")
+    else:
+        with torch.cuda.device(dev):
+            _rc(L.quactlize_ppu_bc_gemv_dev_v1(_p(a16), _p(low), _p(high), _p(units), _p(off), _p(out), rows, n, k, experts,
+                                               max_rows, int(qtype), _stream(a16)), "BC GEMV")
+    return out
+
+
+def gguf_gemv_bc(a, low, high, units, qtype: int):
+    """CUDA-core GEMV over the merged form: Native code planes plus packed scale units -> fp32 [1,n]."""
+    return _bc(a, low, high, units, None, qtype, False)
+
+
+def gguf_gemv_bc_moe(a, low, high, units, row_offsets, qtype: int):
+    """The MoE arm; row_offsets is cumulative so an empty expert is representable -> fp32 [rows,n]."""
+    return _bc(a, low, high, units, row_offsets, qtype, True)
+
+
+def gemv_plane(a, low, high, scale, zero, bits_lo: int, bits_hi: int, group_size: int, code_offset: int = 0,
+               row_offsets=None, out_dtype=None):
+    """Generic per-group plane GEMV (W4A16 / W2A16 / W1A16 ...): W = (lo + 2^bits_lo*hi + code_offset)*scale + zero.
+
+    a fp16 or bf16 [rows,k] (CUDA); low uint8 [E,n,k*bits_lo/8]; scale (and optional zero) fp16 [E,k/group_size,n];
+    dense when row_offsets is None (E == 1), else ragged with cumulative int32 offsets.  Returns [rows,n] in a's dtype
+    unless out_dtype (torch.float16 / bfloat16 / float32) says otherwise."""
+    _check(a.is_cuda and a.dim() == 2 and a.dtype in (torch.float16, torch.bfloat16), "a must be a CUDA fp16/bf16 [rows,k] tensor")
+    _u8(low, "low", 3)
+    e, n, k = low.shape[0], low.shape[1], a.shape[1]
+    _check(low.shape[2] == k * bits_lo // 8, "low plane byte count disagrees with k/bits")
+    if bits_hi:
+        _u8(high, "high", 3)
+        _check(high.shape == (e, n, k * bits_hi // 8), "high plane shape disagrees with bits_hi")
+    _check(scale.dtype == torch.float16 and scale.shape == (e, k // group_size, n), "scale must be fp16 [E,k/group_size,n]")
+    _check(zero is None or (zero.dtype == torch.float16 and zero.shape == scale.shape), "zero must match scale")
+    out_dtype = out_dtype or a.dtype
+    ok = {torch.float16: 0, torch.float32: 1, torch.bfloat16: 2}[out_dtype]
+    rows = a.shape[0]
+    out = torch.empty((rows, n), dtype=out_dtype, device=a.device)
+    experts, max_rows, off = 0, rows, None
+    if row_offsets is not None:
+        experts = e
+        max_rows = _offsets_info(row_offsets, experts, rows)
+        off = row_offsets.to(a.device).contiguous()
+    else:
+        _check(e == 1, "dense artifact must have one expert dimension")
+    if rows == 0:
+        return out
+    a = a.contiguous()
+    with torch.cuda.device(a.device):
+        _rc(_lib.lib().quactlize_b200_gemv_plane_dev_v1(
+            _p(a), _p(low), _p(high) if bits_hi else None, _p(scale.contiguous()), _p(zero.contiguous()) if zero is not None else None,
+            _p(out), rows, n, k, bits_lo, bits_hi, group_size, int(code_offset), 1 if a.dtype == torch.bfloat16 else 0, ok,
+            experts, _p(off), max_rows, _stream(a)), "plane GEMV")
+    return out

@@ -1,0 +1,118 @@
+// Bit-exact helper kernels around the GEMVs: raw block -> fp16 weights, scale pre-pass (raw scale blocks or packed
+// units -> fp16 scale/zero planes).  Every product and sum is an explicit round-to-nearest intrinsic so the device
+// result equals the reference's host definition bit for bit:
+//   weight  = half( (float(d)*sc) * q - float(dmin)*mn )                quactlize/include/gguf_vecdot.hpp:313-321
+//   scale   = half( float(d) * float(sc) ),  zero = -half( float(dmin) * float(mn) ),
+//   zero   := half( float(zero) + zmul * float(scale) )                 quactlize/include/gguf_scale_prepass.hpp:64-98
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "qb_kquant.cuh"
+#include "qb_runtime.hpp"
+
+namespace qb {
+
+// one warp per block, lane -> 8 consecutive elements, one 16-byte store per lane
+template <int QT>
+__global__ void __launch_bounds__(256) dequant_kernel(uint8_t const* __restrict__ blocks, __half* __restrict__ out, int count) {
+  using F = kq::Fmt<QT>;
+  constexpr int GS = 256 / F::kGroups;
+  int const lane = threadIdx.x & 31;
+  int const b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (b >= count) return;
+  uint8_t const* blk = blocks + size_t(b) * F::kBytes;
+  float const d = __half2float(__ushort_as_half(kq::load_u16(blk + F::kD)));
+  float dmin = 0.f;
+  if constexpr (F::kHasMin) dmin = __half2float(__ushort_as_half(kq::load_u16(blk + F::kDmin)));
+  int const i0 = lane * 8, g = i0 / GS, j0 = i0 % GS;
+  int sc, mn;
+  kq::scale_min<QT>(blk + F::kScaleOff, g, sc, mn);
+  float const dl = __fmul_rn(d, float(sc)), ml = __fmul_rn(dmin, float(mn));
+  __align__(16) __half w[8];
+#pragma unroll
+  for (int t = 0; t < 8; ++t)
+    w[t] = __float2half_rn(__fsub_rn(__fmul_rn(dl, float(kq::code<QT>(blk, g, j0 + t))), ml));
+  *reinterpret_cast<uint4*>(out + size_t(b) * 256 + i0) = *reinterpret_cast<uint4 const*>(w);
+}
+
+__device__ __forceinline__ void scale_zero_from_codes(float d, float dmin, int sc, int mn, bool has_min, int zmul,
+                                                      __half& scale, __half& zero) {
+  scale = __float2half_rn(__fmul_rn(d, float(sc)));
+  zero = has_min ? __hneg(__float2half_rn(__fmul_rn(dmin, float(mn)))) : __float2half_rn(0.f);
+  if (zmul != 0) zero = __float2half_rn(__fadd_rn(__half2float(zero), __fmul_rn(float(zmul), __half2float(scale))));
+}
+
+// scale blocks [count][scale_bytes] + headers d,dmin [count] -> planes [count][groups]; one thread per (row, group)
+template <int QT>
+__global__ void __launch_bounds__(256) prepass_kernel(uint8_t const* __restrict__ sblocks, uint16_t const* __restrict__ d,
+                                                      uint16_t const* __restrict__ dmin, int count, int zmul,
+                                                      __half* __restrict__ scale, __half* __restrict__ zero) {
+  using F = kq::Fmt<QT>;
+  int const idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= count * F::kGroups) return;
+  int const r = idx / F::kGroups, g = idx % F::kGroups;
+  int sc, mn;
+  kq::scale_min<QT>(sblocks + size_t(r) * F::kScaleBytes, g, sc, mn);
+  float const df = __half2float(__ushort_as_half(d[r]));
+  float const mf = F::kHasMin ? __half2float(__ushort_as_half(dmin[r])) : 0.f;
+  __half s, z;
+  scale_zero_from_codes(df, mf, sc, mn, F::kHasMin, zmul, s, z);
+  scale[idx] = s; zero[idx] = z;
+}
+
+// units [E][K/256/P][N][unit_total] -> planes [E][K/gs][N]; one thread per (expert, plane row, column), column fastest
+template <int QT>
+__global__ void __launch_bounds__(256) prepass_unit_kernel(uint8_t const* __restrict__ units, __half* __restrict__ scale,
+                                                           __half* __restrict__ zero, int experts, int n, int nsb, int zmul) {
+  using F = kq::Fmt<QT>;
+  using U = kq::Unit<QT>;
+  int64_t const total = int64_t(experts) * nsb * F::kGroups * n;
+  int64_t const idx = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  int const col = int(idx % n);
+  int64_t const r = idx / n;
+  int const g = int(r % F::kGroups);
+  int const sb = int((r / F::kGroups) % nsb);
+  int const e = int(r / (int64_t(F::kGroups) * nsb));
+  int const nu = nsb / U::kSbPerUnit;
+  uint8_t const* u = units + ((int64_t(e) * nu + sb / U::kSbPerUnit) * n + col) * U::kUnitTotal + (sb % U::kSbPerUnit) * U::kSbBytes;
+  int sc, mn;
+  kq::unit_scale_min<QT>(u, g, sc, mn);
+  float const df = __half2float(__ushort_as_half(kq::load_u16(u)));
+  float const mf = F::kHasMin ? __half2float(__ushort_as_half(kq::load_u16(u + 2))) : 0.f;
+  __half s, z;
+  scale_zero_from_codes(df, mf, sc, mn, F::kHasMin, zmul, s, z);
+  scale[idx] = s; zero[idx] = z;
+}
+
+#define QB_QT_SWITCH(qtype, CALL)                                                        \
+  switch (qtype) { case 10: CALL(10); break; case 11: CALL(11); break; case 12: CALL(12); break; \
+                   case 13: CALL(13); break; case 14: CALL(14); break; default: return false; }
+
+bool enqueue_dequantize(uint8_t const* blocks, __half* out, int count, int qtype, cudaStream_t s) {
+#define CALL(Q) dequant_kernel<Q><<<(count + 7) / 8, 256, 0, s>>>(blocks, out, count)
+  QB_QT_SWITCH(qtype, CALL)
+#undef CALL
+  return true;
+}
+
+bool enqueue_prepass(uint8_t const* sblocks, uint16_t const* d, uint16_t const* dmin, int count, int qtype, int zmul,
+                     __half* scale, __half* zero, cudaStream_t s) {
+#define CALL(Q) prepass_kernel<Q><<<(count * kq::Fmt<Q>::kGroups + 255) / 256, 256, 0, s>>>(sblocks, d, dmin, count, zmul, scale, zero)
+  QB_QT_SWITCH(qtype, CALL)
+#undef CALL
+  return true;
+}
+
+bool enqueue_prepass_unit(uint8_t const* units, __half* scale, __half* zero, int experts, int n, int nsb, int qtype,
+                          int zmul, cudaStream_t s) {
+#define CALL(Q) { int64_t const total = int64_t(experts) * nsb * kq::Fmt<Q>::kGroups * n; \
+                  prepass_unit_kernel<Q><<<unsigned((total + 255) / 256), 256, 0, s>>>(units, scale, zero, experts, n, nsb, zmul); }
+  QB_QT_SWITCH(qtype, CALL)
+#undef CALL
+  return true;
+}
+
+}  // namespace qb

@@ -1,0 +1,38 @@
+// Internal launch interfaces between the translation units of libquactlize_b200 (not part of the C ABI).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace qb {
+
+int enqueue_native_gemv(uint8_t const* blocks, __half const* x, float* out, int const* offsets,
+                        int n, int bpr, int experts, int m_rows, int max_rows, int qtype, bool per_row_x,
+                        bool force_generic, cudaStream_t stream);
+bool enqueue_dequantize(uint8_t const* blocks, __half* out, int count, int qtype, cudaStream_t s);
+bool enqueue_prepass(uint8_t const* sblocks, uint16_t const* d, uint16_t const* dmin, int count, int qtype, int zmul,
+                     __half* scale, __half* zero, cudaStream_t s);
+bool enqueue_prepass_unit(uint8_t const* units, __half* scale, __half* zero, int experts, int n, int nsb, int qtype,
+                          int zmul, cudaStream_t s);
+
+// Plane GEMV.  scale_mode: 0 = fp16 planes scale(+zero) [E][K/gs][N]; 1 = packed k-quant units of `qtype`.
+struct PlaneGemvDesc {
+  void const* act;            // fp16 or bf16 [rows][k]
+  uint8_t const* low;         // [E][n][k*lo_bits/8]
+  uint8_t const* high;        // [E][n][k*hi_bits/8] or nullptr
+  void const* scale;          // fp16 [E][k/gs][n]    (scale_mode 0)
+  void const* zero;           // fp16 [E][k/gs][n] or nullptr
+  uint8_t const* units;       // [E][k/256/P][n][unit_total] (scale_mode 1)
+  void* out;                  // fp16 / bf16 / fp32 [rows][n]
+  int const* offsets;         // cumulative [experts+1] or nullptr
+  int n, k, experts, m_rows, max_rows;
+  int lo_bits, hi_bits, group_size, scale_mode, qtype;
+  int code_offset;            // added to the unsigned code before scaling (e.g. -8), 0 if none
+  int act_bf16;               // activations are bf16 (else fp16)
+  int out_kind;               // 0 = fp16, 1 = fp32, 2 = bf16
+};
+int enqueue_plane_gemv(PlaneGemvDesc const& d, cudaStream_t stream);   // 0 ok, 40 unsupported shape
+
+}  // namespace qb

@@ -1,0 +1,125 @@
+"""CPU-side checks of the C-ABI library: it loads, exports every symbol the public header declares, refuses bad
+arguments with the documented codes, and its HOST-ONLY producers are bit-exact against the reference goldens and the
+oracle.  No compute entry is called here (no GPU)."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+import quactlize_b200 as qb
+from conftest import ROOT, load_golden
+from oracle import kquant as kq
+from quactlize_b200 import _lib, synth
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "quactlize_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(quactlize_(?:ppu|b200)_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    names = _declared_symbols()
+    assert len(names) > 30
+    h = C.CDLL(_lib.LIB_PATH)
+    missing = [n for n in names if not hasattr(h, n)]
+    assert not missing, missing
+
+
+def test_binding_table_matches_header():
+    assert sorted(_lib.SIGNATURES) == _declared_symbols()
+    _lib.lib()
+
+
+def test_reference_loader_mandatory_symbols_present():
+    # quactlize/csrc/preprocess/thop/ppu_backend.cpp:85-108 refuses a library that lacks any of these
+    h = C.CDLL(_lib.LIB_PATH)
+    for n in ("quactlize_ppu_vecdot", "quactlize_ppu_vecdot_moe", "quactlize_ppu_dequantize", "quactlize_ppu_prepass",
+              "quactlize_ppu_gemv_lowbit"):
+        assert hasattr(h, n)
+
+
+def test_argument_refusals_need_no_device():
+    L = _lib.lib()
+    assert L.quactlize_ppu_vecdot(None, 144, None, None, 4, 1, 99) == 1           # unknown qtype
+    assert L.quactlize_ppu_vecdot(None, 143, None, None, 4, 1, 12) == 10          # wrong block size
+    assert L.quactlize_ppu_vecdot_dense(None, 144, None, None, 4, 1, 99) == 3
+    assert L.quactlize_ppu_vecdot_dense(None, 144, None, None, 0, 1, 12) == 12
+    assert L.quactlize_ppu_vecdot_moe(None, 144, None, None, None, 8, 1, 2, 4, 2, 99) == 2
+    assert L.quactlize_ppu_vecdot_moe(None, 144, None, None, None, 0, 1, 2, 4, 2, 12) == 11
+    assert L.quactlize_ppu_dequantize(None, 144, None, 0, 12) == 12
+    assert L.quactlize_ppu_prepass(None, 12, None, None, 4, None, None, 8, 12, 3) == 4
+    assert L.quactlize_ppu_prepass_unit(None, None, None, 256, 256, 1, 12, 0) == 7
+    assert L.quactlize_ppu_gemv_lowbit(None, None, None, None, None, None, 1, 256, 256, 32, 99, 0, None, 1) == 6
+    assert L.quactlize_ppu_bc_gemv(None, None, None, None, None, None, 1, 256, 256, 0, 1, 12) == 13
+    assert L.quactlize_ppu_units_bytes(256, 256, 99) == -1
+    assert L.quactlize_ppu_units_bytes(100, 256, 12) == -1
+    assert L.quactlize_ppu_units_bytes(256, 256, 14) == -1                        # Q6_K pairs two superblocks
+    assert L.quactlize_ppu_units_bytes(256, 512, 14) == 256 * 36
+    assert L.quactlize_ppu_units_bytes(256, 512, 12) == 256 * 2 * 16
+    assert L.quactlize_ppu_gemv_lowbit_config_valid_v1(1, 4096, 4096, 32, 12, None) == 1
+    assert L.quactlize_ppu_gemv_lowbit_config_valid_v1(1, 4096, 4096, 16, 12, None) == 0
+    assert L.quactlize_ppu_gemv_lowbit_config_valid_v1(1, 4096, 4096, 32, 12, b"64x64:32x32:s3") == 0
+    assert L.quactlize_ppu_vecdot_moe_config_valid_v1(4, 256, 512, 32, 2, 3, 12, b"vecdot_moe") == 1
+    cfg = (_lib.ConfigV2 * 2)()
+    assert L.quactlize_ppu_list_valid_vecdot_moe_configs_v2(cfg, 2, 4, 256, 512, 32, 2, 3, 12) == 1
+    assert cfg[0].enable_cuda_kernel and cfg[0].name == b"vecdot_moe"
+
+
+def _eq(a, b):
+    a = a.numpy() if isinstance(a, torch.Tensor) else np.asarray(a)
+    b = np.asarray(b)
+    assert a.shape == b.shape, (a.shape, b.shape)
+    if a.dtype == np.float16:
+        a, b = a.view(np.uint16), b.view(np.uint16)
+    assert np.array_equal(a, b)
+
+
+def test_prepare_gemv_host_producer_bit_exact(qtype):
+    g = load_golden(qtype)
+    low, high, scale, zero = qb.gguf_prepare_gemv(torch.from_numpy(g["blocks"]), int(g["n"]), int(g["k"]), qtype)
+    _eq(low, g["low"]); _eq(high, g["high"]); _eq(scale, g["scale"]); _eq(zero, g["zero"])
+
+
+def test_pack_units_host_producer_bit_exact(qtype):
+    g = load_golden(qtype)
+    units = qb.gguf_pack_unit(torch.from_numpy(g["blocks"]), int(g["n"]), int(g["k"]), qtype)
+    _eq(units[0], g["units"])
+
+
+@pytest.mark.parametrize("experts", [1, 3])
+def test_fully_quantized_round_trip(qtype, experts):
+    n, k = 256, 512
+    blocks = synth.kquant_blocks(qtype, experts * n * k // 256, seed=31 + qtype)
+    tb = torch.from_numpy(blocks)
+    if experts == 1:
+        low, high, units = qb.gguf_prepare_fully_quantized_dense(tb, n, k, qtype)
+        units4 = units.unsqueeze(0)
+    else:
+        low, high, units = qb.gguf_prepare_fully_quantized_grouped(tb, n, k, qtype, experts)
+        units4 = units
+    olow, ohigh, ounits = kq.prepare_fully_quantized(blocks, n, k, qtype, experts)
+    _eq(low, olow); _eq(high, ohigh); _eq(units4, ounits)
+    # byte-neutral: the artifact holds exactly the checkpoint's bytes
+    assert low.numel() + high.numel() + units.numel() == blocks.size
+    back = qb.gguf_recover_fully_quantized(low, high, units4, n, k, qtype)
+    _eq(back, blocks)
+
+
+def test_units_need_paired_superblocks():
+    blocks = torch.from_numpy(synth.kquant_blocks(14, 256, seed=1))
+    with pytest.raises(RuntimeError):
+        qb.gguf_prepare_fully_quantized_dense(blocks, 256, 256, 14)
+
+
+def test_shape_contract_errors():
+    blocks = torch.from_numpy(synth.kquant_blocks(12, 16, seed=1))
+    with pytest.raises(RuntimeError):
+        qb.gguf_prepare_gemv(blocks, 8, 300, 12)
+    with pytest.raises(RuntimeError):
+        qb.gguf_prepare_gemv(blocks[:, :100].contiguous(), 8, 512, 12)
+    with pytest.raises(RuntimeError):
+        qb.gguf_dequantize(blocks, 9)

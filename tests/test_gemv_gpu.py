@@ -1,0 +1,273 @@
+"""GPU parity tests of the CUDA-core family, through the C ABI (ctypes) against the numpy oracle and the reference
+goldens.  Integer/byte/fp16-plane results are bit-exact; GEMV outputs are within max-rel 1e-2 of an fp64-accumulated
+dequant-then-matmul (asserted tighter, 2e-3, the reference's own gate is 4e-3: tests/test_gemv_lowbit.cu:299-305)."""
+import numpy as np
+import pytest
+import torch
+
+import quactlize_b200 as qb
+from conftest import load_golden
+from oracle import kquant as kq
+from quactlize_b200 import _lib, synth
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+DEV = "cuda:0"
+
+
+def _cuda(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def _bits(t):
+    a = t.detach().cpu().numpy()
+    return a.view(np.uint16) if a.dtype == np.float16 else a
+
+
+def _wait_ok():
+    torch.cuda.synchronize()
+    assert _lib.lib().quactlize_b200_device_wait_status() == 0
+
+
+# ---- bit-exact kernels ------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("where", ["cuda", "cpu"])
+def test_dequantize_bit_exact(qtype, where):
+    g = load_golden(qtype)
+    b = torch.from_numpy(g["blocks"])
+    out = qb.gguf_dequantize(b.to(DEV) if where == "cuda" else b, qtype)
+    assert np.array_equal(_bits(out), g["dequant"].view(np.uint16))
+
+
+def test_dequantize_large_matches_oracle(qtype):
+    blocks = synth.kquant_blocks(qtype, 4099, seed=3 + qtype)
+    out = qb.gguf_dequantize(_cuda(blocks), qtype)
+    assert np.array_equal(_bits(out), kq.dequantize(blocks, qtype).view(np.uint16))
+
+
+def test_scale_prepass_bit_exact(qtype):
+    g = load_golden(qtype)
+    f = kq.fmt(qtype)
+    b = g["blocks"]
+    d, dmin = kq.d_dmin(b, qtype)
+    sb = torch.from_numpy(np.ascontiguousarray(b[:, f.scale_off:f.scale_off + f.scale_bytes]))
+    for zm in (0, 8):
+        s, z = qb.gguf_scale_prepass(sb, torch.from_numpy(d), torch.from_numpy(dmin) if f.has_min else None, qtype, zm)
+        assert np.array_equal(_bits(s), g[f"prepass_scale_z{zm}"].view(np.uint16))
+        assert np.array_equal(_bits(z), g[f"prepass_zero_z{zm}"].view(np.uint16))
+
+
+@pytest.mark.parametrize("where", ["cuda", "cpu"])
+def test_packed_scale_prepass_bit_exact(qtype, where):
+    g = load_golden(qtype)
+    u = torch.from_numpy(g["units"])
+    u = u.to(DEV) if where == "cuda" else u
+    for zm in (-32, -24, -4, 0, 8):
+        s, z = qb.gguf_packed_scale_prepass(u, qtype, zm)
+        assert np.array_equal(_bits(s), g[f"unit_scale_z{zm}"].view(np.uint16))
+        assert np.array_equal(_bits(z), g[f"unit_zero_z{zm}"].view(np.uint16))
+
+
+# ---- raw-block GEMV ---------------------------------------------------------------------------------------------------
+
+def test_vecdot_dense_golden(qtype):
+    g = load_golden(qtype)
+    n, k = int(g["n"]), int(g["k"])
+    for where in ("cuda", "cpu"):
+        b, x = torch.from_numpy(g["blocks"]), torch.from_numpy(g["x"])
+        if where == "cuda":
+            b, x = b.to(DEV), x.to(DEV)
+        out = qb.gguf_vecdot_dense(b, x, n, k, qtype)
+        assert out.shape == (1, n) and out.dtype == torch.float32
+        assert kq.max_rel(out.cpu().numpy(), g["vecdot_dense"]) < TOL
+    _wait_ok()
+
+
+def test_vecdot_per_block_rows(qtype):
+    blocks = synth.kquant_blocks(qtype, 300, seed=11 + qtype)
+    x = synth.activations(300, 256, seed=5)
+    ref = np.einsum("rk,rk->r", kq.dequantize_f32(blocks, qtype), x.astype(np.float64))
+    for where in ("cuda", "cpu"):
+        b, xx = torch.from_numpy(blocks), torch.from_numpy(x)
+        if where == "cuda":
+            b, xx = b.to(DEV), xx.to(DEV)
+        out = qb.gguf_vecdot(b, xx, qtype)
+        assert kq.max_rel(out.cpu().numpy(), ref) < TOL
+
+
+Q4_SHAPES = [(512, 4096), (96, 14336), (37, 256), (200, 768), (64, 11008 // 256 * 256), (1, 4096), (130, 8192)]
+
+
+@pytest.mark.parametrize("n,k", Q4_SHAPES)
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 8])
+def test_q4k_fast_kernel_vs_oracle(n, k, m):
+    blocks = synth.kquant_blocks(12, n * k // 256, seed=n + k + m)
+    x = synth.activations(m, k, seed=m + 1)
+    x[0, :7] *= 30.0                                     # outliers exercise the power-of-two activation scaling
+    ref = kq.vecdot_dense(blocks, x, n, k, 12)
+    out = qb.gguf_vecdot_rows(_cuda(blocks), _cuda(x), n, k, 12)
+    assert kq.max_rel(out.cpu().numpy(), ref) < TOL
+    gen = qb.gguf_vecdot_rows(_cuda(blocks), _cuda(x), n, k, 12, force_generic=True)
+    assert kq.max_rel(gen.cpu().numpy(), ref) < TOL
+    _wait_ok()
+
+
+def test_q4k_activation_extremes():
+    n, k = 64, 1024
+    blocks = synth.kquant_blocks(12, n * k // 256, seed=9)
+    for scale in (0.0, 1e-4, 1.0, 200.0, 6.0e4 / 8):
+        x = (synth.activations(1, k, seed=2).astype(np.float32) * scale).astype(np.float16)
+        ref = kq.vecdot_dense(blocks, x, n, k, 12)
+        out = qb.gguf_vecdot_dense(_cuda(blocks), _cuda(x), n, k, 12).cpu().numpy()
+        if scale == 0.0:
+            assert np.all(out == 0.0)
+        else:
+            assert kq.max_rel(out, ref) < TOL
+
+
+@pytest.mark.parametrize("m", [1, 3])
+def test_generic_raw_kernel_all_formats(qtype, m):
+    n, k = 70, 1536
+    blocks = synth.kquant_blocks(qtype, n * k // 256, seed=qtype)
+    x = synth.activations(m, k, seed=4)
+    out = qb.gguf_vecdot_rows(_cuda(blocks), _cuda(x), n, k, qtype)
+    assert kq.max_rel(out.cpu().numpy(), kq.vecdot_dense(blocks, x, n, k, qtype)) < TOL
+
+
+@pytest.mark.parametrize("rows_per_expert", [[3, 0, 1, 9], [0, 0, 5], [1], [2, 2, 2, 2, 2, 2, 2, 2]])
+def test_vecdot_moe_ragged(qtype, rows_per_expert):
+    n, k = 48, 1024
+    e = len(rows_per_expert)
+    blocks = synth.kquant_blocks(qtype, e * n * k // 256, seed=17 + qtype).reshape(e, n * k // 256, -1)
+    total = sum(rows_per_expert)
+    x = synth.activations(total, k, seed=6)
+    off = np.concatenate([[0], np.cumsum(rows_per_expert)]).astype(np.int32)
+    ref = kq.vecdot_moe(blocks, x, off, n, k, qtype)
+    for where in ("cuda", "cpu"):
+        b, xx, oo = torch.from_numpy(blocks), torch.from_numpy(x), torch.from_numpy(off)
+        if where == "cuda":
+            b, xx, oo = b.to(DEV), xx.to(DEV), oo.to(DEV)
+        out = qb.gguf_vecdot_moe(b, xx, oo, qtype)
+        assert out.shape == (total, n)
+        assert kq.max_rel(out.cpu().numpy(), ref) < TOL
+    _wait_ok()
+
+
+# ---- scale-first planes -----------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("n,k", [(256, 1024), (512, 4096), (256, 14336)])
+def test_scale_first_gemv_dense(qtype, n, k):
+    f = kq.fmt(qtype)
+    blocks = synth.kquant_blocks(qtype, n * k // 256, seed=qtype + n)
+    low, high, scale, zero = kq.prepare_gemv(blocks, n, k, qtype)
+    a = synth.activations(2, k, seed=8)
+    ref = kq.planes_matmul(a, low, high, scale, zero, f.lo_bits, f.hi_bits, f.group_size)
+    args = [_cuda(a), _cuda(low), _cuda(high), _cuda(scale), _cuda(zero)]
+    out = qb.gguf_gemv_scale_first(*args, qtype)
+    assert out.dtype == torch.float16 and out.shape == (2, n)
+    assert kq.max_rel(out.float().cpu().numpy(), ref) < TOL
+    if n * k <= 256 * 4096:
+        host = qb.gguf_gemv_scale_first(*[t.cpu() for t in args], qtype)
+        assert kq.max_rel(host.float().numpy(), ref) < TOL
+    _wait_ok()
+
+
+def test_scale_first_gemv_moe(qtype):
+    f = kq.fmt(qtype)
+    n, k, rows = 64, 1024, [2, 0, 3, 1]
+    e = len(rows)
+    blocks = synth.kquant_blocks(qtype, e * n * k // 256, seed=qtype).reshape(e, n * k // 256, -1)
+    low, high, scale, zero = kq.prepare_gemv(blocks, n, k, qtype)
+    a = synth.activations(sum(rows), k, seed=8)
+    off = np.concatenate([[0], np.cumsum(rows)]).astype(np.int32)
+    ref = kq.planes_matmul(a, low, high, scale, zero, f.lo_bits, f.hi_bits, f.group_size, off)
+    for where in ("cuda", "cpu"):
+        ts = [torch.from_numpy(np.ascontiguousarray(t)) for t in (a, low, high, scale, zero, off)]
+        if where == "cuda":
+            ts = [t.to(DEV) for t in ts]
+        out = qb.gguf_gemv_scale_first_moe(*ts, qtype)
+        assert kq.max_rel(out.float().cpu().numpy(), ref) < TOL
+    _wait_ok()
+
+
+GENERIC = [(4, 128, 4096, 4096), (4, 32, 512, 1024), (4, 64, 256, 2048), (2, 64, 768, 2048), (2, 64, 2048, 768),
+           (1, 64, 768, 2048), (1, 64, 2048, 768), (2, 32, 256, 512), (1, 128, 256, 1024), (4, 16, 256, 512)]
+
+
+@pytest.mark.parametrize("bits,gs,n,k", GENERIC)
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_generic_plane_gemv_dense(bits, gs, n, k, dtype):
+    low, scale, zero = synth.group_planes(1, n, k, bits, gs, seed=bits * gs)
+    a32 = synth.activations(2, k, seed=3, dtype=np.float32)
+    at = torch.from_numpy(a32).to(dtype)
+    ref = kq.planes_matmul(at.float().numpy(), low, None, scale, zero, bits, 0, gs)
+    out = qb.gemv_plane(at.to(DEV), _cuda(low), None, _cuda(scale), _cuda(zero), bits, 0, gs)
+    assert out.dtype == dtype
+    tol = TOL if dtype == torch.float16 else 6e-3          # bf16 output rounding
+    assert kq.max_rel(out.float().cpu().numpy(), ref) < tol
+    # folded zero-point form: W = (q - 2^(bits-1)) * scale, no zero plane
+    out2 = qb.gemv_plane(at.to(DEV), _cuda(low), None, _cuda(scale), None, bits, 0, gs, code_offset=-(1 << (bits - 1)),
+                         out_dtype=torch.float32)
+    ref2 = kq.planes_matmul(at.float().numpy(), low, None, scale, None, bits, 0, gs, code_offset=-(1 << (bits - 1)))
+    assert kq.max_rel(out2.cpu().numpy(), ref2) < TOL
+    _wait_ok()
+
+
+@pytest.mark.parametrize("bits", [2, 1])
+def test_generic_plane_gemv_decode_moe(bits):
+    # Qwen3-30B-A3B-like decode shape at reduced expert count: ragged rows, empty experts
+    e, n, k, gs = 16, 768, 2048, 64
+    rows = [0, 3, 1, 0, 0, 8, 2, 1, 0, 0, 4, 0, 1, 1, 0, 2]
+    low, scale, zero = synth.group_planes(e, n, k, bits, gs, seed=bits)
+    a = torch.from_numpy(synth.activations(sum(rows), k, seed=1, dtype=np.float32)).to(torch.bfloat16)
+    off = np.concatenate([[0], np.cumsum(rows)]).astype(np.int32)
+    ref = kq.planes_matmul(a.float().numpy(), low, None, scale, zero, bits, 0, gs, off)
+    out = qb.gemv_plane(a.to(DEV), _cuda(low), None, _cuda(scale), _cuda(zero), bits, 0, gs, row_offsets=_cuda(off),
+                        out_dtype=torch.float32)
+    assert kq.max_rel(out.cpu().numpy(), ref) < TOL
+    _wait_ok()
+
+
+# ---- merged artifact (planes + packed units) ----------------------------------------------------------------------------
+
+@pytest.mark.parametrize("n,k", [(256, 1024), (512, 4096)])
+def test_bc_gemv_dense(qtype, n, k):
+    blocks = synth.kquant_blocks(qtype, n * k // 256, seed=qtype * 3)
+    low, high, units = qb.gguf_prepare_fully_quantized_dense(torch.from_numpy(blocks), n, k, qtype)
+    a = synth.activations(1, k, seed=12)
+    ref = kq.vecdot_dense(blocks, a, n, k, qtype)
+    out = qb.gguf_gemv_bc(_cuda(a), low.to(DEV), high.to(DEV), units.to(DEV), qtype)
+    assert out.dtype == torch.float32 and out.shape == (1, n)
+    assert kq.max_rel(out.cpu().numpy(), ref) < TOL
+    host = qb.gguf_gemv_bc(torch.from_numpy(a), low, high, units, qtype)
+    assert kq.max_rel(host.numpy(), ref) < TOL
+    _wait_ok()
+
+
+def test_bc_gemv_moe(qtype):
+    n, k, rows = 256, 1024, [1, 0, 4, 2]
+    e = len(rows)
+    blocks = synth.kquant_blocks(qtype, e * n * k // 256, seed=qtype * 5)
+    low, high, units = qb.gguf_prepare_fully_quantized_grouped(torch.from_numpy(blocks), n, k, qtype, e)
+    a = synth.activations(sum(rows), k, seed=13)
+    off = np.concatenate([[0], np.cumsum(rows)]).astype(np.int32)
+    ref = kq.vecdot_moe(blocks.reshape(e, -1, blocks.shape[1]), a, off, n, k, qtype)
+    out = qb.gguf_gemv_bc_moe(_cuda(a), low.to(DEV), high.to(DEV), units.to(DEV), _cuda(off), qtype)
+    assert kq.max_rel(out.cpu().numpy(), ref) < TOL
+    _wait_ok()
+
+
+# ---- runtime contract ---------------------------------------------------------------------------------------------------
+
+def test_injected_host_failures_leave_output_untouched():
+    L = _lib.lib()
+    g = load_golden(12)
+    b = torch.from_numpy(g["blocks"])
+    for kind in (1, 2, 3, 4, 6):
+        out = torch.full((b.shape[0], 256), 7.0, dtype=torch.float16)
+        L.quactlize_b200_rt_fail_next(kind)
+        rc = L.quactlize_ppu_dequantize(b.data_ptr(), 144, out.data_ptr(), b.shape[0], 12)
+        assert rc == 41 and L.quactlize_b200_rt_last_status() == kind
+        assert bool((out == 7.0).all())
+    out = qb.gguf_dequantize(b, 12)                       # the latch clears on the next call
+    assert np.array_equal(_bits(out), g["dequant"].view(np.uint16))
