@@ -116,9 +116,9 @@ def run_b200(args):
     xs = {k: torch.from_numpy(synth.activations(m, k, seed=5 + k)).to(dev) for _, k in SHAPES}
     outs = [torch.empty((m, n), dtype=torch.float32, device=dev) for n, _, _ in dev_w]
     stream = torch.cuda.current_stream(dev)
-    sp = stream.cuda_stream
 
     def step():
+        sp = torch.cuda.current_stream(dev).cuda_stream        # the capture stream while a graph is being recorded
         for (n, k, w), o in zip(dev_w, outs):
             if m == 1:
                 rc = L.quactlize_ppu_vecdot_dense_dev_v1(w.data_ptr(), BLOCK, xs[k].data_ptr(), o.data_ptr(), n, k // 256, QT, sp)
@@ -157,10 +157,18 @@ def run_b200(args):
     if L.quactlize_b200_device_wait_status() != 0 or not all(bool(torch.isfinite(o).all()) for o in outs):
         raise RuntimeError("GEMV produced non-finite output or a device wait gave up")
 
+    # The decode loop is launch-bound (each GEMV runs for a few microseconds), so one step is recorded once into a
+    # CUDA graph and replayed; --no-graph times plain back-to-back enqueues instead.
+    run_step = step
+    if not args.no_graph:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        run_step = graph.replay
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ms = timed(step, args.steps, max(3, args.warmup))
+    ms = timed(run_step, args.steps, max(3, args.warmup))
     clocks = sampler.stop() if rank == 0 else None
     step_bytes = launches_per_step * WEIGHT_BYTES
     value = world * step_bytes * args.steps / (ms * 1e-3) / 1e9
@@ -221,7 +229,7 @@ def run_b200(args):
                      "us_per_launch": round(per_launch_ms * 1e3, 3)},
         "e2e": {"value": round(e2e_val, 3), "unit": "GB/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                 "api": "quactlize_ppu_vecdot_dense (host pointers, pinned)"},
-        "gpu_launches": args.steps * launches_per_step,
+        "gpu_launches": args.steps * launches_per_step, "launch_mode": "eager" if args.no_graph else "cuda_graph",
         "clocks": clocks,
     }
     if not args.no_cpu:
@@ -326,6 +334,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--m", type=int, default=1, help="activation rows per GEMV (1 = the headline decode case)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-graph", action="store_true", help="enqueue every launch instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -165,6 +165,8 @@ int quactlize_b200_pack_units(uint8_t const* blocks, uint8_t* units, int n, int 
  * the thread's latched status; read-and-clear of the device wait-status word (0 ok, 41 a bounded wait gave up).
  * Mirrors the reference's injectable fake runtime, quactlize/include/gemv_lowbit/gemv_rt.hpp:50-91. */
 void quactlize_b200_rt_fail_next(int kind);
+/* additive: release the device temporaries the calling thread's host-pointer entries keep parked for reuse. */
+void quactlize_b200_rt_trim(void);
 int quactlize_b200_rt_last_status(void);
 int quactlize_b200_device_wait_status(void);
 

@@ -54,6 +54,7 @@ SIGNATURES = {
     "quactlize_b200_prepare_gemv": (I, [P, P, P, P, P, I, I, I, I]),
     "quactlize_b200_pack_units": (I, [P, P, I, I, I, I]),
     "quactlize_b200_rt_fail_next": (None, [I]),
+    "quactlize_b200_rt_trim": (None, []),
     "quactlize_b200_rt_last_status": (I, []),
     "quactlize_b200_device_wait_status": (I, []),
 }

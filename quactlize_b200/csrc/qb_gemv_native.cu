@@ -23,6 +23,8 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <map>
+#include <mutex>
 
 #include "qb_device.cuh"
 #include "qb_kquant.cuh"
@@ -300,37 +302,59 @@ __global__ void __launch_bounds__(256) kquant_gemv_generic_kernel(NativeArgs a) 
 
 namespace {
 
+// Launch geometry is a pure function of (kernel, n, bpr, grid.y, device); it is computed once and cached so the
+// enqueue path does no occupancy queries or attribute calls (decode launches are only a few microseconds long).
+struct Q4Plan { int S, nbs, RS, iters, gx, W; size_t smem; bool ok; };
+
 template <int M, int LPB, int STAGES>
-bool launch_q4k_fast(NativeArgs a, int gy, cudaStream_t stream) {
+Q4Plan const& q4k_plan(int n, int bpr, int gy) {
+  struct Key { int n, bpr, gy, dev; bool operator<(Key const& o) const {
+    return n != o.n ? n < o.n : bpr != o.bpr ? bpr < o.bpr : gy != o.gy ? gy < o.gy : dev < o.dev; } };
+  static std::map<Key, Q4Plan> cache;
+  static std::mutex mu;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lk(mu);
+  Key const key{n, bpr, gy, dev};
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  Q4Plan p{};
   constexpr int BW = 32 / LPB;
   constexpr int MAXW = M >= 4 ? 8 : 12;          // warps per CTA the register budget of this tile allows
-  int const S = (a.bpr + BW - 1) / BW;
-  if (S > MAXW) return false;
-  int const nbs = (a.bpr + S - 1) / S;
-  int const RS = std::max(1, MAXW / S);
-  int const W = S * RS;
-  a.S = S; a.nbs = nbs; a.RS = RS;
   auto kern = q4k_gemv_kernel<M, LPB, STAGES>;
-  size_t const ring = size_t(W) * STAGES * nbs * 144 + size_t(W) * STAGES * 8;
-  int const sms = rt_sm_count();
-  // first guess of iters from a full-occupancy estimate, then fix the grid
-  int iters = 1;
-  for (int pass = 0; pass < 2; ++pass) {
-    size_t const smem = ring + size_t(iters) * RS * S * M * 4;
-    if (smem > 227 * 1024) return false;
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    int occ = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, W * 32, smem) != cudaSuccess || occ < 1) occ = 1;
-    int const resident = std::max(1, occ * sms / std::max(1, gy));
-    int const slots = (a.n + RS - 1) / RS;
-    iters = std::min(64, std::max(1, (slots + resident - 1) / resident));
+  p.S = (bpr + BW - 1) / BW;
+  p.ok = p.S <= MAXW;
+  if (p.ok) {
+    p.nbs = (bpr + p.S - 1) / p.S;
+    p.RS = std::max(1, MAXW / p.S);
+    p.W = p.S * p.RS;
+    size_t const ring = size_t(p.W) * STAGES * p.nbs * 144 + size_t(p.W) * STAGES * 8;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    int const sms = rt_sm_count();
+    int iters = 1;
+    for (int pass = 0; pass < 2 && p.ok; ++pass) {
+      size_t const smem = ring + size_t(iters) * p.RS * p.S * M * 4;
+      if (smem > 227 * 1024) { p.ok = false; break; }
+      int occ = 0;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, p.W * 32, smem) != cudaSuccess || occ < 1) occ = 1;
+      int const resident = std::max(1, occ * sms / std::max(1, gy));
+      int const slots = (n + p.RS - 1) / p.RS;
+      iters = std::min(64, std::max(1, (slots + resident - 1) / resident));
+    }
+    p.iters = iters;
+    p.smem = ring + size_t(iters) * p.RS * p.S * M * 4;
+    if (p.smem > 227 * 1024) p.ok = false;
+    p.gx = (n + p.RS * iters - 1) / (p.RS * iters);
   }
-  a.iters = iters;
-  size_t const smem = ring + size_t(iters) * RS * S * M * 4;
-  if (smem > 227 * 1024) return false;
-  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-  int const gx = (a.n + RS * iters - 1) / (RS * iters);
-  kern<<<dim3(gx, gy), W * 32, smem, stream>>>(a);
+  return cache.emplace(key, p).first->second;
+}
+
+template <int M, int LPB, int STAGES>
+bool launch_q4k_fast(NativeArgs a, int gy, cudaStream_t stream) {
+  Q4Plan const& p = q4k_plan<M, LPB, STAGES>(a.n, a.bpr, gy);
+  if (!p.ok) return false;
+  a.S = p.S; a.nbs = p.nbs; a.RS = p.RS; a.iters = p.iters;
+  q4k_gemv_kernel<M, LPB, STAGES><<<dim3(p.gx, gy), p.W * 32, p.smem, stream>>>(a);
   return true;
 }
 

@@ -20,6 +20,8 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <map>
+#include <mutex>
 
 #include "qb_device.cuh"
 #include "qb_internal.hpp"
@@ -328,43 +330,64 @@ __global__ void __launch_bounds__(512, 1) plane_gemv_kernel(PlaneArgs a) {
 
 namespace {
 
+struct PlanePlan { int S, cps, RS, iters, gx, W, nch; size_t smem; int rc; };
+
 template <int LO, int HI, int NG, int CPL, int MODE, int QT>
 int launch_plane(PlaneGemvDesc const& d, cudaStream_t stream) {
   constexpr int STAGES = 6;
   constexpr int CPC = 128 / LO, HB = CPC * HI / 8;
+  auto kern = plane_gemv_kernel<LO, HI, NG, CPL, MODE, QT, STAGES>;
+  int const gy = d.offsets ? d.experts * d.max_rows : d.m_rows;
+  if (gy <= 0 || gy > 65535) return 40;
+  // launch geometry depends only on (n, k, grid.y, device): computed once, then cached
+  struct Key { int n, k, gy, dev; bool operator<(Key const& o) const {
+    return n != o.n ? n < o.n : k != o.k ? k < o.k : gy != o.gy ? gy < o.gy : dev < o.dev; } };
+  static std::map<Key, PlanePlan> cache;
+  static std::mutex mu;
+  PlanePlan p{};
+  {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lk(mu);
+    Key const key{d.n, d.k, gy, dev};
+    auto it = cache.find(key);
+    if (it == cache.end()) {
+      p.nch = d.k / CPC;
+      p.S = (p.nch + 32 * CPL - 1) / (32 * CPL);
+      p.rc = p.S > 16 ? 40 : 0;
+      if (!p.rc) {
+        p.cps = ((p.nch + p.S - 1) / p.S + 3) & ~3;        // keeps every high-plane segment 16-byte aligned
+        p.RS = std::max(1, 8 / p.S);
+        p.W = p.S * p.RS;
+        size_t const ring = size_t(p.W) * STAGES * p.cps * (16 + HB) + size_t(p.W) * STAGES * 8;
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        int const sms = rt_sm_count();
+        int iters = 1;
+        for (int pass = 0; pass < 2 && !p.rc; ++pass) {
+          size_t const smem = ring + size_t(iters) * p.RS * p.S * 4;
+          if (smem > 227 * 1024) { p.rc = 40; break; }
+          int occ = 0;
+          if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, p.W * 32, smem) != cudaSuccess || occ < 1) occ = 1;
+          int const resident = std::max(1, occ * sms / std::max(1, std::min(gy, 8)));
+          int const slots = (d.n + p.RS - 1) / p.RS;
+          iters = std::min(64, std::max(1, (slots + resident - 1) / resident));
+        }
+        p.iters = iters;
+        p.smem = ring + size_t(iters) * p.RS * p.S * 4;
+        if (p.smem > 227 * 1024) p.rc = 40;
+        p.gx = (d.n + p.RS * iters - 1) / (p.RS * iters);
+      }
+      it = cache.emplace(key, p).first;
+    }
+    p = it->second;
+  }
+  if (p.rc) return p.rc;
   PlaneArgs a{};
   a.d = d;
   a.status = rt_device_status_ptr();
   if (!a.status) return kRuntimeError;
-  a.nch = d.k / CPC;
-  int const S = (a.nch + 32 * CPL - 1) / (32 * CPL);
-  if (S > 16) return 40;
-  int cps = (a.nch + S - 1) / S;
-  cps = (cps + 3) & ~3;                        // keeps every high-plane segment 16-byte aligned
-  a.S = S; a.cps = cps; a.RS = std::max(1, 8 / S);
-  int const W = S * a.RS;
-  int const gy = d.offsets ? d.experts * d.max_rows : d.m_rows;
-  if (gy <= 0 || gy > 65535) return 40;
-  auto kern = plane_gemv_kernel<LO, HI, NG, CPL, MODE, QT, STAGES>;
-  size_t const ring = size_t(W) * STAGES * cps * (16 + HB) + size_t(W) * STAGES * 8;
-  int const sms = rt_sm_count();
-  int iters = 1;
-  for (int pass = 0; pass < 2; ++pass) {
-    size_t const smem = ring + size_t(iters) * a.RS * S * 4;
-    if (smem > 227 * 1024) return 40;
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    int occ = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, W * 32, smem) != cudaSuccess || occ < 1) occ = 1;
-    int const resident = std::max(1, occ * sms / std::max(1, std::min(gy, 8)));
-    int const slots = (d.n + a.RS - 1) / a.RS;
-    iters = std::min(64, std::max(1, (slots + resident - 1) / resident));
-  }
-  a.iters = iters;
-  size_t const smem = ring + size_t(iters) * a.RS * S * 4;
-  if (smem > 227 * 1024) return 40;
-  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-  int const gx = (d.n + a.RS * iters - 1) / (a.RS * iters);
-  kern<<<dim3(gx, gy), W * 32, smem, stream>>>(a);
+  a.nch = p.nch; a.S = p.S; a.cps = p.cps; a.RS = p.RS; a.iters = p.iters;
+  kern<<<dim3(p.gx, gy), p.W * 32, p.smem, stream>>>(a);
   return 0;
 }
 

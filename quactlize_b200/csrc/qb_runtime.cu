@@ -54,6 +54,51 @@ bool rt_copy_out(void const* dev, void* host, size_t bytes, cudaStream_t s) {
   return true;
 }
 
+namespace {
+struct PoolEntry { void* p; size_t bytes; int dev; };
+struct Pool {
+  std::vector<PoolEntry> free_list;
+  size_t held = 0;
+  ~Pool() { for (auto& e : free_list) (void)cudaFree(e.p); }
+};
+Pool& pool() { static thread_local Pool p; return p; }
+constexpr size_t kPoolCap = size_t(1) << 30;      // bytes a thread may keep parked
+}  // namespace
+
+void* rt_pool_take(size_t bytes) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  auto& fl = pool().free_list;
+  int best = -1;
+  for (int i = 0; i < int(fl.size()); ++i)
+    if (fl[i].dev == dev && fl[i].bytes >= bytes && fl[i].bytes <= 2 * bytes + 4096 && (best < 0 || fl[i].bytes < fl[best].bytes)) best = i;
+  if (best < 0) return nullptr;
+  void* p = fl[best].p;
+  pool().held -= fl[best].bytes;
+  fl.erase(fl.begin() + best);
+  return p;
+}
+
+void rt_pool_give(void* p, size_t bytes) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || bytes > kPoolCap / 2) { (void)cudaFree(p); return; }
+  auto& pl = pool();
+  while (!pl.free_list.empty() && (pl.held + bytes > kPoolCap || pl.free_list.size() >= 32)) {
+    (void)cudaFree(pl.free_list.front().p);
+    pl.held -= pl.free_list.front().bytes;
+    pl.free_list.erase(pl.free_list.begin());
+  }
+  pl.free_list.push_back({p, bytes, dev});
+  pl.held += bytes;
+}
+
+void rt_pool_trim() {
+  auto& pl = pool();
+  for (auto& e : pl.free_list) (void)cudaFree(e.p);
+  pl.free_list.clear();
+  pl.held = 0;
+}
+
 int rt_sm_count() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
@@ -69,6 +114,7 @@ int rt_sm_count() {
 
 // ---- additive C entries: fault injection for tests, status query ---------------------------------------------------
 extern "C" void quactlize_b200_rt_fail_next(int kind) { qb::rt_tls().inject = static_cast<qb::RtStatus>(kind); }
+extern "C" void quactlize_b200_rt_trim(void) { qb::rt_pool_trim(); }
 extern "C" int quactlize_b200_rt_last_status(void) { return static_cast<int>(qb::rt_tls().status); }
 extern "C" int quactlize_b200_device_wait_status(void) {
   qb::rt_clear_error();

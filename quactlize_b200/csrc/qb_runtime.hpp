@@ -45,14 +45,22 @@ inline bool rt_injected(RtStatus s) {
   return true;
 }
 
+// Device temporaries of the host-pointer entries come from a small per-thread pool of recently released buffers, so
+// a decode loop through those entries does not pay cudaMalloc/cudaFree (both synchronise the device) on every call.
+void* rt_pool_take(size_t bytes);                 // nullptr when nothing fits
+void rt_pool_give(void* p, size_t bytes);         // keeps or frees
+void rt_pool_trim();                              // frees everything the calling thread holds
+
 inline void* rt_malloc(size_t bytes) {
   if (rt_injected(RtStatus::Allocation)) { rt_record(RtStatus::Allocation, "cudaMalloc", "injected failure"); return nullptr; }
+  if (void* q = rt_pool_take(bytes)) return q;
   void* p = nullptr;
-  cudaError_t const e = cudaMalloc(&p, bytes ? bytes : 1);
-  if (e != cudaSuccess) { rt_record(RtStatus::Allocation, "cudaMalloc", cudaGetErrorString(e)); return nullptr; }
+  cudaError_t e = cudaMalloc(&p, bytes ? bytes : 1);
+  if (e != cudaSuccess) { (void)cudaGetLastError(); rt_pool_trim(); e = cudaMalloc(&p, bytes ? bytes : 1); }
+  if (e != cudaSuccess) { (void)cudaGetLastError(); rt_record(RtStatus::Allocation, "cudaMalloc", cudaGetErrorString(e)); return nullptr; }
   return p;
 }
-inline void rt_free(void* p) { if (p) (void)cudaFree(p); }
+inline void rt_free(void* p, size_t bytes) { if (p) rt_pool_give(p, bytes); }
 inline bool rt_h2d(void* dst, void const* src, size_t bytes, cudaStream_t s) {
   if (rt_injected(RtStatus::HostToDevice)) return rt_record(RtStatus::HostToDevice, "H2D", "injected failure");
   if (!bytes) return true;
@@ -84,7 +92,7 @@ struct DevBuf {
   void* p = nullptr;
   size_t bytes = 0;
   explicit DevBuf(size_t b) : bytes(b) { if (b && rt_ok()) p = rt_malloc(b); }
-  ~DevBuf() { rt_free(p); }
+  ~DevBuf() { rt_free(p, bytes); }
   DevBuf(DevBuf const&) = delete;
   DevBuf& operator=(DevBuf const&) = delete;
   void from_host(void const* src, cudaStream_t s = nullptr) { if (rt_ok() && p && src) rt_h2d(p, src, bytes, s); }
