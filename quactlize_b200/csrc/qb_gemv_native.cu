@@ -27,6 +27,7 @@
 #include <mutex>
 
 #include "qb_device.cuh"
+#include "qb_internal.hpp"
 #include "qb_kquant.cuh"
 #include "qb_runtime.hpp"
 
@@ -388,6 +389,10 @@ int enqueue_native_gemv(uint8_t const* blocks, __half const* x, float* out, int 
   a.status = rt_device_status_ptr();
   int const rows_hint = offsets ? max_rows : m_rows;
   bool const aligned = (reinterpret_cast<uintptr_t>(blocks) % 16 == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0);
+  if (qtype == 12 && !per_row_x && !force_generic && aligned && a.status && rows_hint <= 2) {
+    // one or two activation rows: the single-row kernel, once per row (the second pass hits L2)
+    if (enqueue_q4k_gemv1(blocks, x, out, offsets, n, bpr, a.experts, m_rows, max_rows, a.status, stream)) return 0;
+  }
   if (qtype == 12 && !per_row_x && !force_generic && aligned && a.status) {
     int const mt = rows_hint >= 3 ? 4 : rows_hint == 2 ? 2 : 1;
     a.mtiles = (rows_hint + mt - 1) / mt;

@@ -106,7 +106,8 @@ def test_q4k_fast_kernel_vs_oracle(n, k, m):
     x[0, :7] *= 30.0                                     # outliers exercise the power-of-two activation scaling
     ref = kq.vecdot_dense(blocks, x, n, k, 12)
     out = qb.gguf_vecdot_rows(_cuda(blocks), _cuda(x), n, k, 12)
-    assert kq.max_rel(out.cpu().numpy(), ref) < TOL
+    # 30x outlier activations: the fp16 group sums (8 products each) carry ~2^-11 of the outlier terms
+    assert kq.max_rel(out.cpu().numpy(), ref) < 4e-3
     gen = qb.gguf_vecdot_rows(_cuda(blocks), _cuda(x), n, k, 12, force_generic=True)
     assert kq.max_rel(gen.cpu().numpy(), ref) < TOL
     _wait_ok()
