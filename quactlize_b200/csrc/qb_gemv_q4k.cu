@@ -72,7 +72,7 @@ __device__ __forceinline__ void issue_copy_a(uint32_t dst, void const* src, unsi
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
-constexpr int kQ4MaxPieces = 8;      // 16-byte activation pieces per thread in the prologue: K <= 8*8*256 = 16384
+constexpr int kQ4MaxPieces = 4;      // 16-byte activation pieces per thread in the prologue: K <= 4*8*512 = 16384
 
 // One lane's share (half a block: four groups, 128 weights) of one output row.  `base` is the shared address of the
 // lane's block, `code` of its 64 code bytes.
@@ -122,7 +122,7 @@ __device__ __forceinline__ float q4k_half_block_dot(uint32_t base, uint32_t code
 }
 
 template <int STAGES>
-__global__ void __launch_bounds__(256, 2) q4k_gemv1_kernel(Q4Args a) {
+__global__ void __launch_bounds__(512, 1) q4k_gemv1_kernel(Q4Args a) {
   extern __shared__ __align__(128) uint8_t smem[];
   // the warp index is broadcast from lane 0 so the compiler keeps everything derived from it in uniform registers
   int const T = blockDim.x, W = T >> 5, warp = __shfl_sync(0xffffffffu, int(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
@@ -328,7 +328,7 @@ __global__ void __launch_bounds__(256, 2) q4k_gemv1_kernel(Q4Args a) {
 
 namespace {
 struct Q4Plan1 { int S, nbs, RS, iters, gx, W; size_t smem; bool ok; };
-constexpr int kStages1 = 3;          // x two rows per stage
+constexpr int kStages1 = 2;          // x two rows per stage, 16 warps per SM
 
 Q4Plan1 const& q4k_plan1(int n, int bpr, int gy) {
   struct Key { int n, bpr, gy, dev; bool operator<(Key const& o) const {
@@ -344,10 +344,10 @@ Q4Plan1 const& q4k_plan1(int n, int bpr, int gy) {
   Q4Plan1 p{};
   auto kern = q4k_gemv1_kernel<kStages1>;
   p.S = (bpr + 15) / 16;
-  p.ok = p.S <= 8 && bpr * 256 <= kQ4MaxPieces * 8 * 256;       // 256 threads x 8 pieces x 8 elements
+  p.ok = p.S <= 16;
   if (p.ok) {
     p.nbs = (bpr + p.S - 1) / p.S;
-    p.RS = std::max(1, 8 / p.S);
+    p.RS = std::max(1, 16 / p.S);          // one CTA of up to 16 warps per SM shares a single activation prologue
     p.W = p.S * p.RS;
     if (p.W * 32 * kQ4MaxPieces * 8 < bpr * 256) p.ok = false;
     size_t const fixed = size_t(bpr) * 512 + size_t(bpr) * 32 + 128 + size_t(p.W) * kStages1 * (2 * p.nbs * 144 + 8);
