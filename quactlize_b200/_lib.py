@@ -6,7 +6,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "csrc", "libquactlize_b200.so")
+# QUACTLIZE_B200_LIB selects another build of the same library (as QUACTLIZE_PPU_LIB does for the reference loader)
+LIB_PATH = os.environ.get("QUACTLIZE_B200_LIB") or os.path.join(_HERE, "csrc", "libquactlize_b200.so")
 _lib = None
 
 P, I, I64 = C.c_void_p, C.c_int, C.c_int64

@@ -72,7 +72,11 @@ __device__ __forceinline__ void issue_copy_a(uint32_t dst, void const* src, unsi
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
-constexpr int kQ4MaxPieces = 4;      // 16-byte activation pieces per thread in the prologue: K <= 4*8*512 = 16384
+constexpr int kQ4MaxPieces = 4;      // 16-byte activation pieces per thread in the prologue (K <= 16384 at 512+ threads)
+#ifndef QB_Q4_WARPS
+#define QB_Q4_WARPS 16
+#endif
+constexpr int kQ4Warps = QB_Q4_WARPS;         // warps per CTA (one CTA per SM); bounded by registers: 65536 / (32 * regs)
 
 // One lane's share (half a block: four groups, 128 weights) of one output row.  `base` is the shared address of the
 // lane's block, `code` of its 64 code bytes.
@@ -82,9 +86,13 @@ __device__ __forceinline__ float q4k_half_block_dot(uint32_t base, uint32_t code
   uint4 const hdr = lds128_a(base);
   // groups 0-3 (prt 0): the low six bits of scale bytes 0-3 / 4-7; groups 4-7 (prt 1): nibbles of bytes 8-11 plus the
   // top two bits of bytes 0-3 / 4-7.  Both forms are  (A & ma) | ((B >> 2) & mb)  with per-lane constants.
+#if defined(QB_ABL_NOHDR)
+  uint32_t const sc4 = hdr.y, mn4 = hdr.z;
+#else
   uint32_t const sA = prt ? hdr.w : hdr.y, mA = prt ? (hdr.w >> 4) : hdr.z;
   uint32_t const sc4 = (sA & mask_a) | ((hdr.y >> 2) & mask_b);
   uint32_t const mn4 = (mA & mask_a) | ((hdr.z >> 2) & mask_b);
+#endif
   __half2 const k1024 = __float2half2_rn(1024.f);
   __half2 sch[4];                                               // the four sub-scales as exact fp16 integers, broadcast
   sch[0] = __hsub2(u32_as_h2(__byte_perm(sc4, 0x64646464u, 0x4040)), k1024);
@@ -98,6 +106,9 @@ __device__ __forceinline__ float q4k_half_block_dot(uint32_t base, uint32_t code
     uint4 const qv = lds128_a(code + 16u * c);
     uint32_t const qw[4] = {qv.x, qv.y, qv.z, qv.w};
     __half2 alo, ahi;
+#if defined(QB_ABL_NOCORE)
+    alo = u32_as_h2((qw[0] ^ qw[1]) & 0x03FF03FFu); ahi = u32_as_h2((qw[2] ^ qw[3]) & 0x03FF03FFu);
+#else
 #pragma unroll
     for (int wi = 0; wi < 4; ++wi) {
       uint32_t const w = qw[wi], w8 = w >> 8;
@@ -111,10 +122,14 @@ __device__ __forceinline__ float q4k_half_block_dot(uint32_t base, uint32_t code
       alo = __hfma2(u32_as_h2(w8 & 0x000F000Fu), xr[c][4 * wi + 1], alo);
       ahi = __hfma2(u32_as_h2(w8 & 0x00F000F0u), xr[c][4 * wi + 3], ahi);
     }
+#endif
     // chunks 2j and 2j+1 cover the same two groups: scale in fp16, one fp32 flush per chunk pair
     if ((c & 1) == 0) pair = __hfma2(ahi, sch[c + 1], __hmul2(alo, sch[c]));
     else dsum += h2_sum(__hfma2(ahi, sch[c], __hfma2(alo, sch[c - 1], pair)));
   }
+#if defined(QB_ABL_NOMIN)
+  return __low2float(u32_as_h2(hdr.x)) * fm * dsum;
+#endif
   float2 const dd = __half22float2(u32_as_h2(hdr.x));           // (d, dmin)
   float2 const m01 = bytes_to_f2(mn4, 0x4140), m23 = bytes_to_f2(mn4, 0x4342);   // mins * 2^-24
   float const msum = fmaf(m01.x, sxg[0], fmaf(m01.y, sxg[1], fmaf(m23.x, sxg[2], m23.y * sxg[3])));
@@ -122,7 +137,7 @@ __device__ __forceinline__ float q4k_half_block_dot(uint32_t base, uint32_t code
 }
 
 template <int STAGES>
-__global__ void __launch_bounds__(512, 1) q4k_gemv1_kernel(Q4Args a) {
+__global__ void __launch_bounds__(kQ4Warps * 32, 1) q4k_gemv1_kernel(Q4Args a) {
   extern __shared__ __align__(128) uint8_t smem[];
   // the warp index is broadcast from lane 0 so the compiler keeps everything derived from it in uniform registers
   int const T = blockDim.x, W = T >> 5, warp = __shfl_sync(0xffffffffu, int(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
@@ -136,6 +151,12 @@ __global__ void __launch_bounds__(512, 1) q4k_gemv1_kernel(Q4Args a) {
   } else {
     arow = blockIdx.y;
   }
+#if defined(QB_ABL_EMPTY)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (threadIdx.x == 0 && blockIdx.x == 0) a.out[0] = 1.f;
+  return;
+#endif
   int const bpr = a.bpr, k = bpr * 256;
   // shared memory map
   uint32_t const s0 = smem_u32(smem);
@@ -286,18 +307,12 @@ __global__ void __launch_bounds__(512, 1) q4k_gemv1_kernel(Q4Args a) {
   int st = 0;
   int lr = 2 * rslot;                                            // CTA-local row of the pair's first row
   int const lr_step = 2 * a.RS;
-  int i = 0;
-  for (; i < n_my; ++i) {
-    if (!try_wait_a(st_bar, phase) && !slow_wait_a(st_bar, phase, a.status, kWaitNs)) break;
-    bool const two = lr + 1 < nrows;
-    float t0 = 0.f, t1 = 0.f;
-    if (active) {
-      t0 = q4k_half_block_dot(st_addr + lane_off, st_addr + code_off, xr, sxg, prt, mask_a, mask_b, fm);
-      if (two) t1 = q4k_half_block_dot(st_addr + seg_bytes + lane_off, st_addr + seg_bytes + code_off, xr, sxg, prt, mask_a, mask_b, fm);
-    }
-    __syncwarp();
-    if (lane == 0 && i + STAGES < n_my) issue_pair(st_addr, st_bar);
-    // two-value warp reduction: the lower half-warp ends up with row 0, the upper with row 1
+  // The loop body is branch-free apart from the wait and the single-lane refill: lanes without a block and the missing
+  // second row of an odd tail compute on whatever the buffer holds and are masked at the end, and the warp reduction
+  // of pair i-1 is carried into iteration i so its shuffle latency hides under the next pair's arithmetic.
+  float p0 = 0.f, p1 = 0.f;                                      // previous pair's per-lane partial sums
+  int plr = nrows;                                               // ... and its CTA-local row (nrows = scratch slot)
+  auto reduce_store = [&](float t0, float t1, int row_l) {
     float v = (lane & 16) ? t1 : t0;
     float const u = (lane & 16) ? t0 : t1;
     v += __shfl_xor_sync(0xffffffffu, u, 16);
@@ -305,11 +320,28 @@ __global__ void __launch_bounds__(512, 1) q4k_gemv1_kernel(Q4Args a) {
     v += __shfl_xor_sync(0xffffffffu, v, 4);
     v += __shfl_xor_sync(0xffffffffu, v, 2);
     v += __shfl_xor_sync(0xffffffffu, v, 1);
-    if ((lane & 15) == 0 && (lane == 0 || two)) part[(lr + (lane >> 4)) * a.S + seg] = v;
+    if ((lane & 15) == 0) part[(row_l + (lane >> 4)) * a.S + seg] = v;   // rows nrows, nrows+1 are scratch
+  };
+  int i = 0;
+  for (; i < n_my; ++i) {
+    if (!try_wait_a(st_bar, phase) && !slow_wait_a(st_bar, phase, a.status, kWaitNs)) break;
+#if defined(QB_ABL_NOCOMPUTE)
+    float t0 = __uint_as_float(lds128_a(st_addr + lane_off).x & 0x3FFFFFFFu), t1 = 0.f;
+#else
+    float t0 = q4k_half_block_dot(st_addr + lane_off, st_addr + code_off, xr, sxg, prt, mask_a, mask_b, fm);
+    float t1 = q4k_half_block_dot(st_addr + seg_bytes + lane_off, st_addr + seg_bytes + code_off, xr, sxg, prt, mask_a, mask_b, fm);
+#endif
+    reduce_store(p0, p1, plr);
+    p0 = active ? t0 : 0.f;
+    p1 = (active && lr + 1 < nrows) ? t1 : 0.f;
+    plr = lr;
+    __syncwarp();
+    if (lane == 0 && i + STAGES < n_my) issue_pair(st_addr, st_bar);
     lr += lr_step;
     st_addr += stage_bytes; st_bar += 8u;
     if (++st == STAGES) { st = 0; st_addr = ring32; st_bar = bar32; phase ^= 1u; }
   }
+  reduce_store(p0, p1, plr);
   if (i < n_my) {
     // a wait gave up: drain this warp's other copies still in flight (bounded, short) before the shared memory can be
     // handed to another CTA
@@ -344,10 +376,10 @@ Q4Plan1 const& q4k_plan1(int n, int bpr, int gy) {
   Q4Plan1 p{};
   auto kern = q4k_gemv1_kernel<kStages1>;
   p.S = (bpr + 15) / 16;
-  p.ok = p.S <= 16;
+  p.ok = p.S <= kQ4Warps;
   if (p.ok) {
     p.nbs = (bpr + p.S - 1) / p.S;
-    p.RS = std::max(1, 16 / p.S);          // one CTA of up to 16 warps per SM shares a single activation prologue
+    p.RS = std::max(1, kQ4Warps / p.S);   // one CTA per SM shares a single activation prologue
     p.W = p.S * p.RS;
     if (p.W * 32 * kQ4MaxPieces * 8 < bpr * 256) p.ok = false;
     size_t const fixed = size_t(bpr) * 512 + size_t(bpr) * 32 + 128 + size_t(p.W) * kStages1 * (2 * p.nbs * 144 + 8);
@@ -360,7 +392,7 @@ Q4Plan1 const& q4k_plan1(int n, int bpr, int gy) {
     int const resident = std::max(1, occ * sms / std::max(1, std::min(gy, 8)));
     p.gx = std::max(1, std::min(resident, (n + p.RS - 1) / p.RS));
     p.iters = ((n + p.gx - 1) / p.gx + p.RS - 1) / p.RS;          // rows per slot in the largest CTA
-    p.smem = fixed + size_t((n + p.gx - 1) / p.gx + 2) * p.S * 4;
+    p.smem = fixed + size_t((n + p.gx - 1) / p.gx + 4) * p.S * 4;
     if (p.smem > 227 * 1024) p.ok = false;
   }
   return cache.emplace(key, p).first->second;
