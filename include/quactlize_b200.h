@@ -132,6 +132,89 @@ int quactlize_b200_gemv_plane_dev_v1(void const* act, uint8_t const* low, uint8_
                                      int bits_hi, int group_size, int code_offset, int act_dtype, int out_dtype,
                                      int experts, int const* offsets, int max_rows, void* stream);
 
+/* ================================ tensor-core mixed-input GEMM (dense fpA_intB, MoE grouped) ===================== */
+
+/* Config inventory.  quactlize/include/quactlize_ppu_config.h:42-71, quactlize/csrc/device/ppu_dense_backend.cu:603-664.
+ * One tensor-core tactic is compiled ("128x128x64:tcgen05:s4"); an unknown name logs a decline and runs it. */
+int32_t quactlize_ppu_list_configs(quactlize_ppu_config_v1 const** configs);
+int32_t quactlize_ppu_list_grouped_configs(quactlize_ppu_config_v1 const** configs);
+int32_t quactlize_ppu_list_valid_dense_lowbit_configs_v2(quactlize_ppu_config_v2* configs, int32_t capacity, int m, int n,
+                                                         int k, int group_size, int qtype);
+int32_t quactlize_ppu_list_valid_dense_fully_quantized_configs_v2(quactlize_ppu_config_v2* configs, int32_t capacity, int m,
+                                                                  int n, int k, int group_size, int qtype);
+int32_t quactlize_ppu_list_valid_grouped_fully_quantized_configs_v2(quactlize_ppu_config_v2* configs, int32_t capacity,
+                                                                    int total_rows, int n, int k, int group_size, int experts,
+                                                                    int max_rows, int qtype);
+int32_t quactlize_ppu_dense_lowbit_config_valid_v1(int m, int n, int k, int group_size, int qtype, char const* config_name);
+int32_t quactlize_ppu_dense_fully_quantized_config_valid_v1(int m, int n, int k, int group_size, int qtype, char const* config_name);
+int32_t quactlize_ppu_grouped_lowbit_config_valid_v1(int total_rows, int n, int k, int group_size, int experts, int max_rows,
+                                                     int qtype, char const* config_name);
+int32_t quactlize_ppu_grouped_fully_quantized_config_valid_v1(int total_rows, int n, int k, int group_size, int experts,
+                                                              int max_rows, int qtype, char const* config_name);
+
+/* Dense scale-first GEMM, D fp16 [m][n] = A fp16 [m][k] * W^T; W = cvt(u)*scale + zero with the reference converter's
+ * convention cvt(u) = u - 8 for the int4-low formats (Q4_K/Q5_K/Q6_K) and u for Q2_K/Q3_K.
+ * ppu_dense_backend.cu:666-734. */
+int quactlize_ppu_dense_lowbit(uint16_t const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale,
+                               uint16_t const* zero, uint16_t* out, int m, int n, int k, int group_size, int qtype);
+int quactlize_ppu_dense_lowbit_config_v1(uint16_t const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale,
+                                         uint16_t const* zero, uint16_t* out, int m, int n, int k, int group_size, int qtype,
+                                         char const* config_name);
+/* Dense fully-quantized GEMM (planes + packed units).  ppu_dense_backend.cu:741-846, quactlize_ppu_device.h:34-45.
+ * The workspace (size from the query) receives the fp16 scale/zero planes derived from the units. */
+int quactlize_ppu_dense_fully_quantized(uint16_t const* act, uint8_t const* low, uint8_t const* high, uint8_t const* units,
+                                        uint16_t* out, int m, int n, int k, int qtype);
+int quactlize_ppu_dense_fully_quantized_config_v1(uint16_t const* act, uint8_t const* low, uint8_t const* high,
+                                                  uint8_t const* units, uint16_t* out, int m, int n, int k, int qtype,
+                                                  char const* config_name);
+int64_t quactlize_ppu_dense_fully_quantized_workspace_bytes_v1(int m, int n, int k, int qtype);
+int quactlize_ppu_dense_fully_quantized_dev_v1(uint16_t const* act, uint8_t const* low, uint8_t const* high,
+                                               uint8_t const* units, uint16_t* out, int m, int n, int k, int qtype,
+                                               void* workspace, int64_t workspace_bytes, void* stream);
+int quactlize_ppu_dense_fully_quantized_dev_v2(uint16_t const* act, uint8_t const* low, uint8_t const* high,
+                                               uint8_t const* units, uint16_t* out, int m, int n, int k, int qtype,
+                                               void* workspace, int64_t workspace_bytes, void* stream, char const* config_name);
+/* Grouped scale-first GEMM, scale only: W = (u - 2^(W-1))*scale for two-plane formats, (u - 8)*scale for int4, u*scale
+ * for int2.  Host entries take rows_per_expert [E]; device entries cumulative offsets [E+1].
+ * ppu_dense_backend.cu:974-1127, quactlize_ppu_device.h:47-62. */
+int quactlize_ppu_grouped_lowbit(uint16_t const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale,
+                                 int const* rows_per_expert, uint16_t* out, int total_rows, int n, int k, int group_size,
+                                 int experts, int qtype);
+int quactlize_ppu_grouped_lowbit_config_v1(uint16_t const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale,
+                                           int const* rows_per_expert, uint16_t* out, int total_rows, int n, int k,
+                                           int group_size, int experts, int qtype, char const* config_name);
+int64_t quactlize_ppu_grouped_lowbit_workspace_bytes_v1(int max_rows, int n, int k, int group_size, int experts, int qtype);
+int quactlize_ppu_grouped_lowbit_dev_v1(uint16_t const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale,
+                                        int const* offsets, uint16_t* out, int total_rows, int n, int k, int group_size,
+                                        int experts, int max_rows, int qtype, void* workspace, int64_t workspace_bytes,
+                                        void* stream);
+int quactlize_ppu_grouped_lowbit_dev_v2(uint16_t const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale,
+                                        int const* offsets, uint16_t* out, int total_rows, int n, int k, int group_size,
+                                        int experts, int max_rows, int qtype, void* workspace, int64_t workspace_bytes,
+                                        void* stream, char const* config_name);
+/* Grouped fully-quantized GEMM.  ppu_dense_backend.cu:1134-1251, quactlize_ppu_device.h:64-77. */
+int quactlize_ppu_grouped_fully_quantized(uint16_t const* act, uint8_t const* low, uint8_t const* high, uint8_t const* units,
+                                          int const* rows_per_expert, uint16_t* out, int total_rows, int n, int k, int experts,
+                                          int qtype);
+int quactlize_ppu_grouped_fully_quantized_config_v1(uint16_t const* act, uint8_t const* low, uint8_t const* high,
+                                                    uint8_t const* units, int const* rows_per_expert, uint16_t* out,
+                                                    int total_rows, int n, int k, int experts, int qtype, char const* config_name);
+int64_t quactlize_ppu_grouped_fully_quantized_workspace_bytes_v1(int max_rows, int n, int k, int experts, int qtype);
+int quactlize_ppu_grouped_fully_quantized_dev_v1(uint16_t const* act, uint8_t const* low, uint8_t const* high,
+                                                 uint8_t const* units, int const* offsets, uint16_t* out, int total_rows, int n,
+                                                 int k, int experts, int max_rows, int qtype, void* workspace,
+                                                 int64_t workspace_bytes, void* stream);
+int quactlize_ppu_grouped_fully_quantized_dev_v2(uint16_t const* act, uint8_t const* low, uint8_t const* high,
+                                                 uint8_t const* units, int const* offsets, uint16_t* out, int total_rows, int n,
+                                                 int k, int experts, int max_rows, int qtype, void* workspace,
+                                                 int64_t workspace_bytes, void* stream, char const* config_name);
+/* additive: generic per-group plane GEMM, dense (experts == 0) or grouped; W = (lo + 2^bits_lo*hi + code_offset)*scale + zero
+ * (zero may be NULL); act_dtype 0 = fp16, 1 = bf16, output in the activation dtype; n % 128 == 0, k % 256 == 0.  The reference
+ * reaches these shapes only through C++ templates (quactlize/include/moe_grouped_ppu.cuh:363-411). */
+int quactlize_b200_gemm_plane_dev_v1(void const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale,
+                                     uint16_t const* zero, void* out, int total_rows, int n, int k, int bits_lo, int bits_hi,
+                                     int group_size, int code_offset, int act_dtype, int experts, int const* offsets, void* stream);
+
 /* ================================ host-only artifact producers ================================================== */
 
 /* quactlize/include/quactlize_ppu_packed.h:12-33, quactlize/csrc/device/ppu_unit_pack.cpp:186-233 */

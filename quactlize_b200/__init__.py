@@ -439,12 +439,13 @@ def gguf_gemv_bc_moe(a, low, high, units, row_offsets, qtype: int):
 
 
 def gemv_plane(a, low, high, scale, zero, bits_lo: int, bits_hi: int, group_size: int, code_offset: int = 0,
-               row_offsets=None, out_dtype=None):
+               row_offsets=None, out_dtype=None, max_rows=None):
     """Generic per-group plane GEMV (W4A16 / W2A16 / W1A16 ...): W = (lo + 2^bits_lo*hi + code_offset)*scale + zero.
 
     a fp16 or bf16 [rows,k] (CUDA); low uint8 [E,n,k*bits_lo/8]; scale (and optional zero) fp16 [E,k/group_size,n];
     dense when row_offsets is None (E == 1), else ragged with cumulative int32 offsets.  Returns [rows,n] in a's dtype
-    unless out_dtype (torch.float16 / bfloat16 / float32) says otherwise."""
+    unless out_dtype (torch.float16 / bfloat16 / float32) says otherwise.  Passing max_rows (an upper bound on any
+    expert's row count) skips the host-side validation of a device-resident row_offsets, which would synchronise."""
     _check(a.is_cuda and a.dim() == 2 and a.dtype in (torch.float16, torch.bfloat16), "a must be a CUDA fp16/bf16 [rows,k] tensor")
     _u8(low, "low", 3)
     e, n, k = low.shape[0], low.shape[1], a.shape[1]
@@ -461,7 +462,7 @@ def gemv_plane(a, low, high, scale, zero, bits_lo: int, bits_hi: int, group_size
     experts, max_rows, off = 0, rows, None
     if row_offsets is not None:
         experts = e
-        max_rows = _offsets_info(row_offsets, experts, rows)
+        max_rows = int(max_rows) if max_rows is not None else _offsets_info(row_offsets, experts, rows)
         off = row_offsets.to(a.device).contiguous()
     else:
         _check(e == 1, "dense artifact must have one expert dimension")
@@ -474,3 +475,147 @@ def gemv_plane(a, low, high, scale, zero, bits_lo: int, bits_hi: int, group_size
             _p(out), rows, n, k, bits_lo, bits_hi, group_size, int(code_offset), 1 if a.dtype == torch.bfloat16 else 0, ok,
             experts, _p(off), max_rows, _stream(a)), "plane GEMV")
     return out
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# tensor-core mixed-input GEMM
+
+def gemm_plane(a, low, high, scale, zero, bits_lo: int, bits_hi: int, group_size: int, code_offset: int = 0,
+               row_offsets=None):
+    """Generic per-group plane GEMM on the tensor cores: D = a @ W^T, W = (lo + 2^bits_lo*hi + code_offset)*scale + zero.
+
+    a fp16/bf16 [rows,k] (CUDA); low uint8 [E,n,k*bits_lo/8]; scale (and optional zero) fp16 [E,k/group_size,n];
+    dense when row_offsets is None (E == 1), else grouped with cumulative int32 offsets [E+1] on the device (rows
+    gathered in expert order, empty experts allowed).  n % 128 == 0, k % 256 == 0.  Returns [rows,n] in a's dtype."""
+    _check(a.is_cuda and a.dim() == 2 and a.dtype in (torch.float16, torch.bfloat16), "a must be a CUDA fp16/bf16 [rows,k] tensor")
+    _u8(low, "low", 3)
+    e, n, k = low.shape[0], low.shape[1], a.shape[1]
+    _check(low.shape[2] == k * bits_lo // 8, "low plane byte count disagrees with k/bits")
+    if bits_hi:
+        _u8(high, "high", 3)
+        _check(high.shape == (e, n, k * bits_hi // 8), "high plane shape disagrees with bits_hi")
+    _check(scale.dtype == torch.float16 and scale.shape == (e, k // group_size, n), "scale must be fp16 [E,k/group_size,n]")
+    _check(zero is None or (zero.dtype == torch.float16 and zero.shape == scale.shape), "zero must match scale")
+    rows = a.shape[0]
+    out = torch.empty((rows, n), dtype=a.dtype, device=a.device)
+    experts, off = 0, None
+    if row_offsets is not None:
+        _check(row_offsets.dtype == torch.int32 and row_offsets.numel() == e + 1, "row_offsets must be int32 [experts+1]")
+        experts, off = e, row_offsets.to(a.device).contiguous()
+    else:
+        _check(e == 1, "dense artifact must have one expert dimension")
+    if rows == 0:
+        return out
+    a = a.contiguous()
+    with torch.cuda.device(a.device):
+        _rc(_lib.lib().quactlize_b200_gemm_plane_dev_v1(
+            _p(a), _p(low), _p(high) if bits_hi else None, _p(scale.contiguous()),
+            _p(zero.contiguous()) if zero is not None else None, _p(out), rows, n, k, bits_lo, bits_hi, group_size,
+            int(code_offset), 1 if a.dtype == torch.bfloat16 else 0, experts, _p(off), _stream(a)), "plane GEMM")
+    return out
+
+
+def gguf_prepare_dense(blocks, n: int, k: int, qtype: int):
+    """Scale-first dense artifact with the reference's dense contract (gguf_prepass_ops.cpp:884-922): Native planes and
+    fp16 planes whose zero carries +8*scale for the int4-low formats, matching a converter that emits (low - 8)."""
+    g = _geom(qtype)
+    _check(blocks.dim() == 2, "dense preparation takes one [n*k/256,type_size] weight")
+    _check(n % 256 == 0 and k % 256 == 0, "dense fpA tactic needs n and k multiples of 256")
+    low, high, scale, zero = gguf_prepare_gemv(blocks, n, k, qtype)
+    if g.lo_bits == 4:
+        zero = (zero.float() + 8.0 * scale.float()).to(torch.float16)
+    return low, high, scale, zero
+
+
+def gguf_dense_scale_first(a, low, high, scale, zero, qtype: int):
+    """Dense mixed-input GEMM over a resident `gguf_prepare_dense` artifact -> fp16 [m,n]."""
+    g = _geom(qtype)
+    k = a.shape[1] if a.dim() == 2 else 0
+    _planes_check(a, low, high, g, k)
+    n = low.shape[1]
+    _check(low.shape[0] == 1 and n % 256 == 0, "dense fpA shape needs one expert and n a multiple of 256")
+    _check(scale.dtype == torch.float16 and zero.dtype == torch.float16 and scale.shape == zero.shape == (1, k // g.group_size, n),
+           "scale and zero must be fp16 [1,k/group_size,n]")
+    m = a.shape[0]
+    dev = _same_device(a, low, scale, zero)
+    a16 = _f16(a)
+    if m == 0:
+        return torch.empty((0, n), dtype=torch.float16, device=dev)
+    if dev.type == "cpu":
+        out = torch.empty((m, n), dtype=torch.float16)
+        _rc(_lib.lib().quactlize_ppu_dense_lowbit(_p(a16), _p(low), _p(high), _p(scale.contiguous()), _p(zero.contiguous()), _p(out), m, n, k,
+                                                  g.group_size, int(qtype)), "scale-first dense GEMM")
+        return out
+    return gemm_plane(a16, low, high if g.hi_bits else None, scale, zero, g.lo_bits, g.hi_bits, g.group_size,
+                      code_offset=-8 if g.lo_bits == 4 else 0)
+
+
+def _fq_common(a, low, high, units, g, grouped):
+    k = a.shape[1] if a.dim() == 2 else 0
+    _planes_check(a, low, high, g, k)
+    e, n = low.shape[0], low.shape[1]
+    _check(n % 256 == 0 and k % (256 * g.sb_per_unit) == 0, f"fully-quantized GEMM needs n multiple 256 and k multiple {256 * g.sb_per_unit}")
+    nu = k // 256 // g.sb_per_unit
+    _u8(units, "units")
+    want = (e, nu, n, g.unit_total) if grouped else (nu, n, g.unit_total)
+    _check(tuple(units.shape) == want, f"packed units must be {list(want)} for this format, got {list(units.shape)}")
+    return e, n, k
+
+
+def gguf_dense_fully_quantized(a, low, high, units, qtype: int):
+    """Dense GEMM reading the format's own packed scale bytes (planes + units) -> fp16 [m,n]."""
+    g = _geom(qtype)
+    e, n, k = _fq_common(a, low, high, units, g, False)
+    _check(e == 1, "dense artifact must have one expert dimension")
+    m = a.shape[0]
+    dev = _same_device(a, low, units)
+    a16 = _f16(a)
+    out = torch.empty((m, n), dtype=torch.float16, device=dev)
+    if m == 0:
+        return out
+    L = _lib.lib()
+    if dev.type == "cpu":
+        _rc(L.quactlize_ppu_dense_fully_quantized(_p(a16), _p(low), _p(high), _p(units), _p(out), m, n, k, int(qtype)),
+            "fully-quantized dense GEMM")
+    else:
+        need = L.quactlize_ppu_dense_fully_quantized_workspace_bytes_v1(m, n, k, int(qtype))
+        _check(need >= 0, "shape or format refused by the workspace query")
+        ws = torch.empty(need, dtype=torch.uint8, device=dev)
+        with torch.cuda.device(dev):
+            _rc(L.quactlize_ppu_dense_fully_quantized_dev_v1(_p(a16), _p(low), _p(high), _p(units), _p(out), m, n, k, int(qtype),
+                                                             _p(ws), need, _stream(a16)), "fully-quantized dense GEMM")
+    return out
+
+
+def gguf_grouped_fully_quantized(a, low, high, units, rows_per_expert, qtype: int):
+    """Grouped (MoE) GEMM on packed scale bytes; ragged rows, an expert may have none -> fp16 [total_rows,n]."""
+    g = _geom(qtype)
+    e, n, k = _fq_common(a, low, high, units, g, True)
+    _check(rows_per_expert.dtype == torch.int32 and rows_per_expert.dim() == 1 and rows_per_expert.numel() == e,
+           "rows_per_expert must be contiguous int32 [experts]")
+    rp = rows_per_expert.detach().cpu().contiguous()
+    _check(bool((rp >= 0).all()), "expert row counts must be nonnegative")
+    total = int(rp.sum())
+    _check(total == a.shape[0], f"rows_per_expert sums to {total} but a has {a.shape[0]} rows")
+    dev = _same_device(a, low, units)
+    a16 = _f16(a)
+    out = torch.empty((total, n), dtype=torch.float16, device=dev)
+    if total == 0:
+        return out
+    L = _lib.lib()
+    if dev.type == "cpu":
+        _rc(L.quactlize_ppu_grouped_fully_quantized(_p(a16), _p(low), _p(high), _p(units), _p(rp), _p(out), total, n, k, e, int(qtype)),
+            "fully-quantized grouped GEMM")
+    else:
+        off = torch.cat((torch.zeros(1, dtype=torch.int64), rp.to(torch.int64).cumsum(0))).to(torch.int32).to(dev)
+        mr = int(rp.max())
+        need = L.quactlize_ppu_grouped_fully_quantized_workspace_bytes_v1(max(mr, 1), n, k, e, int(qtype))
+        _check(need >= 0, "shape or format refused by the workspace query")
+        ws = torch.empty(need, dtype=torch.uint8, device=dev)
+        with torch.cuda.device(dev):
+            _rc(L.quactlize_ppu_grouped_fully_quantized_dev_v1(_p(a16), _p(low), _p(high), _p(units), _p(off), _p(out), total, n, k, e,
+                                                               max(mr, 1), int(qtype), _p(ws), need, _stream(a16)), "fully-quantized grouped GEMM")
+    return out
+
+
+__all__ += ["gemm_plane", "gguf_prepare_dense", "gguf_dense_scale_first", "gguf_dense_fully_quantized", "gguf_grouped_fully_quantized"]

@@ -43,6 +43,33 @@ SIGNATURES = {
     "quactlize_ppu_bc_gemv_dev_v1": (I, [P, P, P, P, P, P, I, I, I, I, I, I, P]),
     "quactlize_b200_gemv_lowbit_moe_dev_v1": (I, [P, P, P, P, P, P, I, I, I, I, I, I, P, I, P]),
     "quactlize_b200_gemv_plane_dev_v1": (I, [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, I, P]),
+    "quactlize_ppu_list_configs": (C.c_int32, [P]),
+    "quactlize_ppu_list_grouped_configs": (C.c_int32, [P]),
+    "quactlize_ppu_list_valid_dense_lowbit_configs_v2": (C.c_int32, [P, C.c_int32, I, I, I, I, I]),
+    "quactlize_ppu_list_valid_dense_fully_quantized_configs_v2": (C.c_int32, [P, C.c_int32, I, I, I, I, I]),
+    "quactlize_ppu_list_valid_grouped_fully_quantized_configs_v2": (C.c_int32, [P, C.c_int32, I, I, I, I, I, I, I]),
+    "quactlize_ppu_dense_lowbit_config_valid_v1": (C.c_int32, [I, I, I, I, I, C.c_char_p]),
+    "quactlize_ppu_dense_fully_quantized_config_valid_v1": (C.c_int32, [I, I, I, I, I, C.c_char_p]),
+    "quactlize_ppu_grouped_lowbit_config_valid_v1": (C.c_int32, [I, I, I, I, I, I, I, C.c_char_p]),
+    "quactlize_ppu_grouped_fully_quantized_config_valid_v1": (C.c_int32, [I, I, I, I, I, I, I, C.c_char_p]),
+    "quactlize_ppu_dense_lowbit": (I, [P, P, P, P, P, P, I, I, I, I, I]),
+    "quactlize_ppu_dense_lowbit_config_v1": (I, [P, P, P, P, P, P, I, I, I, I, I, C.c_char_p]),
+    "quactlize_ppu_dense_fully_quantized": (I, [P, P, P, P, P, I, I, I, I]),
+    "quactlize_ppu_dense_fully_quantized_config_v1": (I, [P, P, P, P, P, I, I, I, I, C.c_char_p]),
+    "quactlize_ppu_dense_fully_quantized_workspace_bytes_v1": (I64, [I, I, I, I]),
+    "quactlize_ppu_dense_fully_quantized_dev_v1": (I, [P, P, P, P, P, I, I, I, I, P, I64, P]),
+    "quactlize_ppu_dense_fully_quantized_dev_v2": (I, [P, P, P, P, P, I, I, I, I, P, I64, P, C.c_char_p]),
+    "quactlize_ppu_grouped_lowbit": (I, [P, P, P, P, P, P, I, I, I, I, I, I]),
+    "quactlize_ppu_grouped_lowbit_config_v1": (I, [P, P, P, P, P, P, I, I, I, I, I, I, C.c_char_p]),
+    "quactlize_ppu_grouped_lowbit_workspace_bytes_v1": (I64, [I, I, I, I, I, I]),
+    "quactlize_ppu_grouped_lowbit_dev_v1": (I, [P, P, P, P, P, P, I, I, I, I, I, I, I, P, I64, P]),
+    "quactlize_ppu_grouped_lowbit_dev_v2": (I, [P, P, P, P, P, P, I, I, I, I, I, I, I, P, I64, P, C.c_char_p]),
+    "quactlize_ppu_grouped_fully_quantized": (I, [P, P, P, P, P, P, I, I, I, I, I]),
+    "quactlize_ppu_grouped_fully_quantized_config_v1": (I, [P, P, P, P, P, P, I, I, I, I, I, C.c_char_p]),
+    "quactlize_ppu_grouped_fully_quantized_workspace_bytes_v1": (I64, [I, I, I, I, I]),
+    "quactlize_ppu_grouped_fully_quantized_dev_v1": (I, [P, P, P, P, P, P, I, I, I, I, I, I, P, I64, P]),
+    "quactlize_ppu_grouped_fully_quantized_dev_v2": (I, [P, P, P, P, P, P, I, I, I, I, I, I, P, I64, P, C.c_char_p]),
+    "quactlize_b200_gemm_plane_dev_v1": (I, [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P]),
     "quactlize_ppu_units_bytes": (I64, [I, I, I]),
     "quactlize_ppu_prepare_units": (I, [P, P, I, I, I]),
     "quactlize_ppu_prepare_units_grouped": (I, [P, P, I, I, I, I]),

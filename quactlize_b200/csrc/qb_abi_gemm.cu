@@ -1,0 +1,309 @@
+// C ABI of the tensor-core family: dense and grouped mixed-input GEMM over the scale-first artifact (planes + fp16
+// scale/zero) and over the fully-quantized artifact (planes + packed units), plus the config inventory.
+// Signatures and return codes follow quactlize/csrc/device/ppu_dense_backend.cu:603-1251 of the reference
+// (30 bad arguments, 32 wrong group size, 33 unsupported format, 37 workspace too small, 41 runtime failure).
+//
+// Code conventions of the reference's converters, kept at this boundary: the int4-low formats (Q4_K, Q5_K, Q6_K)
+// arrive with zero planes that assume the converter emits (low - 8) (gguf_prepass_ops.cpp:912-920), the int2-low
+// formats (Q2_K, Q3_K) with an unbiased converter; the scale-only grouped entry centres two-plane codes at 2^(W-1).
+// The fully-quantized entries derive fp16 scale/zero planes from the packed units into the caller's workspace
+// (one bit-exact pre-pass launch) and then run the same GEMM.
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+
+#include "qb_internal.hpp"
+#include "qb_kquant.cuh"
+#include "qb_runtime.hpp"
+#include "../../include/quactlize_b200.h"
+
+using namespace qb;
+
+namespace {
+constexpr char const* kTensorConfig = "128x128x64:tcgen05:s4";
+quactlize_ppu_config_v1 const kDenseConfigs[] = {{false, kTensorConfig, 128, 128, 32, 128, 4}, {true, "gemv_lowbit", 0, 0, 0, 0, 0}};
+quactlize_ppu_config_v1 const kGroupedConfigs[] = {{false, kTensorConfig, 128, 128, 32, 128, 4}, {true, "vecdot_moe", 0, 0, 0, 0, 0}};
+
+bool tensor_name_ok(char const* name) { return !name || !name[0] || std::strcmp(name, kTensorConfig) == 0; }
+void decline(char const* name) {
+  if (!tensor_name_ok(name))
+    std::fprintf(stderr, "[quactlize_b200] tensor config '%s' is not compiled in; running default '%s'\n", name, kTensorConfig);
+}
+bool shape_ok(int n, int k) { return n > 0 && n % 256 == 0 && k > 0 && k % 256 == 0; }
+int converter_offset(int qtype) { return (qtype == 12 || qtype == 13 || qtype == 14) ? -8 : 0; }
+int centred_offset(int qtype) {                     // scale-only grouped: centre of the concatenated code
+  int const w = kq::lo_bits(qtype) + kq::hi_bits(qtype);
+  return kq::hi_bits(qtype) ? -(1 << (w - 1)) : (kq::lo_bits(qtype) == 4 ? -8 : 0);
+}
+int sb_per_unit(int qtype) { return (qtype == 11 || qtype == 14) ? 2 : 1; }
+int unit_sb_bytes(int qtype) { return qtype == 10 ? 20 : qtype == 11 ? 14 : qtype == 14 ? 18 : 16; }
+int64_t plane_elems(int n, int k, int experts, int qtype) { return int64_t(experts) * (k / kq::group_size(qtype)) * n; }
+
+GemmDesc kq_desc(void const* act, uint8_t const* low, uint8_t const* high, void const* scale, void const* zero, void* out,
+                 int rows, int n, int k, int qtype, int experts, int const* offsets, int code_offset) {
+  GemmDesc d{};
+  d.act = act; d.low = low; d.high = kq::hi_bits(qtype) ? high : nullptr; d.scale = scale; d.zero = zero; d.out = out;
+  d.offsets = offsets; d.total_rows = rows; d.n = n; d.k = k; d.experts = experts;
+  d.group_size = kq::group_size(qtype); d.lo_bits = kq::lo_bits(qtype); d.hi_bits = kq::hi_bits(qtype);
+  d.code_offset = code_offset; d.act_bf16 = 0;
+  return d;
+}
+
+// cumulative offsets from per-expert row counts; false if a count is negative or the sum disagrees
+bool make_offsets(int const* rows_per_expert, int experts, int total_rows, int* off) {
+  off[0] = 0;
+  for (int e = 0; e < experts; ++e) { if (rows_per_expert[e] < 0) return false; off[e + 1] = off[e] + rows_per_expert[e]; }
+  return off[experts] == total_rows;
+}
+
+// host-pointer scale-first GEMM (dense: experts == 0)
+int host_planes_gemm(uint16_t const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale, uint16_t const* zero,
+                     uint16_t* out, int rows, int n, int k, int qtype, int experts, int const* rows_per_expert,
+                     int code_offset, char const* what) {
+  rt_clear_error();
+  int const we = experts > 0 ? experts : 1;
+  size_t const lo_b = size_t(we) * n * k * kq::lo_bits(qtype) / 8, hi_b = size_t(we) * n * k * kq::hi_bits(qtype) / 8;
+  size_t const pe = size_t(plane_elems(n, k, we, qtype));
+  int offs[1025];
+  if (experts > 1024) return 30;
+  if (experts > 0 && !make_offsets(rows_per_expert, experts, rows, offs)) return 30;
+  DevBuf da(size_t(rows) * k * 2), dl(lo_b), dh(hi_b), ds(pe * 2), dz(zero ? pe * 2 : 0), dout(size_t(rows) * n * 2),
+      doff(experts > 0 ? size_t(experts + 1) * 4 : 0);
+  da.from_host(act); dl.from_host(low); if (hi_b) dh.from_host(high); ds.from_host(scale); if (zero) dz.from_host(zero);
+  if (experts > 0) doff.from_host(offs);
+  if (!rt_ok()) return kRuntimeError;
+  GemmDesc d = kq_desc(da.p, dl.as<uint8_t>(), dh.as<uint8_t>(), ds.p, zero ? dz.p : nullptr, dout.p, rows, n, k, qtype,
+                       experts, doff.as<int>(), code_offset);
+  int const rc = enqueue_mixed_gemm(d, nullptr);
+  if (rc) return rc;
+  if (!rt_check_launch(what) || !rt_sync(nullptr, what) || !rt_device_status_ok(nullptr, what)) return kRuntimeError;
+  return rt_copy_out(dout.p, out, size_t(rows) * n * 2, nullptr) ? 0 : kRuntimeError;
+}
+
+// device-pointer fully-quantized GEMM: units -> fp16 planes in the workspace -> GEMM
+int dev_units_gemm(uint16_t const* act, uint8_t const* low, uint8_t const* high, uint8_t const* units, int const* offsets,
+                   uint16_t* out, int rows, int n, int k, int experts, int qtype, void* workspace, int64_t workspace_bytes,
+                   cudaStream_t s, char const* what) {
+  int const we = experts > 0 ? experts : 1;
+  int64_t const pe = plane_elems(n, k, we, qtype);
+  if (!workspace || workspace_bytes < pe * 4) return 37;
+  __half* sc = reinterpret_cast<__half*>(workspace);
+  __half* zr = sc + pe;
+  rt_clear_error();
+  if (!enqueue_prepass_unit(units, sc, zr, we, n, k / 256, qtype, -(qtype == 11 ? 4 : qtype == 14 ? 32 : 0), s)) return 33;
+  GemmDesc d = kq_desc(act, low, high, sc, zr, out, rows, n, k, qtype, experts, offsets, 0);
+  int const rc = enqueue_mixed_gemm(d, s);
+  if (rc) return rc;
+  return rt_check_launch(what) ? 0 : kRuntimeError;
+}
+
+int host_units_gemm(uint16_t const* act, uint8_t const* low, uint8_t const* high, uint8_t const* units,
+                    int const* rows_per_expert, uint16_t* out, int rows, int n, int k, int experts, int qtype, char const* what) {
+  rt_clear_error();
+  int const we = experts > 0 ? experts : 1;
+  size_t const lo_b = size_t(we) * n * k * kq::lo_bits(qtype) / 8, hi_b = size_t(we) * n * k * kq::hi_bits(qtype) / 8;
+  size_t const un_b = size_t(we) * (k / 256) * n * unit_sb_bytes(qtype);
+  int64_t const pe = plane_elems(n, k, we, qtype);
+  int offs[1025];
+  if (experts > 1024) return 30;
+  if (experts > 0 && !make_offsets(rows_per_expert, experts, rows, offs)) return 30;
+  DevBuf da(size_t(rows) * k * 2), dl(lo_b), dh(hi_b), du(un_b), ws(size_t(pe) * 4), dout(size_t(rows) * n * 2),
+      doff(experts > 0 ? size_t(experts + 1) * 4 : 0);
+  da.from_host(act); dl.from_host(low); if (hi_b) dh.from_host(high); du.from_host(units);
+  if (experts > 0) doff.from_host(offs);
+  if (!rt_ok()) return kRuntimeError;
+  int const rc = dev_units_gemm(da.as<uint16_t>(), dl.as<uint8_t>(), dh.as<uint8_t>(), du.as<uint8_t>(), doff.as<int>(),
+                                dout.as<uint16_t>(), rows, n, k, experts, qtype, ws.p, pe * 4, nullptr, what);
+  if (rc) return rc;
+  if (!rt_sync(nullptr, what) || !rt_device_status_ok(nullptr, what)) return kRuntimeError;
+  return rt_copy_out(dout.p, out, size_t(rows) * n * 2, nullptr) ? 0 : kRuntimeError;
+}
+
+bool fq_ok(int k, int qtype) { return kq::raw_bytes(qtype) != 0 && (k / 256) % sb_per_unit(qtype) == 0; }
+}  // namespace
+
+// ---- config inventory (quactlize/include/quactlize_ppu_config.h:42-119) ------------------------------------------------
+extern "C" int32_t quactlize_ppu_list_configs(quactlize_ppu_config_v1 const** configs) {
+  if (configs) *configs = kDenseConfigs;
+  return 2;
+}
+extern "C" int32_t quactlize_ppu_list_grouped_configs(quactlize_ppu_config_v1 const** configs) {
+  if (configs) *configs = kGroupedConfigs;
+  return 2;
+}
+extern "C" int32_t quactlize_ppu_dense_lowbit_config_valid_v1(int m, int n, int k, int group_size, int qtype, char const* name) {
+  return tensor_name_ok(name) && kq::raw_bytes(qtype) != 0 && m > 0 && shape_ok(n, k) && group_size == kq::group_size(qtype);
+}
+extern "C" int32_t quactlize_ppu_dense_fully_quantized_config_valid_v1(int m, int n, int k, int group_size, int qtype, char const* name) {
+  return quactlize_ppu_dense_lowbit_config_valid_v1(m, n, k, group_size, qtype, name) && fq_ok(k, qtype);
+}
+extern "C" int32_t quactlize_ppu_grouped_lowbit_config_valid_v1(int total_rows, int n, int k, int group_size, int experts,
+                                                                int max_rows, int qtype, char const* name) {
+  return tensor_name_ok(name) && kq::raw_bytes(qtype) != 0 && total_rows > 0 && experts > 0 && max_rows > 0 && shape_ok(n, k) &&
+         group_size == kq::group_size(qtype);
+}
+extern "C" int32_t quactlize_ppu_grouped_fully_quantized_config_valid_v1(int total_rows, int n, int k, int group_size, int experts,
+                                                                         int max_rows, int qtype, char const* name) {
+  return quactlize_ppu_grouped_lowbit_config_valid_v1(total_rows, n, k, group_size, experts, max_rows, qtype, name) && fq_ok(k, qtype);
+}
+static int32_t list_one(quactlize_ppu_config_v2* configs, int32_t capacity, bool valid) {
+  if (valid && configs && capacity > 0) configs[0] = {false, kTensorConfig, 128, 128, 64, 32, 128, 4};
+  return valid ? 1 : 0;
+}
+extern "C" int32_t quactlize_ppu_list_valid_dense_lowbit_configs_v2(quactlize_ppu_config_v2* c, int32_t cap, int m, int n, int k, int gs, int qtype) {
+  return list_one(c, cap, quactlize_ppu_dense_lowbit_config_valid_v1(m, n, k, gs, qtype, nullptr));
+}
+extern "C" int32_t quactlize_ppu_list_valid_dense_fully_quantized_configs_v2(quactlize_ppu_config_v2* c, int32_t cap, int m, int n, int k, int gs, int qtype) {
+  return list_one(c, cap, quactlize_ppu_dense_fully_quantized_config_valid_v1(m, n, k, gs, qtype, nullptr));
+}
+extern "C" int32_t quactlize_ppu_list_valid_grouped_fully_quantized_configs_v2(quactlize_ppu_config_v2* c, int32_t cap, int total_rows,
+                                                                               int n, int k, int gs, int experts, int max_rows, int qtype) {
+  return list_one(c, cap, quactlize_ppu_grouped_fully_quantized_config_valid_v1(total_rows, n, k, gs, experts, max_rows, qtype, nullptr));
+}
+
+// ---- dense, scale-first ------------------------------------------------------------------------------------------------
+extern "C" int quactlize_ppu_dense_lowbit_config_v1(uint16_t const* act, uint8_t const* low, uint8_t const* high,
+                                                    uint16_t const* scale, uint16_t const* zero, uint16_t* out, int m, int n,
+                                                    int k, int group_size, int qtype, char const* config_name) {
+  if (!act || !low || !scale || !zero || !out || m <= 0 || !shape_ok(n, k)) return 30;
+  if (kq::raw_bytes(qtype) == 0) return 33;
+  if (group_size != kq::group_size(qtype) || (kq::hi_bits(qtype) && !high)) return 32;
+  decline(config_name);
+  return host_planes_gemm(act, low, high, scale, zero, out, m, n, k, qtype, 0, nullptr, converter_offset(qtype), "scale-first dense GEMM");
+}
+extern "C" int quactlize_ppu_dense_lowbit(uint16_t const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale,
+                                          uint16_t const* zero, uint16_t* out, int m, int n, int k, int group_size, int qtype) {
+  return quactlize_ppu_dense_lowbit_config_v1(act, low, high, scale, zero, out, m, n, k, group_size, qtype, nullptr);
+}
+
+// ---- dense, fully quantized ----------------------------------------------------------------------------------------------
+extern "C" int quactlize_ppu_dense_fully_quantized_config_v1(uint16_t const* act, uint8_t const* low, uint8_t const* high,
+                                                             uint8_t const* units, uint16_t* out, int m, int n, int k, int qtype,
+                                                             char const* config_name) {
+  if (!act || !low || !units || !out || m <= 0 || !shape_ok(n, k)) return 30;
+  if (!fq_ok(k, qtype) || (kq::hi_bits(qtype) && !high)) return 33;
+  decline(config_name);
+  return host_units_gemm(act, low, high, units, nullptr, out, m, n, k, 0, qtype, "fully-quantized dense GEMM");
+}
+extern "C" int quactlize_ppu_dense_fully_quantized(uint16_t const* act, uint8_t const* low, uint8_t const* high,
+                                                   uint8_t const* units, uint16_t* out, int m, int n, int k, int qtype) {
+  return quactlize_ppu_dense_fully_quantized_config_v1(act, low, high, units, out, m, n, k, qtype, nullptr);
+}
+extern "C" int64_t quactlize_ppu_dense_fully_quantized_workspace_bytes_v1(int m, int n, int k, int qtype) {
+  if (m <= 0 || !shape_ok(n, k) || !fq_ok(k, qtype)) return -1;
+  return plane_elems(n, k, 1, qtype) * 4;
+}
+extern "C" int quactlize_ppu_dense_fully_quantized_dev_v2(uint16_t const* act, uint8_t const* low, uint8_t const* high,
+                                                          uint8_t const* units, uint16_t* out, int m, int n, int k, int qtype,
+                                                          void* workspace, int64_t workspace_bytes, void* stream,
+                                                          char const* config_name) {
+  int64_t const need = quactlize_ppu_dense_fully_quantized_workspace_bytes_v1(m, n, k, qtype);
+  if (!act || !low || !units || !out || !workspace || need < 0 || workspace_bytes < need || (kq::hi_bits(qtype) && !high)) return 30;
+  decline(config_name);
+  return dev_units_gemm(act, low, high, units, nullptr, out, m, n, k, 0, qtype, workspace, workspace_bytes,
+                        static_cast<cudaStream_t>(stream), "fully-quantized dense GEMM enqueue");
+}
+extern "C" int quactlize_ppu_dense_fully_quantized_dev_v1(uint16_t const* act, uint8_t const* low, uint8_t const* high,
+                                                          uint8_t const* units, uint16_t* out, int m, int n, int k, int qtype,
+                                                          void* workspace, int64_t workspace_bytes, void* stream) {
+  return quactlize_ppu_dense_fully_quantized_dev_v2(act, low, high, units, out, m, n, k, qtype, workspace, workspace_bytes, stream, nullptr);
+}
+
+// ---- grouped, scale-first (scale only) -------------------------------------------------------------------------------------
+extern "C" int quactlize_ppu_grouped_lowbit_config_v1(uint16_t const* act, uint8_t const* low, uint8_t const* high,
+                                                      uint16_t const* scale, int const* rows_per_expert, uint16_t* out,
+                                                      int total_rows, int n, int k, int group_size, int experts, int qtype,
+                                                      char const* config_name) {
+  if (!act || !low || !scale || !rows_per_expert || !out || total_rows <= 0 || experts <= 0 || !shape_ok(n, k)) return 30;
+  if (kq::raw_bytes(qtype) == 0) return 33;
+  if (group_size != kq::group_size(qtype) || (kq::hi_bits(qtype) && !high)) return 32;
+  decline(config_name);
+  return host_planes_gemm(act, low, high, scale, nullptr, out, total_rows, n, k, qtype, experts, rows_per_expert,
+                          centred_offset(qtype), "scale-first grouped GEMM");
+}
+extern "C" int quactlize_ppu_grouped_lowbit(uint16_t const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale,
+                                            int const* rows_per_expert, uint16_t* out, int total_rows, int n, int k,
+                                            int group_size, int experts, int qtype) {
+  return quactlize_ppu_grouped_lowbit_config_v1(act, low, high, scale, rows_per_expert, out, total_rows, n, k, group_size, experts, qtype, nullptr);
+}
+extern "C" int64_t quactlize_ppu_grouped_lowbit_workspace_bytes_v1(int max_rows, int n, int k, int group_size, int experts, int qtype) {
+  if (!quactlize_ppu_grouped_lowbit_config_valid_v1(max_rows, n, k, group_size, experts, max_rows, qtype, nullptr)) return -1;
+  return 256;                                   // this implementation needs no device workspace; a token size keeps callers simple
+}
+extern "C" int quactlize_ppu_grouped_lowbit_dev_v2(uint16_t const* act, uint8_t const* low, uint8_t const* high,
+                                                   uint16_t const* scale, int const* offsets, uint16_t* out, int total_rows, int n,
+                                                   int k, int group_size, int experts, int max_rows, int qtype, void* workspace,
+                                                   int64_t workspace_bytes, void* stream, char const* config_name) {
+  (void)workspace;
+  int64_t const need = quactlize_ppu_grouped_lowbit_workspace_bytes_v1(max_rows, n, k, group_size, experts, qtype);
+  if (!act || !low || !scale || !offsets || !out || total_rows <= 0 || need < 0 || workspace_bytes < need ||
+      (kq::hi_bits(qtype) && !high)) return 30;
+  decline(config_name);
+  rt_clear_error();
+  GemmDesc d = kq_desc(act, low, high, scale, nullptr, out, total_rows, n, k, qtype, experts, offsets, centred_offset(qtype));
+  int const rc = enqueue_mixed_gemm(d, static_cast<cudaStream_t>(stream));
+  if (rc) return rc;
+  return rt_check_launch("scale-first grouped GEMM enqueue") ? 0 : kRuntimeError;
+}
+extern "C" int quactlize_ppu_grouped_lowbit_dev_v1(uint16_t const* act, uint8_t const* low, uint8_t const* high,
+                                                   uint16_t const* scale, int const* offsets, uint16_t* out, int total_rows, int n,
+                                                   int k, int group_size, int experts, int max_rows, int qtype, void* workspace,
+                                                   int64_t workspace_bytes, void* stream) {
+  return quactlize_ppu_grouped_lowbit_dev_v2(act, low, high, scale, offsets, out, total_rows, n, k, group_size, experts, max_rows,
+                                             qtype, workspace, workspace_bytes, stream, nullptr);
+}
+
+// ---- grouped, fully quantized ------------------------------------------------------------------------------------------------
+extern "C" int quactlize_ppu_grouped_fully_quantized_config_v1(uint16_t const* act, uint8_t const* low, uint8_t const* high,
+                                                               uint8_t const* units, int const* rows_per_expert, uint16_t* out,
+                                                               int total_rows, int n, int k, int experts, int qtype,
+                                                               char const* config_name) {
+  if (!act || !low || !units || !rows_per_expert || !out || total_rows <= 0 || experts <= 0 || !shape_ok(n, k)) return 30;
+  if (!fq_ok(k, qtype) || (kq::hi_bits(qtype) && !high)) return 33;
+  decline(config_name);
+  return host_units_gemm(act, low, high, units, rows_per_expert, out, total_rows, n, k, experts, qtype, "fully-quantized grouped GEMM");
+}
+extern "C" int quactlize_ppu_grouped_fully_quantized(uint16_t const* act, uint8_t const* low, uint8_t const* high,
+                                                     uint8_t const* units, int const* rows_per_expert, uint16_t* out,
+                                                     int total_rows, int n, int k, int experts, int qtype) {
+  return quactlize_ppu_grouped_fully_quantized_config_v1(act, low, high, units, rows_per_expert, out, total_rows, n, k, experts, qtype, nullptr);
+}
+extern "C" int64_t quactlize_ppu_grouped_fully_quantized_workspace_bytes_v1(int max_rows, int n, int k, int experts, int qtype) {
+  if (max_rows <= 0 || !shape_ok(n, k) || experts <= 0 || !fq_ok(k, qtype)) return -1;
+  return plane_elems(n, k, experts, qtype) * 4;
+}
+extern "C" int quactlize_ppu_grouped_fully_quantized_dev_v2(uint16_t const* act, uint8_t const* low, uint8_t const* high,
+                                                            uint8_t const* units, int const* offsets, uint16_t* out,
+                                                            int total_rows, int n, int k, int experts, int max_rows, int qtype,
+                                                            void* workspace, int64_t workspace_bytes, void* stream,
+                                                            char const* config_name) {
+  int64_t const need = quactlize_ppu_grouped_fully_quantized_workspace_bytes_v1(max_rows, n, k, experts, qtype);
+  if (!act || !low || !units || !offsets || !out || !workspace || total_rows <= 0 || need < 0 || workspace_bytes < need ||
+      (kq::hi_bits(qtype) && !high)) return 30;
+  decline(config_name);
+  return dev_units_gemm(act, low, high, units, offsets, out, total_rows, n, k, experts, qtype, workspace, workspace_bytes,
+                        static_cast<cudaStream_t>(stream), "fully-quantized grouped GEMM enqueue");
+}
+extern "C" int quactlize_ppu_grouped_fully_quantized_dev_v1(uint16_t const* act, uint8_t const* low, uint8_t const* high,
+                                                            uint8_t const* units, int const* offsets, uint16_t* out,
+                                                            int total_rows, int n, int k, int experts, int max_rows, int qtype,
+                                                            void* workspace, int64_t workspace_bytes, void* stream) {
+  return quactlize_ppu_grouped_fully_quantized_dev_v2(act, low, high, units, offsets, out, total_rows, n, k, experts, max_rows,
+                                                      qtype, workspace, workspace_bytes, stream, nullptr);
+}
+
+// ---- additive: generic per-group planes, fp16 or bf16 activations, dense (experts == 0) or grouped ------------------------
+extern "C" int quactlize_b200_gemm_plane_dev_v1(void const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale,
+                                                uint16_t const* zero, void* out, int total_rows, int n, int k, int bits_lo,
+                                                int bits_hi, int group_size, int code_offset, int act_dtype, int experts,
+                                                int const* offsets, void* stream) {
+  if (act_dtype < 0 || act_dtype > 1 || experts < 0) return 30;
+  rt_clear_error();
+  GemmDesc d{};
+  d.act = act; d.low = low; d.high = bits_hi ? high : nullptr; d.scale = scale; d.zero = zero; d.out = out;
+  d.offsets = offsets; d.total_rows = total_rows; d.n = n; d.k = k; d.experts = experts; d.group_size = group_size;
+  d.lo_bits = bits_lo; d.hi_bits = bits_hi; d.code_offset = code_offset; d.act_bf16 = act_dtype;
+  int const rc = enqueue_mixed_gemm(d, static_cast<cudaStream_t>(stream));
+  if (rc) return rc;
+  return rt_check_launch("plane GEMM enqueue") ? 0 : kRuntimeError;
+}

@@ -1,0 +1,457 @@
+// Mixed-input (fp16/bf16 activation x low-bit weight) GEMM on the 5th-generation tensor cores: dense fpA_intB and
+// MoE grouped (ragged rows per expert) in one kernel.
+//
+//   D[m, n] = sum_k A[m, k] * ( (u[n, k] + off) * S[k/gs, n] + Z[k/gs, n] ),     u = lo + 2^LO * hi
+//
+//   A     fp16/bf16 [rows][K] row-major; grouped: rows concatenated in expert order, cumulative int offsets [E+1]
+//   low   [E][N][K*LO/8], high [E][N][K*HI/8]   Native planes (element k of a row at bit k*bits, LSB first)
+//   S, Z  fp16 [E][K/gs][N]  (Z optional)
+//   D     fp16/bf16 [rows][N]
+//
+// Replaces the reference's PPU collectives: dense (quactlize/include/fpA_intB_ppu.cuh:67-194, mainloop
+// quactlize/include/quactlize_extensions/cutlass/gemm/collective/quactlize_mma_mixed_input.hpp:985-1250) and grouped
+// (quactlize/include/ppu_aiu_gemm_mixed_input_group.hpp:35-311, launcher quactlize/include/moe_grouped_ppu.cuh:69-361).
+//
+// One CTA computes a 128 (rows) x 128 (weight columns) tile; K advances in stages of 64.  Warp-specialised:
+//   warp 0      TMA producer: activation tile (SWIZZLE_128B, K-major), raw weight planes, scale/zero rows -> smem ring
+//   warp 1      one elected thread issues tcgen05.mma (M=128, N=128, K=16, fp32 accumulate in TMEM) and commits
+//   warp 2      allocates / frees the 128 TMEM columns
+//   warps 4-7   dequantise: thread = weight column; 64 codes -> 64 fp16/bf16 values written in the UMMA canonical
+//               128-byte-swizzled K-major layout; afterwards the same warps read the accumulator (tcgen05.ld) and
+//               store D
+// Every mbarrier wait is bounded; a wait that gives up raises a CTA-wide abort flag, records a status code, and the
+// CTA drains its copies, frees its TMEM and exits.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+
+#include "qb_device.cuh"
+#include "qb_internal.hpp"
+#include "qb_runtime.hpp"
+
+namespace qb {
+
+constexpr int kTM = 128, kTN = 128, kTK = 64, kGemmStages = 4;
+constexpr int kRawK = 128, kRawStages = 3;          // weight planes and scale rows arrive in 128-k pieces
+constexpr int kATileBytes = kTM * kTK * 2;          // 16 KB
+constexpr int kBTileBytes = kTN * kTK * 2;          // 16 KB
+constexpr int kRawLoMax = kTN * kRawK * 4 / 8;      // 8 KB (int4)
+constexpr int kRawHiMax = kTN * kRawK * 2 / 8;      // 4 KB (int2 high plane)
+constexpr int kScaleRows = kRawK / 16;              // 8 group rows per piece at gs = 16
+constexpr int kScaleBytes = kScaleRows * kTN * 2;   // 2 KB each for scale and zero
+
+struct GemmArgs {
+  int const* offsets;      // cumulative [E+1] (grouped) or nullptr (dense: rows = m_rows)
+  void* out;
+  int m_rows, n, k, experts, group_size;
+  int code_offset, has_zero;
+  unsigned int* status;
+};
+
+struct GemmSmem {
+  alignas(1024) uint8_t a[kGemmStages][kATileBytes];
+  alignas(1024) uint8_t b[kGemmStages][kBTileBytes];
+  alignas(128) uint8_t raw_lo[kRawStages][kRawLoMax];
+  alignas(128) uint8_t raw_hi[kRawStages][kRawHiMax];
+  alignas(128) uint8_t scale[kRawStages][kScaleBytes];
+  alignas(128) uint8_t zero[kRawStages][kScaleBytes];
+  alignas(8) uint64_t a_full[kGemmStages];     // TMA -> MMA (activation tile landed)
+  alignas(8) uint64_t b_full[kGemmStages];     // dequant warps -> MMA (operand tile written)
+  alignas(8) uint64_t empty[kGemmStages];      // MMA (tcgen05.commit) -> TMA and dequant (a[s], b[s] free)
+  alignas(8) uint64_t raw_full[kRawStages];    // TMA -> dequant
+  alignas(8) uint64_t raw_empty[kRawStages];   // dequant -> TMA
+  alignas(8) uint64_t acc_full;                // MMA -> epilogue
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+
+__device__ __forceinline__ void tma_load_2d(void* dst, CUtensorMap const* map, int c0, int c1, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, CUtensorMap const* map, int c0, int c1, int c2, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+// K-major, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart (SBO), version 1, layout type 2
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= uint64_t((smem_addr & 0x3FFFFu) >> 4);
+  d |= uint64_t(1) << 16;                        // leading byte offset (unused for swizzled K-major), 16-byte units
+  d |= uint64_t(1024 >> 4) << 32;                // stride byte offset
+  d |= uint64_t(1) << 46;                        // descriptor version
+  d |= uint64_t(2) << 61;                        // SWIZZLE_128B
+  return d;
+}
+// kind::f16, fp32 accumulate, A and B K-major, M = 128, N = 128; fmt 0 = fp16, 1 = bf16 for both operands
+__host__ __device__ constexpr uint32_t umma_idesc(int fmt, int m, int n) {
+  return (1u << 4) | (uint32_t(fmt) << 7) | (uint32_t(fmt) << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ bool gemm_wait(GemmSmem& sm, uint64_t* bar, unsigned parity, unsigned int* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long const t0 = global_ns();
+  unsigned spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 31u) == 0) {
+      if (sm.abort_flag) return false;
+      if (global_ns() - t0 > kWaitNs) {
+        sm.abort_flag = 1;
+        if (status) atomicCAS(status, 0u, unsigned(kWaitMmaTimeout));
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// ---- dequantisation of one weight column (64 consecutive k) into the swizzled operand row ---------------------------
+
+template <bool BF16> struct Pack2;
+template <> struct Pack2<false> {
+  using T2 = __half2;
+  static constexpr uint32_t kMagic = 0x64006400u;     // 1024 + u, exact for u < 1024
+  __device__ static __forceinline__ T2 bias() { return __float2half2_rn(1024.f); }
+  __device__ static __forceinline__ T2 from_f(float a, float b) { return __floats2half2_rn(a, b); }
+  __device__ static __forceinline__ uint32_t affine(uint32_t v, T2 s, T2 zo) {
+    T2 const u = __hsub2(*reinterpret_cast<T2*>(&v), bias());
+    T2 const w = __hfma2(u, s, zo);
+    return *reinterpret_cast<uint32_t const*>(&w);
+  }
+};
+template <> struct Pack2<true> {
+  using T2 = __nv_bfloat162;
+  static constexpr uint32_t kMagic = 0x43004300u;     // 128 + u, exact for u < 128
+  __device__ static __forceinline__ T2 bias() { return __float2bfloat162_rn(128.f); }
+  __device__ static __forceinline__ T2 from_f(float a, float b) { return __floats2bfloat162_rn(a, b); }
+  __device__ static __forceinline__ uint32_t affine(uint32_t v, T2 s, T2 zo) {
+    T2 const u = __hsub2(*reinterpret_cast<T2*>(&v), bias());
+    T2 const w = __hfma2(u, s, zo);
+    return *reinterpret_cast<uint32_t const*>(&w);
+  }
+};
+
+// lo/hi point at this column's bytes for the 64-k half being converted; sc/zr at [group 0][this column] of the
+// stage's scale rows (row stride kTN halves).  Output: 8 chunks of 16 bytes, chunk c at position c ^ (col & 7).
+template <int LO, int HI, bool BF16>
+__device__ __forceinline__ void dequant_col(uint8_t const* lo, uint8_t const* hi, __half const* sc, __half const* zr,
+                                            int gs, float coff, uint8_t* brow, int col) {
+  using P = Pack2<BF16>;
+  int const gshift = gs >= 64 ? 31 : (gs == 32 ? 2 : 1);          // chunks per group: >= 8 -> one group, 4, or 2
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    int const g = gs >= 64 ? 0 : (c >> gshift);
+    float const s = __half2float(sc[g * kTN]);
+    float const z = (zr ? __half2float(zr[g * kTN]) : 0.f) + coff * s;
+    typename P::T2 const s2 = P::from_f(s, s), z2 = P::from_f(z, z);
+    uint32_t v[4];
+    if constexpr (LO == 4 && HI == 0) {
+      uint32_t const w = *reinterpret_cast<uint32_t const*>(lo + 4 * c), w4 = w >> 4;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)                               // byte j: (low nibble, high nibble) = elements 2j, 2j+1
+        v[j] = (__byte_perm(w, w4, 0x4400u + 0x1111u * j) & 0x000F000Fu) | P::kMagic;
+    } else {
+      uint32_t L = 0, H = 0;
+      if constexpr (LO == 4) L = *reinterpret_cast<uint32_t const*>(lo + 4 * c);
+      else if constexpr (LO == 2) L = *reinterpret_cast<uint16_t const*>(lo + 2 * c);
+      else L = lo[c];
+      if constexpr (HI == 2) H = *reinterpret_cast<uint16_t const*>(hi + 2 * c);
+      else if constexpr (HI == 1) H = hi[c];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t const u0 = ((L >> (2 * j * LO)) & ((1u << LO) - 1u)) | (HI ? (((H >> (2 * j * HI)) & ((1u << HI) - 1u)) << LO) : 0u);
+        uint32_t const u1 = ((L >> ((2 * j + 1) * LO)) & ((1u << LO) - 1u)) | (HI ? (((H >> ((2 * j + 1) * HI)) & ((1u << HI) - 1u)) << LO) : 0u);
+        v[j] = u0 | (u1 << 16) | P::kMagic;
+      }
+    }
+    uint4 o;
+    o.x = P::affine(v[0], s2, z2); o.y = P::affine(v[1], s2, z2);
+    o.z = P::affine(v[2], s2, z2); o.w = P::affine(v[3], s2, z2);
+    *reinterpret_cast<uint4*>(brow + ((c ^ (col & 7)) << 4)) = o;
+  }
+}
+
+// ---- the kernel -----------------------------------------------------------------------------------------------------
+
+template <int LO, int HI, bool BF16>
+__global__ void __launch_bounds__(256, 1)
+mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_lo,
+                  const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ CUtensorMap map_s,
+                  const __grid_constant__ CUtensorMap map_z, GemmArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  GemmSmem& sm = *reinterpret_cast<GemmSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // ---- which tile: blockIdx.x = weight-column tile, blockIdx.y = row tile (grouped: searched in the per-expert counts)
+  int e = 0, m0, mrows;
+  if (g.offsets) {
+    int t = blockIdx.y, acc = 0;
+    bool found = false;
+    for (int x = 0; x < g.experts; ++x) {
+      int const r0 = g.offsets[x], rows = g.offsets[x + 1] - r0, cnt = (rows + kTM - 1) / kTM;
+      if (t < acc + cnt) { e = x; m0 = r0 + (t - acc) * kTM; mrows = min(kTM, rows - (t - acc) * kTM); found = true; break; }
+      acc += cnt;
+    }
+    if (!found) return;                                       // uniform for the CTA, before any barrier or allocation
+  } else {
+    m0 = blockIdx.y * kTM; mrows = min(kTM, g.m_rows - m0);
+    if (mrows <= 0) return;
+  }
+  int const n0 = blockIdx.x * kTN;
+  int const nks = g.k / kTK;                                  // 64-k stages (k is a multiple of 256)
+  int const gs = g.group_size;
+  int const srows = gs >= kRawK ? 1 : kRawK / gs;             // scale rows per 128-k piece
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kGemmStages; ++s) { mbar_init(&sm.a_full[s], 1); mbar_init(&sm.b_full[s], 4); mbar_init(&sm.empty[s], 1); }
+    for (int s = 0; s < kRawStages; ++s) { mbar_init(&sm.raw_full[s], 1); mbar_init(&sm.raw_empty[s], 4); }
+    mbar_init(&sm.acc_full, 1);
+    sm.abort_flag = 0;
+    mbar_init_fence();
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(uint32_t(kTN)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  uint32_t const tmem = sm.tmem_base;
+
+  if (warp == 0) {
+    // ================= TMA producer =================
+    if (lane == 0) {
+      unsigned const raw_bytes = unsigned(kTN * kRawK * LO / 8) + unsigned(kTN * kRawK * HI / 8) +
+                                 unsigned(srows * kTN * 2) * (g.has_zero ? 2u : 1u);
+      for (int i = 0; i < nks; ++i) {
+        int const s = i % kGemmStages;
+        if ((i & 1) == 0) {
+          int const j = i >> 1, r = j % kRawStages;
+          if (j >= kRawStages && !gemm_wait(sm, &sm.raw_empty[r], unsigned(j / kRawStages - 1) & 1u, g.status)) break;
+          mbar_expect_tx(&sm.raw_full[r], raw_bytes);
+          int const kk = j * kRawK;
+          tma_load_3d(sm.raw_lo[r], &map_lo, kk * LO / 8, n0, e, &sm.raw_full[r]);
+          if constexpr (HI != 0) tma_load_3d(sm.raw_hi[r], &map_hi, kk * HI / 8, n0, e, &sm.raw_full[r]);
+          tma_load_3d(sm.scale[r], &map_s, n0, kk / gs, e, &sm.raw_full[r]);
+          if (g.has_zero) tma_load_3d(sm.zero[r], &map_z, n0, kk / gs, e, &sm.raw_full[r]);
+        }
+        if (i >= kGemmStages && !gemm_wait(sm, &sm.empty[s], unsigned(i / kGemmStages - 1) & 1u, g.status)) break;
+        mbar_expect_tx(&sm.a_full[s], kATileBytes);
+        tma_load_2d(sm.a[s], &map_a, i * kTK, m0, &sm.a_full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    // ================= MMA issuer =================
+    if (lane == 0) {
+      uint32_t const idesc = umma_idesc(BF16 ? 1 : 0, kTM, kTN);
+      bool ok = true;
+      for (int i = 0; i < nks && ok; ++i) {
+        int const s = i % kGemmStages;
+        unsigned const ph = unsigned(i / kGemmStages) & 1u;
+        ok = gemm_wait(sm, &sm.a_full[s], ph, g.status) && gemm_wait(sm, &sm.b_full[s], ph, g.status);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        uint32_t const a_addr = smem_u32(sm.a[s]), b_addr = smem_u32(sm.b[s]);
+#pragma unroll
+        for (int kk = 0; kk < kTK / 16; ++kk)
+          umma_f16(tmem, umma_desc_sw128(a_addr + kk * 32), umma_desc_sw128(b_addr + kk * 32), idesc, (i | kk) ? 1u : 0u);
+        umma_commit(&sm.empty[s]);                             // frees a[s] and b[s] once these MMAs have read them
+      }
+      if (ok) umma_commit(&sm.acc_full);
+    }
+  } else if (warp >= 4) {
+    // ================= dequantise (thread = weight column), then epilogue =================
+    int const col = threadIdx.x - 128;
+    float const coff = float(g.code_offset);
+    bool ok = true;
+    for (int i = 0; i < nks && ok; ++i) {
+      int const s = i % kGemmStages, j = i >> 1, r = j % kRawStages, h = i & 1;
+      if (h == 0) ok = gemm_wait(sm, &sm.raw_full[r], unsigned(j / kRawStages) & 1u, g.status);
+      if (ok && i >= kGemmStages) ok = gemm_wait(sm, &sm.empty[s], unsigned(i / kGemmStages - 1) & 1u, g.status);
+      if (!ok) break;
+      int const srow = gs >= kRawK ? 0 : h * (srows / 2);
+      dequant_col<LO, HI, BF16>(sm.raw_lo[r] + col * (kRawK * LO / 8) + h * (kTK * LO / 8),
+                                sm.raw_hi[r] + col * (kRawK * HI / 8) + h * (kTK * HI / 8),
+                                reinterpret_cast<__half const*>(sm.scale[r]) + srow * kTN + col,
+                                g.has_zero ? reinterpret_cast<__half const*>(sm.zero[r]) + srow * kTN + col : nullptr,
+                                gs, coff, sm.b[s] + col * 128, col);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes -> visible to the MMA
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&sm.b_full[s]);
+        if (h == 1) mbar_arrive(&sm.raw_empty[r]);
+      }
+    }
+    // epilogue: this warp owns TMEM lanes 32*(warp%4) .. +31 = output rows of the tile
+    if (ok) ok = gemm_wait(sm, &sm.acc_full, 0, g.status);
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      int const q = warp & 3, row = q * 32 + lane;
+      size_t const orow = size_t(m0 + row) * g.n + n0;
+#pragma unroll 1
+      for (int c = 0; c < kTN; c += 32) {
+        uint32_t v[32];
+        uint32_t const taddr = tmem + (uint32_t(q * 32) << 16) + uint32_t(c);
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+            "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+              "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+              "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+              "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+            : "r"(taddr) : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row < mrows) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int t = 0; t < 16; ++t) {
+            float const f0 = __uint_as_float(v[2 * t]), f1 = __uint_as_float(v[2 * t + 1]);
+            if constexpr (BF16) { __nv_bfloat162 const hh = __floats2bfloat162_rn(f0, f1); pk[t] = *reinterpret_cast<uint32_t const*>(&hh); }
+            else { __half2 const hh = __floats2half2_rn(f0, f1); pk[t] = *reinterpret_cast<uint32_t const*>(&hh); }
+          }
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(g.out) + orow + c);
+#pragma unroll
+          for (int t = 0; t < 4; ++t) dst[t] = make_uint4(pk[4 * t], pk[4 * t + 1], pk[4 * t + 2], pk[4 * t + 3]);
+        }
+      }
+    }
+  }
+  // ---- teardown: everyone meets here (all waits are bounded), then the allocating warp frees the TMEM columns
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (sm.abort_flag && threadIdx.x == 0) {
+    // drain copies that may still be in flight so they do not land in shared memory handed to another CTA
+    for (int s = 0; s < kGemmStages; ++s) { (void)mbar_wait_bounded(&sm.a_full[s], 0, nullptr, 0, 100000000ull); (void)mbar_wait_bounded(&sm.a_full[s], 1, nullptr, 0, 100000000ull); }
+    for (int s = 0; s < kRawStages; ++s) { (void)mbar_wait_bounded(&sm.raw_full[s], 0, nullptr, 0, 100000000ull); (void)mbar_wait_bounded(&sm.raw_full[s], 1, nullptr, 0, 100000000ull); }
+  }
+  __syncthreads();
+  if (warp == 2) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(uint32_t(kTN)) : "memory");
+  }
+}
+
+// ---- host side: tensor maps and launch ---------------------------------------------------------------------------------
+
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, cuuint64_t const*, cuuint64_t const*,
+                                   cuuint32_t const*, cuuint32_t const*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    else
+      (void)cudaGetLastError();
+  });
+  return fn;
+}
+
+bool make_map(CUtensorMap* m, CUtensorMapDataType dt, int rank, void const* base, cuuint64_t const* dims,
+              cuuint64_t const* strides_bytes, cuuint32_t const* box, CUtensorMapSwizzle sw) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint32_t const ones[3] = {1, 1, 1};
+  return fn(m, dt, cuuint32_t(rank), const_cast<void*>(base), dims, strides_bytes, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int LO, int HI, bool BF16>
+int launch_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
+  int const E = d.experts > 0 ? d.experts : 1;
+  int const gs = d.group_size;
+  int const srows = gs >= kRawK ? 1 : kRawK / gs;
+  CUtensorMap ma, ml, mh, ms, mz;
+  {
+    cuuint64_t dims[2] = {cuuint64_t(d.k), cuuint64_t(d.total_rows)};
+    cuuint64_t str[1] = {cuuint64_t(d.k) * 2};
+    cuuint32_t box[2] = {cuuint32_t(kTK), cuuint32_t(kTM)};
+    if (!make_map(&ma, BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, d.act, dims, str, box,
+                  CU_TENSOR_MAP_SWIZZLE_128B)) return kRuntimeError;
+  }
+  {
+    cuuint64_t const rb = cuuint64_t(d.k) * LO / 8;
+    cuuint64_t dims[3] = {rb, cuuint64_t(d.n), cuuint64_t(E)};
+    cuuint64_t str[2] = {rb, rb * d.n};
+    cuuint32_t box[3] = {cuuint32_t(kRawK * LO / 8), cuuint32_t(kTN), 1};
+    if (!make_map(&ml, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.low, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
+  }
+  if constexpr (HI != 0) {
+    cuuint64_t const rb = cuuint64_t(d.k) * HI / 8;
+    cuuint64_t dims[3] = {rb, cuuint64_t(d.n), cuuint64_t(E)};
+    cuuint64_t str[2] = {rb, rb * d.n};
+    cuuint32_t box[3] = {cuuint32_t(kRawK * HI / 8), cuuint32_t(kTN), 1};
+    if (!make_map(&mh, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.high, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
+  } else {
+    mh = ml;
+  }
+  {
+    cuuint64_t const kg = cuuint64_t(d.k / gs);
+    cuuint64_t dims[3] = {cuuint64_t(d.n), kg, cuuint64_t(E)};
+    cuuint64_t str[2] = {cuuint64_t(d.n) * 2, cuuint64_t(d.n) * 2 * kg};
+    cuuint32_t box[3] = {cuuint32_t(kTN), cuuint32_t(srows), 1};
+    if (!make_map(&ms, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, d.scale, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
+    if (d.zero) {
+      if (!make_map(&mz, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, d.zero, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
+    } else {
+      mz = ms;
+    }
+  }
+  GemmArgs g{};
+  g.offsets = d.experts > 0 ? d.offsets : nullptr;
+  g.out = d.out; g.m_rows = d.total_rows; g.n = d.n; g.k = d.k; g.experts = E; g.group_size = gs;
+  g.code_offset = d.code_offset; g.has_zero = d.zero ? 1 : 0;
+  g.status = rt_device_status_ptr();
+  if (!g.status) return kRuntimeError;
+  auto kern = mixed_gemm_kernel<LO, HI, BF16>;
+  size_t const smem = sizeof(GemmSmem) + 1024;
+  static bool attr_set = false;
+  if (!attr_set) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); attr_set = true; }
+  int const mtiles = (d.total_rows + kTM - 1) / kTM + (d.experts > 0 ? d.experts : 0);
+  if (mtiles > 65535) return 30;
+  kern<<<dim3(d.n / kTN, mtiles), 256, smem, stream>>>(ma, ml, mh, ms, mz, g);
+  return 0;
+}
+
+}  // namespace
+
+int enqueue_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
+  if (!d.act || !d.low || !d.scale || !d.out || d.total_rows <= 0 || d.n <= 0 || d.n % kTN || d.k <= 0 || d.k % 256 ||
+      d.group_size < 16 || (d.group_size & (d.group_size - 1)) || d.k % d.group_size || (d.hi_bits && !d.high) ||
+      (d.experts > 0 && !d.offsets)) return 30;
+  auto al = [](void const* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  if (!al(d.act) || !al(d.low) || !al(d.scale) || !al(d.out) || (d.zero && !al(d.zero)) || (d.hi_bits && !al(d.high))) return 30;
+  int const key = d.lo_bits * 10 + d.hi_bits;
+#define QB_GEMM_CASE(K, L, H) case K: return d.act_bf16 ? launch_mixed_gemm<L, H, true>(d, stream) : launch_mixed_gemm<L, H, false>(d, stream);
+  switch (key) {
+    QB_GEMM_CASE(40, 4, 0) QB_GEMM_CASE(41, 4, 1) QB_GEMM_CASE(42, 4, 2) QB_GEMM_CASE(20, 2, 0) QB_GEMM_CASE(21, 2, 1)
+    QB_GEMM_CASE(10, 1, 0)
+    default: return 33;
+  }
+#undef QB_GEMM_CASE
+}
+
+}  // namespace qb

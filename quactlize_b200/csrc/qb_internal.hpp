@@ -37,4 +37,17 @@ struct PlaneGemvDesc {
 };
 int enqueue_plane_gemv(PlaneGemvDesc const& d, cudaStream_t stream);   // 0 ok, 40 unsupported shape
 
+// Tensor-core mixed-input GEMM (dense when experts == 0, else grouped with cumulative offsets).
+struct GemmDesc {
+  void const* act;            // fp16 or bf16 [total_rows][k]
+  uint8_t const* low;         // [E][n][k*lo_bits/8]
+  uint8_t const* high;        // [E][n][k*hi_bits/8] or nullptr
+  void const* scale;          // fp16 [E][k/gs][n]
+  void const* zero;           // fp16 [E][k/gs][n] or nullptr
+  void* out;                  // act dtype [total_rows][n]
+  int const* offsets;         // cumulative device int [experts+1] (grouped)
+  int total_rows, n, k, experts, group_size, lo_bits, hi_bits, code_offset, act_bf16;
+};
+int enqueue_mixed_gemm(GemmDesc const& d, cudaStream_t stream);    // 0 ok, 30/33 refused, 41 runtime
+
 }  // namespace qb
