@@ -6,6 +6,7 @@ replay over enough distinct weight copies to exceed the 126 MB L2).  One JSON li
 cfg1  W4A16 dense GEMV, M=1, K=N=4096, gs=128 (generic plane kernel, fp16)
 cfg2  GGUF Q4_K raw-block GEMV, M in {1,4,8}, 4096->14336 and 14336->4096
 cfg3  bit-plane k-quant GEMV (planes + packed units), M=1, K=4096, N in {4096,14336}, Q6_K / Q5_K / Q3_K
+cfg4  prefill MoE grouped W4A16 GEMM (tensor cores), Mixtral-8x7B shapes; fpa = dense fpA_intB M=2048 N=K=4096
 cfg5  decode MoE, 128 experts top-8, hidden 2048 / intermediate 768, W2A16 and W1A16 gs=64, bf16, 1..64 tokens
 """
 from __future__ import annotations
@@ -158,7 +159,10 @@ def cfg4(reps):
                           "frac_of_measured_bf16_peak": round(flops / us / 1e6 / 1652.4, 4)}), flush=True)
         del low, scale, zero, a
         torch.cuda.empty_cache()
-    # dense fpA_intB at the reference's bench default (M=2048, N=K=4096, int4 gs=32)
+
+
+def fpa(reps):
+    """Dense fpA_intB at the reference's bench default: M=2048, N=K=4096, int4 gs=32, fp16."""
     m, n, k = 2048, 4096, 4096
     low, scale, zero = synth.group_planes(1, n, k, 4, 32, seed=5)
     a = torch.randn((m, k), device=DEV, dtype=torch.float16)
@@ -179,7 +183,7 @@ def main():
     _lib.lib()
     torch.cuda.set_device(0)
     for name in args.only.split(","):
-        {"cfg1": cfg1, "cfg2": cfg2, "cfg3": cfg3, "cfg4": cfg4, "cfg5": cfg5}[name](args.reps)
+        {"cfg1": cfg1, "cfg2": cfg2, "cfg3": cfg3, "cfg4": cfg4, "cfg5": cfg5, "fpa": fpa}[name](args.reps)
         torch.cuda.empty_cache()
     assert _lib.lib().quactlize_b200_device_wait_status() == 0
 

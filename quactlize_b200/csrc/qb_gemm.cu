@@ -36,8 +36,8 @@
 
 namespace qb {
 
-constexpr int kTM = 128, kTN = 128, kTK = 64, kGemmStages = 4;
-constexpr int kRawK = 128, kRawStages = 3;          // weight planes and scale rows arrive in 128-k pieces
+constexpr int kTM = 128, kTN = 128, kTK = 64;       // UMMA tile; a CTA stacks MT of them along the rows (MT = 1 or 2)
+constexpr int kRawK = 128;                          // weight planes and scale rows arrive in 128-k pieces
 constexpr int kATileBytes = kTM * kTK * 2;          // 16 KB
 constexpr int kBTileBytes = kTN * kTK * 2;          // 16 KB
 constexpr int kRawLoMax = kTN * kRawK * 4 / 8;      // 8 KB (int4)
@@ -53,18 +53,24 @@ struct GemmArgs {
   unsigned int* status;
 };
 
-struct GemmSmem {
-  alignas(1024) uint8_t a[kGemmStages][kATileBytes];
-  alignas(1024) uint8_t b[kGemmStages][kBTileBytes];
-  alignas(128) uint8_t raw_lo[kRawStages][kRawLoMax];
-  alignas(128) uint8_t raw_hi[kRawStages][kRawHiMax];
-  alignas(128) uint8_t scale[kRawStages][kScaleBytes];
-  alignas(128) uint8_t zero[kRawStages][kScaleBytes];
-  alignas(8) uint64_t a_full[kGemmStages];     // TMA -> MMA (activation tile landed)
-  alignas(8) uint64_t b_full[kGemmStages];     // dequant warps -> MMA (operand tile written)
-  alignas(8) uint64_t empty[kGemmStages];      // MMA (tcgen05.commit) -> TMA and dequant (a[s], b[s] free)
-  alignas(8) uint64_t raw_full[kRawStages];    // TMA -> dequant
-  alignas(8) uint64_t raw_empty[kRawStages];   // dequant -> TMA
+template <int MT> struct GemmCfg {
+  static constexpr int kStages = MT == 1 ? 4 : 3;      // 64-k stages of (activation tile, operand tile)
+  static constexpr int kRawStages = MT == 1 ? 3 : 2;   // 128-k pieces of raw planes + scale rows
+};
+
+template <int MT> struct GemmSmem {
+  static constexpr int ST = GemmCfg<MT>::kStages, RST = GemmCfg<MT>::kRawStages;
+  alignas(1024) uint8_t a[ST][MT * kATileBytes];
+  alignas(1024) uint8_t b[ST][kBTileBytes];
+  alignas(128) uint8_t raw_lo[RST][kRawLoMax];
+  alignas(128) uint8_t raw_hi[RST][kRawHiMax];
+  alignas(128) uint8_t scale[RST][kScaleBytes];
+  alignas(128) uint8_t zero[RST][kScaleBytes];
+  alignas(8) uint64_t a_full[ST];              // TMA -> MMA (activation tile landed)
+  alignas(8) uint64_t b_full[ST];              // dequant warps -> MMA (operand tile written)
+  alignas(8) uint64_t empty[ST];               // MMA (tcgen05.commit) -> TMA and dequant (a[s], b[s] free)
+  alignas(8) uint64_t raw_full[RST];           // TMA -> dequant
+  alignas(8) uint64_t raw_empty[RST];          // dequant -> TMA
   alignas(8) uint64_t acc_full;                // MMA -> epilogue
   uint32_t tmem_base;
   volatile int abort_flag;
@@ -103,7 +109,8 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-__device__ __forceinline__ bool gemm_wait(GemmSmem& sm, uint64_t* bar, unsigned parity, unsigned int* status) {
+template <class SM>
+__device__ __forceinline__ bool gemm_wait(SM& sm, uint64_t* bar, unsigned parity, unsigned int* status) {
   if (mbar_try_wait(bar, parity)) return true;
   unsigned long long const t0 = global_ns();
   unsigned spins = 0;
@@ -150,11 +157,12 @@ template <> struct Pack2<true> {
 // stage's scale rows (row stride kTN halves).  Output: 8 chunks of 16 bytes, chunk c at position c ^ (col & 7).
 template <int LO, int HI, bool BF16>
 __device__ __forceinline__ void dequant_col(uint8_t const* lo, uint8_t const* hi, __half const* sc, __half const* zr,
-                                            int gs, float coff, uint8_t* brow, int col) {
+                                            int gs, float coff, uint8_t* brow, int col, int c_begin, int c_end) {
   using P = Pack2<BF16>;
   int const gshift = gs >= 64 ? 31 : (gs == 32 ? 2 : 1);          // chunks per group: >= 8 -> one group, 4, or 2
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
+    if (c < c_begin || c >= c_end) continue;
     int const g = gs >= 64 ? 0 : (c >> gshift);
     float const s = __half2float(sc[g * kTN]);
     float const z = (zr ? __half2float(zr[g * kTN]) : 0.f) + coff * s;
@@ -188,13 +196,15 @@ __device__ __forceinline__ void dequant_col(uint8_t const* lo, uint8_t const* hi
 
 // ---- the kernel -----------------------------------------------------------------------------------------------------
 
-template <int LO, int HI, bool BF16>
-__global__ void __launch_bounds__(256, 1)
+template <int LO, int HI, bool BF16, int MT>
+__global__ void __launch_bounds__(128 + 128 * MT, 1)
 mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_lo,
                   const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ CUtensorMap map_s,
                   const __grid_constant__ CUtensorMap map_z, GemmArgs g) {
   extern __shared__ uint8_t smem_raw[];
-  GemmSmem& sm = *reinterpret_cast<GemmSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  using SM = GemmSmem<MT>;
+  constexpr int kGemmStages = SM::ST, kRawStages = SM::RST, kRows = kTM * MT;
+  SM& sm = *reinterpret_cast<SM*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   // ---- which tile: blockIdx.x = weight-column tile, blockIdx.y = row tile (grouped: searched in the per-expert counts)
@@ -203,13 +213,13 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     int t = blockIdx.y, acc = 0;
     bool found = false;
     for (int x = 0; x < g.experts; ++x) {
-      int const r0 = g.offsets[x], rows = g.offsets[x + 1] - r0, cnt = (rows + kTM - 1) / kTM;
-      if (t < acc + cnt) { e = x; m0 = r0 + (t - acc) * kTM; mrows = min(kTM, rows - (t - acc) * kTM); found = true; break; }
+      int const r0 = g.offsets[x], rows = g.offsets[x + 1] - r0, cnt = (rows + kRows - 1) / kRows;
+      if (t < acc + cnt) { e = x; m0 = r0 + (t - acc) * kRows; mrows = min(kRows, rows - (t - acc) * kRows); found = true; break; }
       acc += cnt;
     }
     if (!found) return;                                       // uniform for the CTA, before any barrier or allocation
   } else {
-    m0 = blockIdx.y * kTM; mrows = min(kTM, g.m_rows - m0);
+    m0 = blockIdx.y * kRows; mrows = min(kRows, g.m_rows - m0);
     if (mrows <= 0) return;
   }
   int const n0 = blockIdx.x * kTN;
@@ -218,15 +228,15 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   int const srows = gs >= kRawK ? 1 : kRawK / gs;             // scale rows per 128-k piece
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kGemmStages; ++s) { mbar_init(&sm.a_full[s], 1); mbar_init(&sm.b_full[s], 4); mbar_init(&sm.empty[s], 1); }
-    for (int s = 0; s < kRawStages; ++s) { mbar_init(&sm.raw_full[s], 1); mbar_init(&sm.raw_empty[s], 4); }
+    for (int s = 0; s < kGemmStages; ++s) { mbar_init(&sm.a_full[s], 1); mbar_init(&sm.b_full[s], 4 * MT); mbar_init(&sm.empty[s], 1); }
+    for (int s = 0; s < kRawStages; ++s) { mbar_init(&sm.raw_full[s], 1); mbar_init(&sm.raw_empty[s], 4 * MT); }
     mbar_init(&sm.acc_full, 1);
     sm.abort_flag = 0;
     mbar_init_fence();
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 2) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(uint32_t(kTN)) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(uint32_t(kTN * MT)) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -252,7 +262,7 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           if (g.has_zero) tma_load_3d(sm.zero[r], &map_z, n0, kk / gs, e, &sm.raw_full[r]);
         }
         if (i >= kGemmStages && !gemm_wait(sm, &sm.empty[s], unsigned(i / kGemmStages - 1) & 1u, g.status)) break;
-        mbar_expect_tx(&sm.a_full[s], kATileBytes);
+        mbar_expect_tx(&sm.a_full[s], MT * kATileBytes);
         tma_load_2d(sm.a[s], &map_a, i * kTK, m0, &sm.a_full[s]);
       }
     }
@@ -270,14 +280,17 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         uint32_t const a_addr = smem_u32(sm.a[s]), b_addr = smem_u32(sm.b[s]);
 #pragma unroll
         for (int kk = 0; kk < kTK / 16; ++kk)
-          umma_f16(tmem, umma_desc_sw128(a_addr + kk * 32), umma_desc_sw128(b_addr + kk * 32), idesc, (i | kk) ? 1u : 0u);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)                      // MT accumulators share one dequantised operand tile
+            umma_f16(tmem + mt * kTN, umma_desc_sw128(a_addr + mt * kATileBytes + kk * 32), umma_desc_sw128(b_addr + kk * 32),
+                     idesc, (i | kk) ? 1u : 0u);
         umma_commit(&sm.empty[s]);                             // frees a[s] and b[s] once these MMAs have read them
       }
       if (ok) umma_commit(&sm.acc_full);
     }
   } else if (warp >= 4) {
     // ================= dequantise (thread = weight column), then epilogue =================
-    int const col = threadIdx.x - 128;
+    int const col = (threadIdx.x - 128) & 127, part = (threadIdx.x - 128) >> 7;   // MT threads share a column, 8/MT chunks each
     float const coff = float(g.code_offset);
     bool ok = true;
     for (int i = 0; i < nks && ok; ++i) {
@@ -290,7 +303,7 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                                 sm.raw_hi[r] + col * (kRawK * HI / 8) + h * (kTK * HI / 8),
                                 reinterpret_cast<__half const*>(sm.scale[r]) + srow * kTN + col,
                                 g.has_zero ? reinterpret_cast<__half const*>(sm.zero[r]) + srow * kTN + col : nullptr,
-                                gs, coff, sm.b[s] + col * 128, col);
+                                gs, coff, sm.b[s] + col * 128, col, part * (8 / MT), (part + 1) * (8 / MT));
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes -> visible to the MMA
       __syncwarp();
       if (lane == 0) {
@@ -302,12 +315,12 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     if (ok) ok = gemm_wait(sm, &sm.acc_full, 0, g.status);
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      int const q = warp & 3, row = q * 32 + lane;
+      int const q = warp & 3, mt = (warp - 4) >> 2, row = mt * kTM + q * 32 + lane;
       size_t const orow = size_t(m0 + row) * g.n + n0;
 #pragma unroll 1
       for (int c = 0; c < kTN; c += 32) {
         uint32_t v[32];
-        uint32_t const taddr = tmem + (uint32_t(q * 32) << 16) + uint32_t(c);
+        uint32_t const taddr = tmem + (uint32_t(q * 32) << 16) + uint32_t(mt * kTN + c);
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
             "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -343,7 +356,7 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   __syncthreads();
   if (warp == 2) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(uint32_t(kTN)) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(uint32_t(kTN * MT)) : "memory");
   }
 }
 
@@ -379,7 +392,7 @@ bool make_map(CUtensorMap* m, CUtensorMapDataType dt, int rank, void const* base
             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int LO, int HI, bool BF16>
+template <int LO, int HI, bool BF16, int MT>
 int launch_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
   int const E = d.experts > 0 ? d.experts : 1;
   int const gs = d.group_size;
@@ -388,7 +401,7 @@ int launch_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
   {
     cuuint64_t dims[2] = {cuuint64_t(d.k), cuuint64_t(d.total_rows)};
     cuuint64_t str[1] = {cuuint64_t(d.k) * 2};
-    cuuint32_t box[2] = {cuuint32_t(kTK), cuuint32_t(kTM)};
+    cuuint32_t box[2] = {cuuint32_t(kTK), cuuint32_t(kTM * MT)};
     if (!make_map(&ma, BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, d.act, dims, str, box,
                   CU_TENSOR_MAP_SWIZZLE_128B)) return kRuntimeError;
   }
@@ -426,13 +439,13 @@ int launch_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
   g.code_offset = d.code_offset; g.has_zero = d.zero ? 1 : 0;
   g.status = rt_device_status_ptr();
   if (!g.status) return kRuntimeError;
-  auto kern = mixed_gemm_kernel<LO, HI, BF16>;
-  size_t const smem = sizeof(GemmSmem) + 1024;
+  auto kern = mixed_gemm_kernel<LO, HI, BF16, MT>;
+  size_t const smem = sizeof(GemmSmem<MT>) + 1024;
   static bool attr_set = false;
   if (!attr_set) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); attr_set = true; }
-  int const mtiles = (d.total_rows + kTM - 1) / kTM + (d.experts > 0 ? d.experts : 0);
+  int const mtiles = (d.total_rows + kTM * MT - 1) / (kTM * MT) + (d.experts > 0 ? d.experts : 0);
   if (mtiles > 65535) return 30;
-  kern<<<dim3(d.n / kTN, mtiles), 256, smem, stream>>>(ma, ml, mh, ms, mz, g);
+  kern<<<dim3(d.n / kTN, mtiles), 128 + 128 * MT, smem, stream>>>(ma, ml, mh, ms, mz, g);
   return 0;
 }
 
@@ -445,7 +458,11 @@ int enqueue_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
   auto al = [](void const* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   if (!al(d.act) || !al(d.low) || !al(d.scale) || !al(d.out) || (d.zero && !al(d.zero)) || (d.hi_bits && !al(d.high))) return 30;
   int const key = d.lo_bits * 10 + d.hi_bits;
-#define QB_GEMM_CASE(K, L, H) case K: return d.act_bf16 ? launch_mixed_gemm<L, H, true>(d, stream) : launch_mixed_gemm<L, H, false>(d, stream);
+  // two stacked accumulators (256-row tiles) halve the dequantisation work per flop; small problems keep 128-row tiles
+  int const avg_rows = d.experts > 0 ? d.total_rows / d.experts : d.total_rows;
+  bool const big = avg_rows >= 192;
+#define QB_GEMM_CASE(K, L, H) case K: return d.act_bf16 ? (big ? launch_mixed_gemm<L, H, true, 2>(d, stream) : launch_mixed_gemm<L, H, true, 1>(d, stream)) \
+                                                        : (big ? launch_mixed_gemm<L, H, false, 2>(d, stream) : launch_mixed_gemm<L, H, false, 1>(d, stream));
   switch (key) {
     QB_GEMM_CASE(40, 4, 0) QB_GEMM_CASE(41, 4, 1) QB_GEMM_CASE(42, 4, 2) QB_GEMM_CASE(20, 2, 0) QB_GEMM_CASE(21, 2, 1)
     QB_GEMM_CASE(10, 1, 0)

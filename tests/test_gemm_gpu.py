@@ -39,9 +39,9 @@ def test_gemm_plane_dense(bits, gs, m, n, k, dtype):
     _check(out, ref, dtype == torch.bfloat16)
 
 
-def test_gemm_plane_grouped_ragged():
+@pytest.mark.parametrize("rows", [[130, 0, 1, 257, 0, 64], [300, 0, 513, 1, 256, 700]], ids=["tile128", "tile256"])
+def test_gemm_plane_grouped_ragged(rows):
     e, n, k, bits, gs = 6, 256, 512, 4, 128
-    rows = [130, 0, 1, 257, 0, 64]
     low, scale, zero = synth.group_planes(e, n, k, bits, gs, seed=3)
     a = torch.from_numpy(synth.activations(sum(rows), k, seed=9, dtype=np.float32)).to(torch.bfloat16)
     off = np.concatenate([[0], np.cumsum(rows)]).astype(np.int32)
