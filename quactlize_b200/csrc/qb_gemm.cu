@@ -62,8 +62,8 @@ template <int MT> struct GemmSmem {
   static constexpr int ST = GemmCfg<MT>::kStages, RST = GemmCfg<MT>::kRawStages;
   alignas(1024) uint8_t a[ST][MT * kATileBytes];
   alignas(1024) uint8_t b[ST][kBTileBytes];
-  alignas(128) uint8_t raw_lo[RST][kRawLoMax];
-  alignas(128) uint8_t raw_hi[RST][kRawHiMax];
+  alignas(1024) uint8_t raw_lo[RST][kRawLoMax];   // rows of 16*LO bytes, TMA-swizzled when 64 or 32 bytes long
+  alignas(1024) uint8_t raw_hi[RST][kRawHiMax];
   alignas(128) uint8_t scale[RST][kScaleBytes];
   alignas(128) uint8_t zero[RST][kScaleBytes];
   alignas(8) uint64_t a_full[ST];              // TMA -> MMA (activation tile landed)
@@ -153,33 +153,68 @@ template <> struct Pack2<true> {
   }
 };
 
-// lo/hi point at this column's bytes for the 64-k half being converted; sc/zr at [group 0][this column] of the
-// stage's scale rows (row stride kTN halves).  Output: 8 chunks of 16 bytes, chunk c at position c ^ (col & 7).
-template <int LO, int HI, bool BF16>
-__device__ __forceinline__ void dequant_col(uint8_t const* lo, uint8_t const* hi, __half const* sc, __half const* zr,
-                                            int gs, float coff, uint8_t* brow, int col, int c_begin, int c_end) {
-  using P = Pack2<BF16>;
-  int const gshift = gs >= 64 ? 31 : (gs == 32 ? 2 : 1);          // chunks per group: >= 8 -> one group, 4, or 2
+// Raw plane rows of a 128-k piece are 16*BITS bytes; consecutive columns therefore sit 64 / 32 / 16 bytes apart, which
+// would put a warp's loads on a few banks.  The TMA writes 64- and 32-byte rows with the matching swizzle (16-byte chunk
+// index XOR row bits), and this reads through the same XOR with the widest load that covers the thread's bytes.
+template <int NB, int RB>
+__device__ __forceinline__ void load_raw(uint8_t const* tile, uint32_t off, uint32_t* out) {
+  constexpr uint32_t mask = RB == 64 ? 3u : (RB == 32 ? 1u : 0u);
+  if constexpr (NB >= 16) {
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    if (c < c_begin || c >= c_end) continue;
+    for (int i = 0; i < NB / 16; ++i) {
+      uint32_t const o = off + 16 * i;
+      uint4 const v = *reinterpret_cast<uint4 const*>(tile + (o ^ (((o >> 7) & mask) << 4)));
+      out[4 * i] = v.x; out[4 * i + 1] = v.y; out[4 * i + 2] = v.z; out[4 * i + 3] = v.w;
+    }
+  } else if constexpr (NB == 8) {
+    uint2 const v = *reinterpret_cast<uint2 const*>(tile + (off ^ (((off >> 7) & mask) << 4)));
+    out[0] = v.x; out[1] = v.y;
+  } else {
+    static_assert(NB == 4, "a thread converts at least four 8-element chunks of a 1-bit plane");
+    out[0] = *reinterpret_cast<uint32_t const*>(tile + (off ^ (((off >> 7) & mask) << 4)));
+  }
+}
+
+// the BITS*8 plane bits of local chunk i out of the words load_raw() returned
+template <int BITS>
+__device__ __forceinline__ uint32_t chunk_bits(uint32_t const* w, int i) {
+  if constexpr (BITS == 4) return w[i];
+  else if constexpr (BITS == 2) return (w[i >> 1] >> (16 * (i & 1))) & 0xFFFFu;
+  else return (w[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+}
+
+// One thread converts NC consecutive 8-element chunks (from chunk c0 of the 64-k half h) of weight column `col`.
+// lo_tile/hi_tile: the stage's raw 128-k pieces; sc/zr: [group 0][this column] of the scale rows for this half
+// (row stride kTN halves).  Output chunk c lands at 16-byte position c ^ (col & 7) of the operand row (SWIZZLE_128B).
+template <int LO, int HI, bool BF16, int NC>
+__device__ __forceinline__ void dequant_col(uint8_t const* lo_tile, uint8_t const* hi_tile, __half const* sc, __half const* zr,
+                                            int gs, float coff, uint8_t* brow, int col, int h, int c0) {
+  using P = Pack2<BF16>;
+  uint32_t lw[(NC * LO + 3) / 4], hw[HI ? (NC * HI + 3) / 4 : 1];
+  load_raw<NC * LO, 16 * LO>(lo_tile, uint32_t(col * (16 * LO) + h * (8 * LO) + c0 * LO), lw);
+  if constexpr (HI > 0) load_raw<NC * HI, 16 * HI>(hi_tile, uint32_t(col * (16 * HI) + h * (8 * HI) + c0 * HI), hw);
+  int const gshift = gs >= 64 ? 31 : (gs == 32 ? 2 : 1);          // chunks per group: >= 8 -> one group, 4, or 2
+  int gprev = -1;
+  typename P::T2 s2, z2;
+#pragma unroll
+  for (int i = 0; i < NC; ++i) {
+    int const c = c0 + i;
     int const g = gs >= 64 ? 0 : (c >> gshift);
-    float const s = __half2float(sc[g * kTN]);
-    float const z = (zr ? __half2float(zr[g * kTN]) : 0.f) + coff * s;
-    typename P::T2 const s2 = P::from_f(s, s), z2 = P::from_f(z, z);
+    if (g != gprev) {
+      float const s = __half2float(sc[g * kTN]);
+      float const z = (zr ? __half2float(zr[g * kTN]) : 0.f) + coff * s;
+      s2 = P::from_f(s, s); z2 = P::from_f(z, z);
+      gprev = g;
+    }
     uint32_t v[4];
     if constexpr (LO == 4 && HI == 0) {
-      uint32_t const w = *reinterpret_cast<uint32_t const*>(lo + 4 * c), w4 = w >> 4;
+      uint32_t const w = lw[i], w4 = w >> 4;
 #pragma unroll
       for (int j = 0; j < 4; ++j)                               // byte j: (low nibble, high nibble) = elements 2j, 2j+1
         v[j] = (__byte_perm(w, w4, 0x4400u + 0x1111u * j) & 0x000F000Fu) | P::kMagic;
     } else {
-      uint32_t L = 0, H = 0;
-      if constexpr (LO == 4) L = *reinterpret_cast<uint32_t const*>(lo + 4 * c);
-      else if constexpr (LO == 2) L = *reinterpret_cast<uint16_t const*>(lo + 2 * c);
-      else L = lo[c];
-      if constexpr (HI == 2) H = *reinterpret_cast<uint16_t const*>(hi + 2 * c);
-      else if constexpr (HI == 1) H = hi[c];
+      uint32_t const L = chunk_bits<LO>(lw, i);
+      uint32_t const H = HI ? chunk_bits<HI ? HI : 1>(hw, i) : 0u;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         uint32_t const u0 = ((L >> (2 * j * LO)) & ((1u << LO) - 1u)) | (HI ? (((H >> (2 * j * HI)) & ((1u << HI) - 1u)) << LO) : 0u);
@@ -299,11 +334,10 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       if (ok && i >= kGemmStages) ok = gemm_wait(sm, &sm.empty[s], unsigned(i / kGemmStages - 1) & 1u, g.status);
       if (!ok) break;
       int const srow = gs >= kRawK ? 0 : h * (srows / 2);
-      dequant_col<LO, HI, BF16>(sm.raw_lo[r] + col * (kRawK * LO / 8) + h * (kTK * LO / 8),
-                                sm.raw_hi[r] + col * (kRawK * HI / 8) + h * (kTK * HI / 8),
-                                reinterpret_cast<__half const*>(sm.scale[r]) + srow * kTN + col,
-                                g.has_zero ? reinterpret_cast<__half const*>(sm.zero[r]) + srow * kTN + col : nullptr,
-                                gs, coff, sm.b[s] + col * 128, col, part * (8 / MT), (part + 1) * (8 / MT));
+      dequant_col<LO, HI, BF16, 8 / MT>(sm.raw_lo[r], sm.raw_hi[r],
+                                        reinterpret_cast<__half const*>(sm.scale[r]) + srow * kTN + col,
+                                        g.has_zero ? reinterpret_cast<__half const*>(sm.zero[r]) + srow * kTN + col : nullptr,
+                                        gs, coff, sm.b[s] + col * 128, col, h, part * (8 / MT));
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes -> visible to the MMA
       __syncwarp();
       if (lane == 0) {
@@ -392,6 +426,11 @@ bool make_map(CUtensorMap* m, CUtensorMapDataType dt, int rank, void const* base
             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// swizzle of a raw plane tile by its row length (what load_raw() undoes)
+inline CUtensorMapSwizzle plane_swizzle(int row_bytes) {
+  return row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : (row_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
 template <int LO, int HI, bool BF16, int MT>
 int launch_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
   int const E = d.experts > 0 ? d.experts : 1;
@@ -410,14 +449,14 @@ int launch_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
     cuuint64_t dims[3] = {rb, cuuint64_t(d.n), cuuint64_t(E)};
     cuuint64_t str[2] = {rb, rb * d.n};
     cuuint32_t box[3] = {cuuint32_t(kRawK * LO / 8), cuuint32_t(kTN), 1};
-    if (!make_map(&ml, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.low, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
+    if (!make_map(&ml, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.low, dims, str, box, plane_swizzle(16 * LO))) return kRuntimeError;
   }
   if constexpr (HI != 0) {
     cuuint64_t const rb = cuuint64_t(d.k) * HI / 8;
     cuuint64_t dims[3] = {rb, cuuint64_t(d.n), cuuint64_t(E)};
     cuuint64_t str[2] = {rb, rb * d.n};
     cuuint32_t box[3] = {cuuint32_t(kRawK * HI / 8), cuuint32_t(kTN), 1};
-    if (!make_map(&mh, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.high, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
+    if (!make_map(&mh, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.high, dims, str, box, plane_swizzle(16 * HI))) return kRuntimeError;
   } else {
     mh = ml;
   }
