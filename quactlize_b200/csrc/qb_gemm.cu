@@ -12,13 +12,17 @@
 // quactlize/include/quactlize_extensions/cutlass/gemm/collective/quactlize_mma_mixed_input.hpp:985-1250) and grouped
 // (quactlize/include/ppu_aiu_gemm_mixed_input_group.hpp:35-311, launcher quactlize/include/moe_grouped_ppu.cuh:69-361).
 //
-// One CTA computes a 128 (rows) x 128 (weight columns) tile; K advances in stages of 64.  Warp-specialised:
-//   warp 0      TMA producer: activation tile (SWIZZLE_128B, K-major), raw weight planes, scale/zero rows -> smem ring
-//   warp 1      one elected thread issues tcgen05.mma (M=128, N=128, K=16, fp32 accumulate in TMEM) and commits
-//   warp 2      allocates / frees the 128 TMEM columns
-//   warps 4-7   dequantise: thread = weight column; 64 codes -> 64 fp16/bf16 values written in the UMMA canonical
-//               128-byte-swizzled K-major layout; afterwards the same warps read the accumulator (tcgen05.ld) and
-//               store D
+// One CTA computes MT x NT UMMA tiles of 128 rows x 128 weight columns (2 x 2 for prefill-sized problems, 1 x 1 for small
+// ones); K advances in stages of 64.  Warp-specialised:
+//   warp 0        TMA producer: activation tiles (SWIZZLE_128B, K-major) into their own ring; raw weight planes and
+//                 scale/zero rows, in 128-k pieces, into a second ring
+//   warp 1        one elected thread issues tcgen05.mma (M=128, N=128*NT, K=16, fp32 accumulators in TMEM) and commits
+//   warp 2        allocates / frees the 128*MT*NT TMEM columns
+//   warps 4..     4*MT dequant warps: thread = weight column; 64 codes -> 64 fp16/bf16 values written in the UMMA
+//                 canonical 128-byte-swizzled K-major layout (third ring); afterwards the same warps read the
+//                 accumulators (tcgen05.ld) and store D
+// The three rings are sized so that about a microsecond of copies is in flight: a tile's worth of tensor-core work per
+// byte of shared memory is what the 2 x 2 shape buys (half the activation bytes per flop of 2 x 1).
 // Every mbarrier wait is bounded; a wait that gives up raises a CTA-wide abort flag, records a status code, and the
 // CTA drains its copies, frees its TMEM and exits.
 #include <cuda.h>
@@ -36,12 +40,10 @@
 
 namespace qb {
 
-constexpr int kTM = 128, kTN = 128, kTK = 64;       // UMMA tile; a CTA stacks MT of them along the rows (MT = 1 or 2)
+constexpr int kTM = 128, kTN = 128, kTK = 64;       // UMMA tile and K stage
 constexpr int kRawK = 128;                          // weight planes and scale rows arrive in 128-k pieces
 constexpr int kATileBytes = kTM * kTK * 2;          // 16 KB
 constexpr int kBTileBytes = kTN * kTK * 2;          // 16 KB
-constexpr int kRawLoMax = kTN * kRawK * 4 / 8;      // 8 KB (int4)
-constexpr int kRawHiMax = kTN * kRawK * 2 / 8;      // 4 KB (int2 high plane)
 constexpr int kScaleRows = kRawK / 16;              // 8 group rows per piece at gs = 16
 constexpr int kScaleBytes = kScaleRows * kTN * 2;   // 2 KB each for scale and zero
 
@@ -53,22 +55,22 @@ struct GemmArgs {
   unsigned int* status;
 };
 
-template <int MT> struct GemmCfg {
-  static constexpr int kStages = MT == 1 ? 4 : 3;      // 64-k stages of (activation tile, operand tile)
-  static constexpr int kRawStages = MT == 1 ? 3 : 2;   // 128-k pieces of raw planes + scale rows
-};
-
-template <int MT> struct GemmSmem {
-  static constexpr int ST = GemmCfg<MT>::kStages, RST = GemmCfg<MT>::kRawStages;
-  alignas(1024) uint8_t a[ST][MT * kATileBytes];
-  alignas(1024) uint8_t b[ST][kBTileBytes];
-  alignas(1024) uint8_t raw_lo[RST][kRawLoMax];   // rows of 16*LO bytes, TMA-swizzled when 64 or 32 bytes long
-  alignas(1024) uint8_t raw_hi[RST][kRawHiMax];
-  alignas(128) uint8_t scale[RST][kScaleBytes];
-  alignas(128) uint8_t zero[RST][kScaleBytes];
-  alignas(8) uint64_t a_full[ST];              // TMA -> MMA (activation tile landed)
-  alignas(8) uint64_t b_full[ST];              // dequant warps -> MMA (operand tile written)
-  alignas(8) uint64_t empty[ST];               // MMA (tcgen05.commit) -> TMA and dequant (a[s], b[s] free)
+template <int LO, int HI, int MT, int NT> struct GemmSmem {
+  static constexpr bool kBig = MT * NT == 4;
+  static constexpr int AST = kBig ? 3 : 4;            // activation ring: 64-k tiles of 128*MT rows
+  static constexpr int BST = kBig ? 2 : 4;            // dequantised operand ring: 64-k tiles of 128*NT columns
+  static constexpr int RST = kBig ? 2 : 3;            // raw ring: 128-k pieces of planes + scale rows
+  static constexpr int kLoBytes = kTN * kRawK * LO / 8, kHiBytes = HI ? kTN * kRawK * HI / 8 : 1024;
+  alignas(1024) uint8_t a[AST][MT * kATileBytes];
+  alignas(1024) uint8_t b[BST][NT * kBTileBytes];
+  alignas(1024) uint8_t raw_lo[RST][NT][kLoBytes];   // rows of 16*LO bytes, TMA-swizzled when 64 or 32 bytes long
+  alignas(1024) uint8_t raw_hi[RST][NT][kHiBytes];
+  alignas(128) uint8_t scale[RST][NT][kScaleBytes];
+  alignas(128) uint8_t zero[RST][NT][kScaleBytes];
+  alignas(8) uint64_t a_full[AST];             // TMA -> MMA (activation tile landed)
+  alignas(8) uint64_t a_empty[AST];            // MMA (tcgen05.commit) -> TMA
+  alignas(8) uint64_t b_full[BST];             // dequant warps -> MMA (operand tile written)
+  alignas(8) uint64_t b_empty[BST];            // MMA (tcgen05.commit) -> dequant warps
   alignas(8) uint64_t raw_full[RST];           // TMA -> dequant
   alignas(8) uint64_t raw_empty[RST];          // dequant -> TMA
   alignas(8) uint64_t acc_full;                // MMA -> epilogue
@@ -231,14 +233,16 @@ __device__ __forceinline__ void dequant_col(uint8_t const* lo_tile, uint8_t cons
 
 // ---- the kernel -----------------------------------------------------------------------------------------------------
 
-template <int LO, int HI, bool BF16, int MT>
+template <int LO, int HI, bool BF16, int MT, int NT>
 __global__ void __launch_bounds__(128 + 128 * MT, 1)
 mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_lo,
                   const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ CUtensorMap map_s,
                   const __grid_constant__ CUtensorMap map_z, GemmArgs g) {
   extern __shared__ uint8_t smem_raw[];
-  using SM = GemmSmem<MT>;
-  constexpr int kGemmStages = SM::ST, kRawStages = SM::RST, kRows = kTM * MT;
+  using SM = GemmSmem<LO, HI, MT, NT>;
+  constexpr int AST = SM::AST, BST = SM::BST, RST = SM::RST, kRows = kTM * MT, kCols = kTN * NT;
+  constexpr int kDqWarps = 4 * MT;                            // also the epilogue warps: one per 32 accumulator lanes
+  constexpr int NC = 8 * NT / MT;                             // 8-element chunks a dequant thread converts per stage
   SM& sm = *reinterpret_cast<SM*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -257,21 +261,24 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     m0 = blockIdx.y * kRows; mrows = min(kRows, g.m_rows - m0);
     if (mrows <= 0) return;
   }
-  int const n0 = blockIdx.x * kTN;
+  int const n0 = blockIdx.x * kCols;
+  int const nt_here = min(NT, (g.n - n0) / kTN);              // a 256-wide tile may hang over the last 128 columns
+  int const mt_here = min(MT, (mrows + kTM - 1) / kTM);       // ... and a ragged row tile over the last 128 rows
   int const nks = g.k / kTK;                                  // 64-k stages (k is a multiple of 256)
   int const gs = g.group_size;
   int const srows = gs >= kRawK ? 1 : kRawK / gs;             // scale rows per 128-k piece
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kGemmStages; ++s) { mbar_init(&sm.a_full[s], 1); mbar_init(&sm.b_full[s], 4 * MT); mbar_init(&sm.empty[s], 1); }
-    for (int s = 0; s < kRawStages; ++s) { mbar_init(&sm.raw_full[s], 1); mbar_init(&sm.raw_empty[s], 4 * MT); }
+    for (int s = 0; s < AST; ++s) { mbar_init(&sm.a_full[s], 1); mbar_init(&sm.a_empty[s], 1); }
+    for (int s = 0; s < BST; ++s) { mbar_init(&sm.b_full[s], kDqWarps); mbar_init(&sm.b_empty[s], 1); }
+    for (int s = 0; s < RST; ++s) { mbar_init(&sm.raw_full[s], 1); mbar_init(&sm.raw_empty[s], kDqWarps); }
     mbar_init(&sm.acc_full, 1);
     sm.abort_flag = 0;
     mbar_init_fence();
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 2) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(uint32_t(kTN * MT)) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(uint32_t(kTN * MT * NT)) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -282,79 +289,95 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   if (warp == 0) {
     // ================= TMA producer =================
     if (lane == 0) {
-      unsigned const raw_bytes = unsigned(kTN * kRawK * LO / 8) + unsigned(kTN * kRawK * HI / 8) +
-                                 unsigned(srows * kTN * 2) * (g.has_zero ? 2u : 1u);
+      unsigned const raw_bytes = unsigned(NT) * (unsigned(kTN * kRawK * LO / 8) + unsigned(kTN * kRawK * HI / 8) +
+                                                 unsigned(srows * kTN * 2) * (g.has_zero ? 2u : 1u));
       for (int i = 0; i < nks; ++i) {
-        int const s = i % kGemmStages;
+        int const sa = i % AST;
         if ((i & 1) == 0) {
-          int const j = i >> 1, r = j % kRawStages;
-          if (j >= kRawStages && !gemm_wait(sm, &sm.raw_empty[r], unsigned(j / kRawStages - 1) & 1u, g.status)) break;
+          int const j = i >> 1, r = j % RST;
+          if (j >= RST && !gemm_wait(sm, &sm.raw_empty[r], unsigned(j / RST - 1) & 1u, g.status)) break;
           mbar_expect_tx(&sm.raw_full[r], raw_bytes);
           int const kk = j * kRawK;
-          tma_load_3d(sm.raw_lo[r], &map_lo, kk * LO / 8, n0, e, &sm.raw_full[r]);
-          if constexpr (HI != 0) tma_load_3d(sm.raw_hi[r], &map_hi, kk * HI / 8, n0, e, &sm.raw_full[r]);
-          tma_load_3d(sm.scale[r], &map_s, n0, kk / gs, e, &sm.raw_full[r]);
-          if (g.has_zero) tma_load_3d(sm.zero[r], &map_z, n0, kk / gs, e, &sm.raw_full[r]);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {                    // columns past n are out of bounds: zero-filled, still counted
+            tma_load_3d(sm.raw_lo[r][nt], &map_lo, kk * LO / 8, n0 + nt * kTN, e, &sm.raw_full[r]);
+            if constexpr (HI != 0) tma_load_3d(sm.raw_hi[r][nt], &map_hi, kk * HI / 8, n0 + nt * kTN, e, &sm.raw_full[r]);
+            tma_load_3d(sm.scale[r][nt], &map_s, n0 + nt * kTN, kk / gs, e, &sm.raw_full[r]);
+            if (g.has_zero) tma_load_3d(sm.zero[r][nt], &map_z, n0 + nt * kTN, kk / gs, e, &sm.raw_full[r]);
+          }
         }
-        if (i >= kGemmStages && !gemm_wait(sm, &sm.empty[s], unsigned(i / kGemmStages - 1) & 1u, g.status)) break;
-        mbar_expect_tx(&sm.a_full[s], MT * kATileBytes);
-        tma_load_2d(sm.a[s], &map_a, i * kTK, m0, &sm.a_full[s]);
+        if (i >= AST && !gemm_wait(sm, &sm.a_empty[sa], unsigned(i / AST - 1) & 1u, g.status)) break;
+#ifdef QB_GABL_NOA
+        if (i >= AST) { mbar_arrive(&sm.a_full[sa]); continue; }
+#endif
+        mbar_expect_tx(&sm.a_full[sa], MT * kATileBytes);
+        tma_load_2d(sm.a[sa], &map_a, i * kTK, m0, &sm.a_full[sa]);
       }
     }
   } else if (warp == 1) {
     // ================= MMA issuer =================
     if (lane == 0) {
-      uint32_t const idesc = umma_idesc(BF16 ? 1 : 0, kTM, kTN);
+      uint32_t const idesc = umma_idesc(BF16 ? 1 : 0, kTM, kTN * nt_here);
       bool ok = true;
       for (int i = 0; i < nks && ok; ++i) {
-        int const s = i % kGemmStages;
-        unsigned const ph = unsigned(i / kGemmStages) & 1u;
-        ok = gemm_wait(sm, &sm.a_full[s], ph, g.status) && gemm_wait(sm, &sm.b_full[s], ph, g.status);
+        int const sa = i % AST, sb = i % BST;
+        ok = gemm_wait(sm, &sm.a_full[sa], unsigned(i / AST) & 1u, g.status) &&
+             gemm_wait(sm, &sm.b_full[sb], unsigned(i / BST) & 1u, g.status);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        uint32_t const a_addr = smem_u32(sm.a[s]), b_addr = smem_u32(sm.b[s]);
+        uint32_t const a_addr = smem_u32(sm.a[sa]), b_addr = smem_u32(sm.b[sb]);
+#ifndef QB_GABL_NOMMA
 #pragma unroll
         for (int kk = 0; kk < kTK / 16; ++kk)
 #pragma unroll
-          for (int mt = 0; mt < MT; ++mt)                      // MT accumulators share one dequantised operand tile
-            umma_f16(tmem + mt * kTN, umma_desc_sw128(a_addr + mt * kATileBytes + kk * 32), umma_desc_sw128(b_addr + kk * 32),
-                     idesc, (i | kk) ? 1u : 0u);
-        umma_commit(&sm.empty[s]);                             // frees a[s] and b[s] once these MMAs have read them
+          for (int mt = 0; mt < MT; ++mt)                      // every row block multiplies the same dequantised operand tile
+            if (mt < mt_here)
+              umma_f16(tmem + mt * kCols, umma_desc_sw128(a_addr + mt * kATileBytes + kk * 32), umma_desc_sw128(b_addr + kk * 32),
+                       idesc, (i | kk) ? 1u : 0u);
+#endif
+        umma_commit(&sm.a_empty[sa]);                          // frees the rings' slots once these MMAs have read them
+        umma_commit(&sm.b_empty[sb]);
       }
       if (ok) umma_commit(&sm.acc_full);
     }
   } else if (warp >= 4) {
     // ================= dequantise (thread = weight column), then epilogue =================
-    int const col = (threadIdx.x - 128) & 127, part = (threadIdx.x - 128) >> 7;   // MT threads share a column, 8/MT chunks each
+    int const t = threadIdx.x - 128;
+    int const col = t % kCols, part = t / kCols;               // kCols columns x (128*MT / kCols) chunk ranges
+    int const nt = col >> 7, cin = col & 127;
+    bool const live = nt < nt_here;
     float const coff = float(g.code_offset);
     bool ok = true;
     for (int i = 0; i < nks && ok; ++i) {
-      int const s = i % kGemmStages, j = i >> 1, r = j % kRawStages, h = i & 1;
-      if (h == 0) ok = gemm_wait(sm, &sm.raw_full[r], unsigned(j / kRawStages) & 1u, g.status);
-      if (ok && i >= kGemmStages) ok = gemm_wait(sm, &sm.empty[s], unsigned(i / kGemmStages - 1) & 1u, g.status);
+      int const sb = i % BST, j = i >> 1, r = j % RST, h = i & 1;
+      if (h == 0) ok = gemm_wait(sm, &sm.raw_full[r], unsigned(j / RST) & 1u, g.status);
+      if (ok && i >= BST) ok = gemm_wait(sm, &sm.b_empty[sb], unsigned(i / BST - 1) & 1u, g.status);
       if (!ok) break;
       int const srow = gs >= kRawK ? 0 : h * (srows / 2);
-      dequant_col<LO, HI, BF16, 8 / MT>(sm.raw_lo[r], sm.raw_hi[r],
-                                        reinterpret_cast<__half const*>(sm.scale[r]) + srow * kTN + col,
-                                        g.has_zero ? reinterpret_cast<__half const*>(sm.zero[r]) + srow * kTN + col : nullptr,
-                                        gs, coff, sm.b[s] + col * 128, col, h, part * (8 / MT));
+#ifndef QB_GABL_NODEQ
+      if (live)
+        dequant_col<LO, HI, BF16, NC>(sm.raw_lo[r][nt], sm.raw_hi[r][nt],
+                                      reinterpret_cast<__half const*>(sm.scale[r][nt]) + srow * kTN + cin,
+                                      g.has_zero ? reinterpret_cast<__half const*>(sm.zero[r][nt]) + srow * kTN + cin : nullptr,
+                                      gs, coff, sm.b[sb] + col * 128, cin, h, part * NC);
+#endif
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes -> visible to the MMA
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(&sm.b_full[s]);
+        mbar_arrive(&sm.b_full[sb]);
         if (h == 1) mbar_arrive(&sm.raw_empty[r]);
       }
     }
-    // epilogue: this warp owns TMEM lanes 32*(warp%4) .. +31 = output rows of the tile
+    // epilogue: this warp owns TMEM lanes 32*(warp%4) .. +31 of row block mt = 32 output rows of the tile
     if (ok) ok = gemm_wait(sm, &sm.acc_full, 0, g.status);
-    if (ok) {
+    int const q = warp & 3, mt = (warp - 4) >> 2, row = mt * kTM + q * 32 + lane;
+    if (ok && mt < mt_here) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      int const q = warp & 3, mt = (warp - 4) >> 2, row = mt * kTM + q * 32 + lane;
       size_t const orow = size_t(m0 + row) * g.n + n0;
 #pragma unroll 1
-      for (int c = 0; c < kTN; c += 32) {
+      for (int c = 0; c < kTN * nt_here; c += 32) {
         uint32_t v[32];
-        uint32_t const taddr = tmem + (uint32_t(q * 32) << 16) + uint32_t(mt * kTN + c);
+        uint32_t const taddr = tmem + (uint32_t(q * 32) << 16) + uint32_t(mt * kCols + c);
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
             "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -367,14 +390,14 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         if (row < mrows) {
           uint32_t pk[16];
 #pragma unroll
-          for (int t = 0; t < 16; ++t) {
-            float const f0 = __uint_as_float(v[2 * t]), f1 = __uint_as_float(v[2 * t + 1]);
-            if constexpr (BF16) { __nv_bfloat162 const hh = __floats2bfloat162_rn(f0, f1); pk[t] = *reinterpret_cast<uint32_t const*>(&hh); }
-            else { __half2 const hh = __floats2half2_rn(f0, f1); pk[t] = *reinterpret_cast<uint32_t const*>(&hh); }
+          for (int u = 0; u < 16; ++u) {
+            float const f0 = __uint_as_float(v[2 * u]), f1 = __uint_as_float(v[2 * u + 1]);
+            if constexpr (BF16) { __nv_bfloat162 const hh = __floats2bfloat162_rn(f0, f1); pk[u] = *reinterpret_cast<uint32_t const*>(&hh); }
+            else { __half2 const hh = __floats2half2_rn(f0, f1); pk[u] = *reinterpret_cast<uint32_t const*>(&hh); }
           }
           uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(g.out) + orow + c);
 #pragma unroll
-          for (int t = 0; t < 4; ++t) dst[t] = make_uint4(pk[4 * t], pk[4 * t + 1], pk[4 * t + 2], pk[4 * t + 3]);
+          for (int u = 0; u < 4; ++u) dst[u] = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
         }
       }
     }
@@ -384,13 +407,13 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   __syncthreads();
   if (sm.abort_flag && threadIdx.x == 0) {
     // drain copies that may still be in flight so they do not land in shared memory handed to another CTA
-    for (int s = 0; s < kGemmStages; ++s) { (void)mbar_wait_bounded(&sm.a_full[s], 0, nullptr, 0, 100000000ull); (void)mbar_wait_bounded(&sm.a_full[s], 1, nullptr, 0, 100000000ull); }
-    for (int s = 0; s < kRawStages; ++s) { (void)mbar_wait_bounded(&sm.raw_full[s], 0, nullptr, 0, 100000000ull); (void)mbar_wait_bounded(&sm.raw_full[s], 1, nullptr, 0, 100000000ull); }
+    for (int s = 0; s < AST; ++s) { (void)mbar_wait_bounded(&sm.a_full[s], 0, nullptr, 0, 100000000ull); (void)mbar_wait_bounded(&sm.a_full[s], 1, nullptr, 0, 100000000ull); }
+    for (int s = 0; s < RST; ++s) { (void)mbar_wait_bounded(&sm.raw_full[s], 0, nullptr, 0, 100000000ull); (void)mbar_wait_bounded(&sm.raw_full[s], 1, nullptr, 0, 100000000ull); }
   }
   __syncthreads();
   if (warp == 2) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(uint32_t(kTN * MT)) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(uint32_t(kTN * MT * NT)) : "memory");
   }
 }
 
@@ -431,7 +454,7 @@ inline CUtensorMapSwizzle plane_swizzle(int row_bytes) {
   return row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : (row_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
-template <int LO, int HI, bool BF16, int MT>
+template <int LO, int HI, bool BF16, int MT, int NT>
 int launch_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
   int const E = d.experts > 0 ? d.experts : 1;
   int const gs = d.group_size;
@@ -478,13 +501,14 @@ int launch_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
   g.code_offset = d.code_offset; g.has_zero = d.zero ? 1 : 0;
   g.status = rt_device_status_ptr();
   if (!g.status) return kRuntimeError;
-  auto kern = mixed_gemm_kernel<LO, HI, BF16, MT>;
-  size_t const smem = sizeof(GemmSmem<MT>) + 1024;
+  auto kern = mixed_gemm_kernel<LO, HI, BF16, MT, NT>;
+  size_t const smem = sizeof(GemmSmem<LO, HI, MT, NT>) + 1024;
+  static_assert(sizeof(GemmSmem<LO, HI, MT, NT>) + 1024 <= 232448, "shared memory of one CTA");
   static bool attr_set = false;
   if (!attr_set) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); attr_set = true; }
   int const mtiles = (d.total_rows + kTM * MT - 1) / (kTM * MT) + (d.experts > 0 ? d.experts : 0);
   if (mtiles > 65535) return 30;
-  kern<<<dim3(d.n / kTN, mtiles), 128 + 128 * MT, smem, stream>>>(ma, ml, mh, ms, mz, g);
+  kern<<<dim3((d.n + kTN * NT - 1) / (kTN * NT), mtiles), 128 + 128 * MT, smem, stream>>>(ma, ml, mh, ms, mz, g);
   return 0;
 }
 
@@ -497,11 +521,11 @@ int enqueue_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
   auto al = [](void const* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   if (!al(d.act) || !al(d.low) || !al(d.scale) || !al(d.out) || (d.zero && !al(d.zero)) || (d.hi_bits && !al(d.high))) return 30;
   int const key = d.lo_bits * 10 + d.hi_bits;
-  // two stacked accumulators (256-row tiles) halve the dequantisation work per flop; small problems keep 128-row tiles
+  // 256 x 256 CTA tiles (four accumulators = all 512 TMEM columns) for prefill-sized problems; small ones keep 128 x 128
   int const avg_rows = d.experts > 0 ? d.total_rows / d.experts : d.total_rows;
   bool const big = avg_rows >= 192;
-#define QB_GEMM_CASE(K, L, H) case K: return d.act_bf16 ? (big ? launch_mixed_gemm<L, H, true, 2>(d, stream) : launch_mixed_gemm<L, H, true, 1>(d, stream)) \
-                                                        : (big ? launch_mixed_gemm<L, H, false, 2>(d, stream) : launch_mixed_gemm<L, H, false, 1>(d, stream));
+#define QB_GEMM_CASE(K, L, H) case K: return d.act_bf16 ? (big ? launch_mixed_gemm<L, H, true, 2, 2>(d, stream) : launch_mixed_gemm<L, H, true, 1, 1>(d, stream)) \
+                                                        : (big ? launch_mixed_gemm<L, H, false, 2, 2>(d, stream) : launch_mixed_gemm<L, H, false, 1, 1>(d, stream));
   switch (key) {
     QB_GEMM_CASE(40, 4, 0) QB_GEMM_CASE(41, 4, 1) QB_GEMM_CASE(42, 4, 2) QB_GEMM_CASE(20, 2, 0) QB_GEMM_CASE(21, 2, 1)
     QB_GEMM_CASE(10, 1, 0)
