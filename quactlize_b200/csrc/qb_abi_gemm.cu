@@ -20,9 +20,9 @@
 using namespace qb;
 
 namespace {
-constexpr char const* kTensorConfig = "128x128x64:tcgen05:s4";
-quactlize_ppu_config_v1 const kDenseConfigs[] = {{false, kTensorConfig, 128, 128, 32, 128, 4}, {true, "gemv_lowbit", 0, 0, 0, 0, 0}};
-quactlize_ppu_config_v1 const kGroupedConfigs[] = {{false, kTensorConfig, 128, 128, 32, 128, 4}, {true, "vecdot_moe", 0, 0, 0, 0, 0}};
+constexpr char const* kTensorConfig = "256x256x64:tcgen05";
+quactlize_ppu_config_v1 const kDenseConfigs[] = {{false, kTensorConfig, 256, 256, 128, 256, 3}, {true, "gemv_lowbit", 0, 0, 0, 0, 0}};
+quactlize_ppu_config_v1 const kGroupedConfigs[] = {{false, kTensorConfig, 256, 256, 128, 256, 3}, {true, "vecdot_moe", 0, 0, 0, 0, 0}};
 
 bool tensor_name_ok(char const* name) { return !name || !name[0] || std::strcmp(name, kTensorConfig) == 0; }
 void decline(char const* name) {
@@ -147,7 +147,7 @@ extern "C" int32_t quactlize_ppu_grouped_fully_quantized_config_valid_v1(int tot
   return quactlize_ppu_grouped_lowbit_config_valid_v1(total_rows, n, k, group_size, experts, max_rows, qtype, name) && fq_ok(k, qtype);
 }
 static int32_t list_one(quactlize_ppu_config_v2* configs, int32_t capacity, bool valid) {
-  if (valid && configs && capacity > 0) configs[0] = {false, kTensorConfig, 128, 128, 64, 32, 128, 4};
+  if (valid && configs && capacity > 0) configs[0] = {false, kTensorConfig, 256, 256, 64, 128, 256, 3};
   return valid ? 1 : 0;
 }
 extern "C" int32_t quactlize_ppu_list_valid_dense_lowbit_configs_v2(quactlize_ppu_config_v2* c, int32_t cap, int m, int n, int k, int gs, int qtype) {
