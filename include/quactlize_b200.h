@@ -135,7 +135,7 @@ int quactlize_b200_gemv_plane_dev_v1(void const* act, uint8_t const* low, uint8_
 /* ================================ tensor-core mixed-input GEMM (dense fpA_intB, MoE grouped) ===================== */
 
 /* Config inventory.  quactlize/include/quactlize_ppu_config.h:42-71, quactlize/csrc/device/ppu_dense_backend.cu:603-664.
- * One tensor-core tactic is compiled ("128x128x64:tcgen05:s4"); an unknown name logs a decline and runs it. */
+ * One tensor-core tactic is listed ("256x256x64:tcgen05"; small problems run its 128x128 form); an unknown name logs a decline and runs it. */
 int32_t quactlize_ppu_list_configs(quactlize_ppu_config_v1 const** configs);
 int32_t quactlize_ppu_list_grouped_configs(quactlize_ppu_config_v1 const** configs);
 int32_t quactlize_ppu_list_valid_dense_lowbit_configs_v2(quactlize_ppu_config_v2* configs, int32_t capacity, int m, int n,
@@ -214,6 +214,18 @@ int quactlize_ppu_grouped_fully_quantized_dev_v2(uint16_t const* act, uint8_t co
 int quactlize_b200_gemm_plane_dev_v1(void const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale,
                                      uint16_t const* zero, void* out, int total_rows, int n, int k, int bits_lo, int bits_hi,
                                      int group_size, int code_offset, int act_dtype, int experts, int const* offsets, void* stream);
+
+/* No counterpart in the reference.  The fully-quantized dense GEMM of quactlize_ppu_dense_fully_quantized_dev_v1 for
+ * callers that cannot allocate device memory and have no workspace to hand over: the fp16 scale/zero planes derived
+ * from the packed units go to a fixed array inside the library's device image, QUACTLIZE_B200_STATIC_SCRATCH_BYTES
+ * per device.  Enqueues on `stream` and returns; allocates nothing.  37 = the planes (4 * k/group_size * n bytes) exceed
+ * the array; 30 / 33 / 41 as for the regular entry.  The first call on a device looks the array's address up: make it
+ * outside stream capture.  All calls on a device share the array (each rewrites what it reads, nothing needs
+ * clearing); calls that may overlap in time on one device race on it. */
+#define QUACTLIZE_B200_STATIC_SCRATCH_BYTES (16 * 1024 * 1024)
+int quactlize_b200_dense_fully_quantized_static_v1(uint16_t const* act, uint8_t const* low, uint8_t const* high,
+                                                   uint8_t const* units, uint16_t* out, int m, int n, int k, int qtype,
+                                                   void* stream);
 
 /* ================================ host-only artifact producers ================================================== */
 

@@ -70,6 +70,7 @@ SIGNATURES = {
     "quactlize_ppu_grouped_fully_quantized_dev_v1": (I, [P, P, P, P, P, P, I, I, I, I, I, I, P, I64, P]),
     "quactlize_ppu_grouped_fully_quantized_dev_v2": (I, [P, P, P, P, P, P, I, I, I, I, I, I, P, I64, P, C.c_char_p]),
     "quactlize_b200_gemm_plane_dev_v1": (I, [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P]),
+    "quactlize_b200_dense_fully_quantized_static_v1": (I, [P, P, P, P, P, I, I, I, I, P]),
     "quactlize_ppu_units_bytes": (I64, [I, I, I]),
     "quactlize_ppu_prepare_units": (I, [P, P, I, I, I]),
     "quactlize_ppu_prepare_units_grouped": (I, [P, P, I, I, I, I]),
