@@ -4,8 +4,8 @@ TEST INFRASTRUCTURE ONLY.  Nothing in the product path imports this file or anyt
 tests, the smoke check and the CPU-baseline leg of the benchmark load the resulting library, and only as the
 checker / the timed CPU reference.
 
-The sources are compiled where they lie in the read-only reference checkout (default ``/root/reference``,
-override with ``QUACTLIZE_REFERENCE_ROOT``); nothing is copied.  The reference extension is host C++ that needs
+The sources are compiled where they lie in the read-only reference checkout (``QUACTLIZE_REFERENCE_ROOT``, else the
+default location coded in ``ref_root()``); nothing is copied.  The reference extension is host C++ that needs
 CUTLASS/CuTe *headers* only; the stock CUTLASS tree vendored with flashinfer serves.  Sources compiled
 (paths inside the reference project):
 

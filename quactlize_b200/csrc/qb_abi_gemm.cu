@@ -31,6 +31,7 @@ void decline(char const* name) {
 }
 bool shape_ok(int n, int k) { return n > 0 && n % 256 == 0 && k > 0 && k % 256 == 0; }
 int converter_offset(int qtype) { return (qtype == 12 || qtype == 13 || qtype == 14) ? -8 : 0; }
+int placed_zmul(int qtype) { return qtype == 11 ? -4 : (qtype == 12 || qtype == 13) ? 8 : qtype == 14 ? -24 : 0; }
 int centred_offset(int qtype) {                     // scale-only grouped: centre of the concatenated code
   int const w = kq::lo_bits(qtype) + kq::hi_bits(qtype);
   return kq::hi_bits(qtype) ? -(1 << (w - 1)) : (kq::lo_bits(qtype) == 4 ? -8 : 0);
@@ -90,8 +91,10 @@ int dev_units_gemm(uint16_t const* act, uint8_t const* low, uint8_t const* high,
   __half* sc = reinterpret_cast<__half*>(workspace);
   __half* zr = sc + pe;
   rt_clear_error();
-  if (!enqueue_prepass_unit(units, sc, zr, we, n, k / 256, qtype, -(qtype == 11 ? 4 : qtype == 14 ? 32 : 0), s)) return 33;
-  GemmDesc d = kq_desc(act, low, high, sc, zr, out, rows, n, k, qtype, experts, offsets, 0);
+  // the reference's placed-code convention (quactlize/formats.py:315-321): int4-low codes are converted as (low - 8) and
+  // the zero plane carries the matching correction, which keeps |zero| small and its fp16 rounding with it
+  if (!enqueue_prepass_unit(units, sc, zr, we, n, k / 256, qtype, placed_zmul(qtype), s)) return 33;
+  GemmDesc d = kq_desc(act, low, high, sc, zr, out, rows, n, k, qtype, experts, offsets, converter_offset(qtype));
   int const rc = enqueue_mixed_gemm(d, s);
   if (rc) return rc;
   return rt_check_launch(what) ? 0 : kRuntimeError;

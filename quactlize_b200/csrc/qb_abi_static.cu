@@ -87,15 +87,16 @@ extern "C" int quactlize_b200_dense_fully_quantized_static_v1(uint16_t const* ac
   cudaStream_t const s = static_cast<cudaStream_t>(stream);
   __half* const sc = reinterpret_cast<__half*>(scratch);
   __half* const zr = sc + plane_elems;
-  // pre-pass: packed units -> fp16 planes, every element of both planes written (the plane codes are offset-binary,
-  // so the zero plane folds minus the format's code bias)
-  int const zmul = -(qtype == 11 ? 4 : qtype == 14 ? 32 : 0);
+  // pre-pass: packed units -> fp16 planes, every element of both planes written.  Same code convention as the regular
+  // entry: int4-low codes convert as (low - 8), the zero plane carries the matching correction.
+  int const zmul = qtype == 11 ? -4 : (qtype == 12 || qtype == 13) ? 8 : qtype == 14 ? -24 : 0;
+  int const code_offset = (qtype == 12 || qtype == 13 || qtype == 14) ? -8 : 0;
   if (!enqueue_prepass_unit(units, sc, zr, 1, n, k / 256, qtype, zmul, s)) return 33;
   GemmDesc d{};
   d.act = act; d.low = low; d.high = kq::hi_bits(qtype) ? high : nullptr; d.scale = sc; d.zero = zr; d.out = out;
   d.offsets = nullptr; d.total_rows = m; d.n = n; d.k = k; d.experts = 0;
   d.group_size = kq::group_size(qtype); d.lo_bits = kq::lo_bits(qtype); d.hi_bits = kq::hi_bits(qtype);
-  d.code_offset = 0; d.act_bf16 = 0;
+  d.code_offset = code_offset; d.act_bf16 = 0;
   int const rc = enqueue_mixed_gemm(d, s);
   if (rc) return rc;
   return rt_check_launch("fully-quantized dense GEMM (static scratch) enqueue") ? 0 : kRuntimeError;

@@ -1,5 +1,7 @@
 """Pins the numpy oracle: bit-for-bit against golden vectors produced by the reference's own host ops
 (tests/golden/make_golden.py) and against the official gguf package's dequantiser."""
+import os
+
 import numpy as np
 import pytest
 
@@ -90,3 +92,40 @@ def test_planes_matmul_matches_dequant(qtype):
     ref = a.astype(np.float64) @ w.T
     got = kq.planes_matmul(a, low, high, scale, zero, f.lo_bits, f.hi_bits, f.group_size)
     assert kq.max_rel(got, ref) < 2e-3
+
+
+# ---- the reference's real-weight golden vectors for the tensor-core arithmetic (repacked by make_real_fixtures.py) ----
+
+def _real(name):
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", name))
+
+
+def test_real_q2k_w2a16_gold():
+    """tests/test_w2a16_real.cu:1-9: a Q2_K slice at its native gs=16, D = A @ (q*scale + zero)."""
+    f = _real("real_q2k_w2a16.npz")
+    ref = kq.planes_matmul(f["a"].astype(np.float32), f["low"], None, f["scale"], f["zero"], 2, 0, int(f["gs"]))
+    assert kq.max_rel(ref, f["gold"].astype(np.float64)) < 2e-3
+
+
+def test_real_q3k_two_plane_gold():
+    """tests/test_q3_concat_real.cu:1-12: W = dl*(low2 + 4*high1 - 4); the fixture's split scales obey
+    scale_hi = 4*scale_lo and zero_lo = -4*scale_lo exactly (powers of two), so one two-plane product reproduces it."""
+    f = _real("real_q3k_two_plane.npz")
+    assert np.array_equal(f["scale_hi"].astype(np.float32), 4 * f["scale_lo"].astype(np.float32))
+    assert np.array_equal(f["zero_lo"].astype(np.float32), -4 * f["scale_lo"].astype(np.float32))
+    ref = kq.planes_matmul(f["a"].astype(np.float32), f["low"], f["high"], f["scale_lo"], None, 2, 1, int(f["gs"]), code_offset=-4)
+    assert kq.max_rel(ref, f["gold"].astype(np.float64)) < 2e-3
+
+
+def test_real_q4k_blocks_gold():
+    """tests/rwmoep_loader.hpp:12-22: real Q4_K columns in native form (codes, 6-bit sc/mn, fp16 d/dmin), repacked into
+    raw 144-byte blocks; gold = A @ dequant(W)."""
+    f = _real("real_q4k_blocks.npz")
+    a, blocks, gold = f["a"], f["blocks"], f["gold"].astype(np.float64)
+    n, k = gold.shape[1], a.shape[1]
+    ref = a.astype(np.float64) @ kq.dequantize_f32(blocks, 12).reshape(n, k).T.astype(np.float64)
+    assert kq.max_rel(ref, gold) < 2e-3
+    # the official gguf dequantiser reads the repacked blocks the same way
+    import gguf
+    off = gguf.quants.dequantize(blocks, gguf.GGMLQuantizationType.Q4_K).reshape(n, k)
+    assert np.array_equal(off.astype(np.float32), kq.dequantize_f32(blocks, 12).reshape(n, k))
