@@ -459,10 +459,11 @@ def gemv_plane(a, low, high, scale, zero, bits_lo: int, bits_hi: int, group_size
     ok = {torch.float16: 0, torch.float32: 1, torch.bfloat16: 2}[out_dtype]
     rows = a.shape[0]
     out = torch.empty((rows, n), dtype=out_dtype, device=a.device)
-    experts, max_rows, off = 0, rows, None
+    experts, bound, off = 0, rows, None
     if row_offsets is not None:
         experts = e
-        max_rows = int(max_rows) if max_rows is not None else _offsets_info(row_offsets, experts, rows)
+        bound = int(max_rows) if max_rows is not None else _offsets_info(row_offsets, experts, rows)
+        _check(0 < bound <= max(rows, 1), "max_rows must bound the rows of any one expert")
         off = row_offsets.to(a.device).contiguous()
     else:
         _check(e == 1, "dense artifact must have one expert dimension")
@@ -473,7 +474,7 @@ def gemv_plane(a, low, high, scale, zero, bits_lo: int, bits_hi: int, group_size
         _rc(_lib.lib().quactlize_b200_gemv_plane_dev_v1(
             _p(a), _p(low), _p(high) if bits_hi else None, _p(scale.contiguous()), _p(zero.contiguous()) if zero is not None else None,
             _p(out), rows, n, k, bits_lo, bits_hi, group_size, int(code_offset), 1 if a.dtype == torch.bfloat16 else 0, ok,
-            experts, _p(off), max_rows, _stream(a)), "plane GEMV")
+            experts, _p(off), bound, _stream(a)), "plane GEMV")
     return out
 
 

@@ -37,6 +37,7 @@
 #include "qb_device.cuh"
 #include "qb_internal.hpp"
 #include "qb_runtime.hpp"
+#include "qb_tma.hpp"
 
 namespace qb {
 
@@ -513,6 +514,11 @@ int launch_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
 }
 
 }  // namespace
+
+bool tma_make_map(CUtensorMap* m, CUtensorMapDataType dt, int rank, void const* base, cuuint64_t const* dims,
+                  cuuint64_t const* strides_bytes, cuuint32_t const* box, CUtensorMapSwizzle sw) {
+  return make_map(m, dt, rank, base, dims, strides_bytes, box, sw);
+}
 
 int enqueue_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
   if (!d.act || !d.low || !d.scale || !d.out || d.total_rows <= 0 || d.n <= 0 || d.n % kTN || d.k <= 0 || d.k % 256 ||

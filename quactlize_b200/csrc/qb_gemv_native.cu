@@ -402,6 +402,9 @@ int enqueue_native_gemv(uint8_t const* blocks, __half const* x, float* out, int 
     else if (mt == 2) ok = launch_q4k_fast<2, 4, 8>(a, gy, stream);
     else ok = launch_q4k_fast<4, 8, 8>(a, gy, stream);   // more rows: several 4-row tiles share the weight reads in L2
     if (ok) return 0;
+    // long rows leave no room for a multi-row tile's activations: stream the weights once per row instead (the first
+    // pass pulls them into L2 for the others) rather than fall back to plain loads
+    if (rows_hint <= 16 && enqueue_q4k_gemv1(blocks, x, out, offsets, n, bpr, a.experts, m_rows, max_rows, a.status, stream)) return 0;
   }
   if (per_row_x) {
     a.mtiles = 1;

@@ -19,6 +19,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstdint>
 #include <map>
 #include <mutex>
@@ -404,6 +405,12 @@ int launch_plane_cpl(PlaneGemvDesc const& d, cudaStream_t s) {
 
 int enqueue_plane_gemv(PlaneGemvDesc const& d, cudaStream_t s) {
   if (d.k <= 0 || d.k % 256 || d.n <= 0) return 40;
+  // the row-thread kernel covers the common shapes; QUACTLIZE_B200_PLANE_GEMV=segment keeps the kernel below for comparison
+  static bool const segment_only = [] { char const* v = std::getenv("QUACTLIZE_B200_PLANE_GEMV"); return v && v[0] == 's'; }();
+  if (!segment_only) {
+    int const rc = enqueue_rowthread_gemv(d, s);
+    if (rc != 40) return rc;
+  }
   auto aligned = [](void const* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   if (!aligned(d.low) || (d.hi_bits && !aligned(d.high)) || !aligned(d.act)) return 40;
   if (d.scale_mode == 1) {

@@ -1,0 +1,542 @@
+// Decode GEMV over the bit-plane artifacts, "row-thread" form: every lane owns (one weight row, one quarter of a
+// 256-code K slice), so the scale channel -- fp16 planes [E][k/gs][n] or packed units [E][k/256/P][n][bytes], both with
+// n innermost -- is read with consecutive lanes on consecutive columns, and nothing is reduced across lanes until the
+// very end.  Same math as the segment-per-warp kernel in qb_gemv_planes.cu:
+//
+//   out[t, r] = sum_k a[t, k] * ( (u[r,k] + off) * s[r, k/gs] + z[r, k/gs] ),   u = lo + 2^LO * hi
+//
+// Replaces the reference kernels gemv_kernel (quactlize/include/gemv_lowbit/gemv_kernel.hpp:44-246) and
+// bc_vecdot::rows_kernel (quactlize/include/gguf_bc_vecdot.hpp:152-227); the reference names the scale loads, not
+// the weight stream, as what limits its kernel (gemv_kernel.hpp:147-161) -- this layout is the answer to that.
+//
+// Work decomposition.  A tile is 8 rows x 256 codes of a plane: a tiled TMA copy with the swizzle matching its row
+// length (128 / 64 / 32 bytes), so the 8 x 4 lanes of a warp read it without bank conflicts.  A CTA of 16 warps owns a
+// set of 8-row blocks; the tiles of those blocks, listed block by block, are cut into 16 equal contiguous runs, one
+// per warp, each streamed through the warp's own ring of mbarrier-tracked stages.  A run may begin and end inside a
+// block, so a warp leaves one partial sum per block it touched in shared memory; after the only CTA barrier the
+// contributions of each block are added in warp order, so results do not depend on timing.
+//
+// Activations: the CTA turns its activation row once into "pattern order" in shared memory -- for each plane word the
+// half2 operands that the mask-only code extraction needs ((w & mask) read as fp16 IS code * 2^shift * 2^-24; the
+// power-of-two activation pre-scale and the shift are folded into the operand) -- plus the sums of x over every
+// 16/32/64-code run for the zero / code-offset terms.  Lanes fetch these with 128-bit broadcast loads.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <map>
+#include <mutex>
+
+#include "qb_device.cuh"
+#include "qb_internal.hpp"
+#include "qb_kquant.cuh"
+#include "qb_runtime.hpp"
+#include "qb_tma.hpp"
+
+namespace qb {
+
+namespace {
+
+constexpr int kRows = 8;             // rows of a tile
+constexpr int kSlice = 256;          // codes of a tile along K
+constexpr int kPart = 64;            // codes one lane converts per tile (4 lanes per row)
+constexpr int kPartStride = 144;     // bytes between the pattern runs of consecutive parts: 128 + 16 keeps the four
+                                     // parts a warp reads at once on different banks
+
+struct RtArgs {
+  PlaneGemvDesc d;
+  int ns, nblocks;                   // K slices per block, row blocks
+  unsigned int* status;
+};
+
+__device__ __forceinline__ void tma_tile_3d(void* dst, CUtensorMap const* map, int c0, int c1, int c2, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+__device__ __forceinline__ float act_at(void const* base, size_t i, int bf16) {
+  uint16_t const h = __ldg(reinterpret_cast<uint16_t const*>(base) + i);
+  return bf16 ? __uint_as_float(uint32_t(h) << 16) : __half2float(__ushort_as_half(h));
+}
+
+// one 32-bit plane word of B-bit codes against its NP = 16/B pattern operands
+template <int B>
+__device__ __forceinline__ __half2 rt_acc_word(uint32_t w, __half2 const* xs, __half2 acc) {
+  constexpr int PER = 8 / B;
+  constexpr uint32_t M1 = ((1u << B) - 1u) * 0x00010001u;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    uint32_t const ws = h ? (w >> 8) : w;
+#pragma unroll
+    for (int o = 0; o < PER; ++o) acc = __hfma2(u32_as_h2(ws & (M1 << (o * B))), xs[h * PER + o], acc);
+  }
+  return acc;
+}
+
+// this lane's 64 codes of plane row `r`, part `kp`, out of a swizzled tile whose rows are 32*B bytes
+template <int B>
+__device__ __forceinline__ void load_part(uint8_t const* tile, int r, int kp, uint32_t* w) {
+  if constexpr (B == 4) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      uint4 const v = lds128(tile + r * 128 + (((2 * kp + j) ^ r) << 4));
+      w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+    }
+  } else if constexpr (B == 2) {
+    uint4 const v = lds128(tile + r * 64 + ((kp ^ ((r >> 1) & 3)) << 4));
+    w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+  } else {
+    uint8_t const* p = tile + r * 32 + ((((kp >> 1) ^ ((r >> 2) & 1))) << 4) + (kp & 1) * 8;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[0]), "=r"(w[1]) : "r"(smem_u32(p)));
+  }
+}
+
+// 32 bits starting at bit `bit` of a little-endian bit string held in words u[0..N-1]
+template <int N>
+__device__ __forceinline__ uint32_t bits_at(uint32_t const* u, int bit) {
+  int const wi = bit >> 5;
+  uint32_t lo = u[0], hi = N > 1 ? u[1] : 0u;
+#pragma unroll
+  for (int i = 1; i < N; ++i) {
+    if (wi == i) { lo = u[i]; hi = i + 1 < N ? u[i + 1] : 0u; }
+  }
+  return __funnelshift_r(lo, hi, bit & 31);
+}
+
+// LO/HI plane bits; MODE 0 fp16 scale(+zero) planes with NQ = 64/min(gs,64) runs per part, MODE 1 packed units of QT
+template <int LO, int HI, int MODE, int QT, int NQ, int STAGES>
+__global__ void __launch_bounds__(512, 1)
+rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_constant__ CUtensorMap map_hi, RtArgs a) {
+  constexpr int Q = kPart / NQ;                       // codes per run: one scale group (or 64 codes of a wider one)
+  constexpr int NWL = kPart * LO / 32;                // low-plane words per part: 8 / 4 / 2
+  constexpr int NWH = HI ? kPart * HI / 32 : 1;       // high-plane words per part: 4 / 2
+  constexpr int CWL = 32 / LO, CWH = HI ? 32 / HI : 32;
+  constexpr int NPL = 16 / LO, NPH = HI ? 16 / HI : 1;
+  constexpr int U = Q < 32 ? Q : 32;                  // codes per fp16 accumulation run (then fp32)
+  constexpr int NU = kPart / U;
+  constexpr int LO_TILE = kRows * 32 * LO, HI_TILE = HI ? kRows * 32 * HI : 0;
+  static_assert(CWL <= U, "a low-plane word must not straddle accumulation runs");
+  constexpr bool kCrossHi = HI && CWH > U;            // a high word spans two runs (1-bit plane, 16-code groups)
+  static_assert(!kCrossHi || CWH == 2 * U, "a high-plane word may span at most two runs");
+
+  PlaneGemvDesc const& d = a.d;
+  extern __shared__ uint8_t smem_dyn[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int const kp = lane >> 3, r = lane & 7;
+
+  // ---- which activation row / expert ---------------------------------------------------------------------------------
+  // grid.y is the activation row; a ragged launch looks its expert up in the cumulative offsets (one probe per thread)
+  int e = 0;
+  int const arow = blockIdx.y;
+  if (d.offsets) {
+    volatile int* s_expert = reinterpret_cast<volatile int*>(smem);      // a ring slot, not yet in use
+    if (threadIdx.x == 0) *s_expert = -1;
+    __syncthreads();
+    for (int t = threadIdx.x; t < d.experts; t += blockDim.x)
+      if (arow >= d.offsets[t] && arow < d.offsets[t + 1]) *s_expert = t;
+    __syncthreads();
+    e = *s_expert;
+    __syncthreads();                                  // everyone has read it before the first copy may land there
+    if (e < 0) return;                                // uniform for the CTA: a row beyond the last offset
+  }
+  int const k = d.k, n = d.n;
+
+  // ---- shared memory carve-up -----------------------------------------------------------------------------------------
+  constexpr int W = 16;
+  int const nparts = k / kPart;
+  uint8_t* lo_ring = smem;                                              // [W][STAGES][LO_TILE]
+  uint8_t* hi_ring = lo_ring + size_t(W) * STAGES * LO_TILE;             // [W][STAGES][HI_TILE]
+  uint8_t* xlo = hi_ring + size_t(W) * STAGES * HI_TILE;                 // [nparts][kPartStride]
+  uint8_t* xhi = xlo + size_t(nparts) * kPartStride;                     // same, if HI
+  float* sxq = reinterpret_cast<float*>(xhi + (HI ? size_t(nparts) * kPartStride : 0));   // [k/Q]
+  uint16_t* xraw = reinterpret_cast<uint16_t*>(sxq + k / Q);             // [k] raw activations (prologue only)
+  float* red = reinterpret_cast<float*>(xraw + k);                       // [16]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(red + 16);                // [W][STAGES]
+  float* part = reinterpret_cast<float*>(bars + W * STAGES);             // [blocks of this CTA + 16][kRows]
+  (void)xhi;
+
+  // ---- this warp's share of the work ------------------------------------------------------------------------------------
+  // The CTA owns blocks blockIdx.x, blockIdx.x + gridDim.x, ...; their tiles, listed block by block, are cut into 16
+  // equal runs, one per warp, so a warp's run may start and end inside a block.
+  int const ns = a.ns;
+  int const nb_c = blockIdx.x < a.nblocks ? (a.nblocks - 1 - blockIdx.x) / gridDim.x + 1 : 0;   // blocks of this CTA
+  int const T = nb_c * ns;
+  int const t0 = int((long long)warp * T / 16), t1 = int((long long)(warp + 1) * T / 16);
+  int const ntiles = t1 - t0;
+  uint64_t* mybars = bars + warp * STAGES;
+  uint8_t* mylo = lo_ring + size_t(warp) * STAGES * LO_TILE;
+  uint8_t* myhi = hi_ring + size_t(warp) * STAGES * HI_TILE;
+
+  auto issue = [&](int q) {                                // q counts this warp's tiles
+    int const st = q % STAGES, tile = t0 + q, bi = tile / ns, sl = tile % ns;
+    int const row0 = (blockIdx.x + bi * gridDim.x) * kRows;
+    mbar_expect_tx(&mybars[st], LO_TILE + HI_TILE);
+    tma_tile_3d(mylo + st * LO_TILE, &map_lo, sl * (kSlice * LO / 8), row0, e, &mybars[st]);
+    if constexpr (HI != 0) tma_tile_3d(myhi + st * HI_TILE, &map_hi, sl * (kSlice * HI / 8), row0, e, &mybars[st]);
+  };
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) mbar_init(&mybars[s], 1);
+    mbar_init_fence();
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    for (int q = 0; q < STAGES && q < ntiles; ++q) issue(q);          // the weight stream starts before the activations are ready
+  }
+  for (int i = threadIdx.x; i < (nb_c + 16) * kRows; i += blockDim.x) part[i] = 0.f;
+
+  // ---- CTA prologue: activations into pattern order --------------------------------------------------------------------
+  // pass 1: raw 16-bit activations to shared memory, max |x|, and the sum of x over every Q-code run (lanes hold
+  // consecutive 8-element pieces, so a run is Q/8 neighbouring lanes)
+  size_t const xoff = size_t(arow) * k;
+  float mx = 0.f;
+  for (int i = threadIdx.x * 8; i < k; i += blockDim.x * 8) {            // k % 256 == 0: whole warps in or out
+    uint4 const v = __ldg(reinterpret_cast<uint4 const*>(reinterpret_cast<uint16_t const*>(d.act) + xoff + i));
+    *reinterpret_cast<uint4*>(xraw + i) = v;
+    uint32_t const w4[4] = {v.x, v.y, v.z, v.w};
+    float p = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      uint32_t const h = (w4[j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
+      float const f = d.act_bf16 ? __uint_as_float(h << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(h)));
+      mx = fmaxf(mx, fabsf(f));
+      p += f;
+    }
+#pragma unroll
+    for (int o = 1; o < Q / 8; o <<= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
+    if ((lane & (Q / 8 - 1)) == 0) sxq[i / Q] = p;
+  }
+  mx = warp_max(mx);
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  mx = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) if (i < int(blockDim.x >> 5)) mx = fmaxf(mx, red[i]);
+  int const ex = pow2_scale_exponent(mx, HI ? 15 - LO : 15);
+  float const fm = ldexpf(1.f, 24 - ex);
+  auto xval = [&](int c) -> float {
+    uint32_t const h = xraw[c];
+    return d.act_bf16 ? __uint_as_float(h << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(h)));
+  };
+  // pass 2: one half2 operand per code pair, multiplier 2^(ex - shift) built from its exponent bits
+  for (int t = threadIdx.x; t < k / 2; t += blockDim.x) {
+    constexpr int PER = 8 / LO;
+    int const word = t / NPL, p = t % NPL, h = p / PER, o = p % PER;
+    int const c0 = word * CWL + h * PER + o;
+    float const m = __int_as_float((127 + ex - o * LO) << 23);
+    __half2 const v = __floats2half2_rn(xval(c0) * m, xval(c0 + 16 / LO) * m);
+    int const pt = (word * CWL) / kPart;
+    *reinterpret_cast<__half2*>(xlo + size_t(pt) * kPartStride + size_t(t - pt * (kPart / 2)) * 4) = v;
+  }
+  if constexpr (HI != 0) {
+    for (int t = threadIdx.x; t < k / 2; t += blockDim.x) {
+      constexpr int HB = HI ? HI : 1, PER = 8 / HB;
+      int const word = t / NPH, p = t % NPH, h = p / PER, o = p % PER;
+      int const c0 = word * CWH + h * PER + o;
+      float const m = __int_as_float((127 + ex + LO - o * HB) << 23);
+      __half2 const v = __floats2half2_rn(xval(c0) * m, xval(c0 + 16 / HB) * m);
+      int const pt = (word * CWH) / kPart;
+      *reinterpret_cast<__half2*>(xhi + size_t(pt) * kPartStride + size_t(t - pt * (kPart / 2)) * 4) = v;
+    }
+  }
+  __syncthreads();
+
+  // ---- scale channel of one tile, fetched one tile ahead -----------------------------------------------------------------
+  constexpr int NSC = MODE == 0 ? NQ : 5;
+  uint32_t cur[NSC], nxt[NSC];
+  int const gs = d.group_size, kg = MODE == 0 ? k / gs : 0;
+  auto fetch = [&](int q, uint32_t* dst) {
+    int const tile = t0 + q, bi = tile / ns, s = tile % ns;
+    int const row = (blockIdx.x + bi * gridDim.x) * kRows + r;
+#pragma unroll
+    for (int i = 0; i < NSC; ++i) dst[i] = 0u;
+    if (row >= n) return;
+    if constexpr (MODE == 0) {
+      uint16_t const* sp = reinterpret_cast<uint16_t const*>(d.scale);
+      uint16_t const* zp = reinterpret_cast<uint16_t const*>(d.zero);
+      int const k0 = s * kSlice + kp * kPart;
+#pragma unroll
+      for (int j = 0; j < NQ; ++j) {
+        size_t const gi = (size_t(e) * kg + size_t(k0 + j * Q) / gs) * n + row;
+        uint32_t const sv = __ldg(sp + gi), zv = zp ? uint32_t(__ldg(zp + gi)) : 0u;
+        dst[j] = sv | (zv << 16);
+      }
+    } else {
+      using UU = kq::Unit<QT>;
+      int const nu = (k / 256) / UU::kSbPerUnit;
+      uint16_t const* u16 = reinterpret_cast<uint16_t const*>(
+          d.units + ((size_t(e) * nu + s / UU::kSbPerUnit) * n + row) * UU::kUnitTotal + (s % UU::kSbPerUnit) * UU::kSbBytes);
+#pragma unroll
+      for (int i = 0; i < (UU::kSbBytes + 3) / 4; ++i) {
+        uint32_t const lo16 = __ldg(u16 + 2 * i);
+        uint32_t const hi16 = (4 * i + 2 < UU::kSbBytes) ? uint32_t(__ldg(u16 + 2 * i + 1)) : 0u;
+        dst[i] = lo16 | (hi16 << 16);
+      }
+    }
+  };
+#pragma unroll
+  for (int i = 0; i < NSC; ++i) nxt[i] = 0u;
+  if (ntiles > 0) fetch(0, nxt);
+
+  float const coff = float(d.code_offset);
+  bool dead = false;
+  int q = 0, cur_b = ntiles > 0 ? t0 / ns : 0;
+  float tot = 0.f;
+  // a warp's sum for one block goes to slot (block + warp): runs are contiguous and ordered, so slots never collide
+  auto flush = [&](int bi) {
+    float v = tot;
+    v += __shfl_xor_sync(0xffffffffu, v, 8);
+    v += __shfl_xor_sync(0xffffffffu, v, 16);
+    if (lane < kRows) part[(bi + warp) * kRows + lane] = v;
+    tot = 0.f;
+  };
+  for (; q < ntiles; ++q) {
+    {
+      {
+        int const st = q % STAGES;
+        int const tile = t0 + q, bi = tile / ns, s = tile % ns;
+        if (bi != cur_b) { flush(cur_b); cur_b = bi; }
+#pragma unroll
+        for (int i = 0; i < NSC; ++i) cur[i] = nxt[i];
+        if (q + 1 < ntiles) fetch(q + 1, nxt);
+        if (!mbar_wait_bounded(&mybars[st], unsigned(q / STAGES) & 1u, a.status, kWaitStageTimeout)) { dead = true; break; }
+        int const pt = s * (kSlice / kPart) + kp;
+        uint32_t wl[NWL], wh[NWH];
+        load_part<LO>(mylo + st * LO_TILE, r, kp, wl);
+        if constexpr (HI != 0) load_part<(HI ? HI : 1)>(myhi + st * HI_TILE, r, kp, wh);
+        float usum[NU];
+        {
+          uint8_t const* xp = xlo + size_t(pt) * kPartStride;
+#pragma unroll
+          for (int u = 0; u < NU; ++u) {
+            __half2 acc = __float2half2_rn(0.f);
+#pragma unroll
+            for (int wi = u * (U / CWL); wi < (u + 1) * (U / CWL); ++wi) {
+              __half2 xs[NPL];
+#pragma unroll
+              for (int v = 0; v < NPL / 4; ++v) {
+                uint4 const xv = lds128(xp + wi * (NPL * 4) + v * 16);
+                xs[4 * v] = u32_as_h2(xv.x); xs[4 * v + 1] = u32_as_h2(xv.y); xs[4 * v + 2] = u32_as_h2(xv.z); xs[4 * v + 3] = u32_as_h2(xv.w);
+              }
+              acc = rt_acc_word<LO>(wl[wi], xs, acc);
+            }
+            if constexpr (HI != 0 && !kCrossHi) {
+              uint8_t const* xq = xhi + size_t(pt) * kPartStride;
+#pragma unroll
+              for (int wi = u * (U / CWH); wi < (u + 1) * (U / CWH); ++wi) {
+                __half2 xs[NPH];
+#pragma unroll
+                for (int v = 0; v < NPH / 4; ++v) {
+                  uint4 const xv = lds128(xq + wi * (NPH * 4) + v * 16);
+                  xs[4 * v] = u32_as_h2(xv.x); xs[4 * v + 1] = u32_as_h2(xv.y); xs[4 * v + 2] = u32_as_h2(xv.z); xs[4 * v + 3] = u32_as_h2(xv.w);
+                }
+                acc = rt_acc_word<(HI ? HI : 1)>(wh[wi], xs, acc);
+              }
+            }
+            usum[u] = h2_sum(acc);
+          }
+          if constexpr (kCrossHi) {                     // the low half-lane of a high word is run 2w, the high one run 2w+1
+            uint8_t const* xq = xhi + size_t(pt) * kPartStride;
+#pragma unroll
+            for (int wi = 0; wi < NWH; ++wi) {
+              __half2 xs[NPH];
+#pragma unroll
+              for (int v = 0; v < NPH / 4; ++v) {
+                uint4 const xv = lds128(xq + wi * (NPH * 4) + v * 16);
+                xs[4 * v] = u32_as_h2(xv.x); xs[4 * v + 1] = u32_as_h2(xv.y); xs[4 * v + 2] = u32_as_h2(xv.z); xs[4 * v + 3] = u32_as_h2(xv.w);
+              }
+              float2 const f = __half22float2(rt_acc_word<(HI ? HI : 1)>(wh[wi], xs, __float2half2_rn(0.f)));
+              usum[2 * wi] += f.x; usum[2 * wi + 1] += f.y;
+            }
+          }
+        }
+        // runs -> scale groups
+#pragma unroll
+        for (int j = 0; j < NQ; ++j) {
+          float gsum = 0.f;
+#pragma unroll
+          for (int u = j * (NU / NQ); u < (j + 1) * (NU / NQ); ++u) gsum += usum[u];
+          float const sx = sxq[pt * NQ + j];
+          if constexpr (MODE == 0) {
+            float2 const sz = __half22float2(u32_as_h2(cur[j]));
+            tot = fmaf(sz.x, fmaf(fm, gsum, coff * sx), tot);
+            tot = fmaf(sz.y, sx, tot);
+          } else {
+            using F = kq::Fmt<QT>;
+            using UU = kq::Unit<QT>;
+            int const grp = kp * NQ + j;                 // group inside the superblock
+            float2 const dd = __half22float2(u32_as_h2(cur[0]));     // (d, dmin); dmin lane meaningless without a min
+            uint32_t const sraw = bits_at<5>(cur, UU::bit_of(grp, 0)) & ((1u << F::kScaleBits) - 1u);
+            int sc = int(sraw);
+            if constexpr (F::kSignedScale) sc = int(int8_t(sraw));
+            sc -= F::kScaleBias;
+            float const sv = dd.x * float(sc);
+            tot = fmaf(sv, fmaf(fm, gsum, -float(F::kCodeBias) * sx), tot);
+            if constexpr (F::kHasMin) {
+              uint32_t const mraw = bits_at<5>(cur, UU::bit_of(grp, 1)) & ((1u << F::kMinBits) - 1u);
+              tot = fmaf(-dd.y * float(mraw), sx, tot);
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0 && q + STAGES < ntiles) issue(q + STAGES);
+      }
+    }
+  }
+  if (ntiles > 0 && !dead) flush(cur_b);
+  if (dead)                                               // let copies already in flight land before the CTA's memory is reused
+    for (int i = q + 1; i < ntiles && i < q + STAGES; ++i)
+      (void)mbar_wait_bounded(&mybars[i % STAGES], unsigned(i / STAGES) & 1u, nullptr, 0, 250000000ull);
+  __syncthreads();
+  // ---- every block's contributions, added in warp order (fixed: results do not depend on timing) ------------------------------
+  for (int o = threadIdx.x; o < nb_c * kRows; o += blockDim.x) {
+    int const bi = o / kRows, rr = o % kRows;
+    int const row = (blockIdx.x + bi * gridDim.x) * kRows + rr;
+    if (row >= n) continue;
+    float sum = 0.f;
+    for (int w2 = 0; w2 < 16; ++w2) {
+      int const u0 = int((long long)w2 * T / 16), u1 = int((long long)(w2 + 1) * T / 16);
+      if (u0 < (bi + 1) * ns && u1 > bi * ns) sum += part[(bi + w2) * kRows + rr];
+    }
+    size_t const oi = size_t(arow) * n + row;
+    if (d.out_kind == 1) reinterpret_cast<float*>(d.out)[oi] = sum;
+    else if (d.out_kind == 0) reinterpret_cast<__half*>(d.out)[oi] = __float2half_rn(sum);
+    else reinterpret_cast<__nv_bfloat16*>(d.out)[oi] = __float2bfloat16_rn(sum);
+  }
+}
+
+struct RtPlan { int gx, rc; size_t smem; };
+struct RtMaps { CUtensorMap lo, hi; };
+
+template <int LO, int HI, int MODE, int QT, int NQ>
+int launch_rowthread(PlaneGemvDesc const& d, cudaStream_t stream) {
+  constexpr int STAGES = (LO + HI >= 5) ? 4 : (LO + HI == 4 ? 6 : 8);     // about the same bytes in flight for every tile size
+  constexpr int Q = kPart / NQ;
+  constexpr int LO_TILE = kRows * 32 * LO, HI_TILE = HI ? kRows * 32 * HI : 0;
+  auto kern = rowthread_gemv_kernel<LO, HI, MODE, QT, NQ, STAGES>;
+  int const gy = d.m_rows;                                    // one grid row per activation row, ragged or not
+  if (gy <= 0 || gy > 65535) return 40;
+  int const E = d.experts > 0 ? d.experts : 1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  // ---- launch geometry: cached per (n, k, grid.y, device) ----------------------------------------------------------------
+  struct Key { int n, k, gy, dev; bool operator<(Key const& o) const {
+    return n != o.n ? n < o.n : k != o.k ? k < o.k : gy != o.gy ? gy < o.gy : dev < o.dev; } };
+  static std::map<Key, RtPlan> plans;
+  static std::mutex mu;
+  RtPlan p{};
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    Key const key{d.n, d.k, gy, dev};
+    auto it = plans.find(key);
+    if (it == plans.end()) {
+      int const nblocks = (d.n + kRows - 1) / kRows, sms = rt_sm_count();
+      int const act_rows = gy;
+      int const share = std::max(1, sms / std::max(1, std::min(act_rows, sms)));   // CTAs per activation row: one wave in all
+      p.gx = std::max(1, std::min(nblocks, share));
+      int per = std::min(512, (nblocks + p.gx - 1) / p.gx);            // blocks per CTA, evened; bounded by the partial-sum table
+      p.gx = (nblocks + per - 1) / per;
+      int const nparts = d.k / kPart;
+      p.smem = 1024 + size_t(16) * STAGES * (LO_TILE + HI_TILE) + size_t(nparts) * kPartStride * (HI ? 2 : 1) +
+               size_t(d.k / Q) * 4 + size_t(d.k) * 2 + 16 * 4 + size_t(16) * STAGES * 8 + size_t(per + 16) * kRows * 4;
+      p.rc = p.smem > 227 * 1024 ? 40 : 0;
+      // one ceiling for every shape of this instantiation: plans of other shapes are cached and never set it again
+      if (!p.rc && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) { (void)cudaGetLastError(); p.rc = 40; }
+      it = plans.emplace(key, p).first;
+    }
+    p = it->second;
+  }
+  if (p.rc) {
+    if (std::getenv("QUACTLIZE_B200_DEBUG")) std::fprintf(stderr, "[quactlize_b200] row-thread GEMV declines n=%d k=%d gy=%d: smem %zu\n", d.n, d.k, gy, p.smem);
+    return p.rc;
+  }
+  // ---- tensor maps: cached per plane pointer -------------------------------------------------------------------------------
+  struct MKey { void const* lo; void const* hi; int n, k, e; bool operator<(MKey const& o) const {
+    return lo != o.lo ? lo < o.lo : hi != o.hi ? hi < o.hi : n != o.n ? n < o.n : k != o.k ? k < o.k : e < o.e; } };
+  static std::map<MKey, RtMaps> maps;
+  static std::mutex mmu;
+  RtMaps m;
+  {
+    std::lock_guard<std::mutex> lk(mmu);
+    MKey const key{d.low, HI ? d.high : nullptr, d.n, d.k, E};
+    auto it = maps.find(key);
+    if (it == maps.end()) {
+      if (maps.size() > 4096) maps.clear();
+      RtMaps nm{};
+      {
+        cuuint64_t const rb = cuuint64_t(d.k) * LO / 8;
+        cuuint64_t dims[3] = {rb, cuuint64_t(d.n), cuuint64_t(E)};
+        cuuint64_t str[2] = {rb, rb * d.n};
+        cuuint32_t box[3] = {cuuint32_t(kSlice * LO / 8), cuuint32_t(kRows), 1};
+        if (!tma_make_map(&nm.lo, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.low, dims, str, box, tma_row_swizzle(kSlice * LO / 8))) return kRuntimeError;
+      }
+      if constexpr (HI != 0) {
+        cuuint64_t const rb = cuuint64_t(d.k) * HI / 8;
+        cuuint64_t dims[3] = {rb, cuuint64_t(d.n), cuuint64_t(E)};
+        cuuint64_t str[2] = {rb, rb * d.n};
+        cuuint32_t box[3] = {cuuint32_t(kSlice * HI / 8), cuuint32_t(kRows), 1};
+        if (!tma_make_map(&nm.hi, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.high, dims, str, box, tma_row_swizzle(kSlice * HI / 8))) return kRuntimeError;
+      } else {
+        nm.hi = nm.lo;
+      }
+      it = maps.emplace(key, nm).first;
+    }
+    m = it->second;
+  }
+  RtArgs a{};
+  a.d = d;
+  a.ns = d.k / kSlice; a.nblocks = (d.n + kRows - 1) / kRows;
+  a.status = rt_device_status_ptr();
+  if (!a.status) return kRuntimeError;
+  kern<<<dim3(p.gx, gy), 512, p.smem, stream>>>(m.lo, m.hi, a);
+  return 0;
+}
+
+}  // namespace
+
+// 0 launched; 40 = this form does not cover the shape (the caller falls back to the segment-per-warp kernel)
+int enqueue_rowthread_gemv(PlaneGemvDesc const& d, cudaStream_t s) {
+  if (std::getenv("QUACTLIZE_B200_DEBUG"))
+    std::fprintf(stderr, "[quactlize_b200] row-thread GEMV n=%d k=%d rows=%d experts=%d max_rows=%d bits=%d+%d gs=%d mode=%d act=%p low=%p\n",
+                 d.n, d.k, d.m_rows, d.experts, d.max_rows, d.lo_bits, d.hi_bits, d.group_size, d.scale_mode, d.act, (void const*)d.low);
+  if (d.k <= 0 || d.k % 256 || d.n < 8) return 40;
+  auto aligned = [](void const* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  if (!aligned(d.low) || (d.hi_bits && !aligned(d.high)) || !aligned(d.act)) return 40;
+  if (d.scale_mode == 1) {
+    switch (d.qtype) {
+      case 10: return launch_rowthread<2, 0, 1, 10, 4>(d, s);
+      case 11: return launch_rowthread<2, 1, 1, 11, 4>(d, s);
+      case 12: return launch_rowthread<4, 0, 1, 12, 2>(d, s);
+      case 13: return launch_rowthread<4, 1, 1, 13, 2>(d, s);
+      case 14: return launch_rowthread<4, 2, 1, 14, 4>(d, s);
+      default: return 40;
+    }
+  }
+  int const gs = d.group_size;
+  if (gs < 16 || (gs & (gs - 1)) || d.k % gs) return 40;
+  int const nq = gs >= 64 ? 1 : 64 / gs;
+  int const key = d.lo_bits * 100 + d.hi_bits * 10 + nq;
+  switch (key) {
+    case 401: return launch_rowthread<4, 0, 0, 0, 1>(d, s);
+    case 402: return launch_rowthread<4, 0, 0, 0, 2>(d, s);
+    case 404: return launch_rowthread<4, 0, 0, 0, 4>(d, s);
+    case 412: return launch_rowthread<4, 1, 0, 0, 2>(d, s);
+    case 411: return launch_rowthread<4, 1, 0, 0, 1>(d, s);
+    case 424: return launch_rowthread<4, 2, 0, 0, 4>(d, s);
+    case 421: return launch_rowthread<4, 2, 0, 0, 1>(d, s);
+    case 201: return launch_rowthread<2, 0, 0, 0, 1>(d, s);
+    case 202: return launch_rowthread<2, 0, 0, 0, 2>(d, s);
+    case 204: return launch_rowthread<2, 0, 0, 0, 4>(d, s);
+    case 214: return launch_rowthread<2, 1, 0, 0, 4>(d, s);
+    case 211: return launch_rowthread<2, 1, 0, 0, 1>(d, s);
+    case 101: return launch_rowthread<1, 0, 0, 0, 1>(d, s);
+    case 102: return launch_rowthread<1, 0, 0, 0, 2>(d, s);
+    default: return 40;
+  }
+}
+
+}  // namespace qb

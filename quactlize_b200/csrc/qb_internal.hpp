@@ -36,6 +36,7 @@ struct PlaneGemvDesc {
   int out_kind;               // 0 = fp16, 1 = fp32, 2 = bf16
 };
 int enqueue_plane_gemv(PlaneGemvDesc const& d, cudaStream_t stream);   // 0 ok, 40 unsupported shape
+int enqueue_rowthread_gemv(PlaneGemvDesc const& d, cudaStream_t stream);   // row-thread form; 40 = shape not covered by it
 
 // Tensor-core mixed-input GEMM (dense when experts == 0, else grouped with cumulative offsets).
 struct GemmDesc {
