@@ -225,7 +225,7 @@ def run_b200(args):
                    "l2": f"inputs larger than L2: {launches_per_step * WEIGHT_BYTES / 1e6:.0f} MB of weights per step, rotating"},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "traffic": traffic, "peak_source": how,
-                     "kernel": "q4k_gemv_kernel", "algorithmic_bytes_per_launch": alg,
+                     "kernel": "q4k_gemv1_kernel", "algorithmic_bytes_per_launch": alg,
                      "us_per_launch": round(per_launch_ms * 1e3, 3)},
         "e2e": {"value": round(e2e_val, 3), "unit": "GB/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                 "api": "quactlize_ppu_vecdot_dense (host pointers, pinned)"},
