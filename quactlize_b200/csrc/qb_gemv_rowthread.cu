@@ -64,6 +64,18 @@ __device__ __forceinline__ float act_at(void const* base, size_t i, int bf16) {
   return bf16 ? __uint_as_float(uint32_t(h) << 16) : __half2float(__ushort_as_half(h));
 }
 
+// shared-memory accesses by 32-bit shared-space address (keeps the address arithmetic in 32 bits)
+__device__ __forceinline__ uint4 lds128_a(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
+
 // one 32-bit plane word of B-bit codes against its NP = 16/B pattern operands
 template <int B>
 __device__ __forceinline__ __half2 rt_acc_word(uint32_t w, __half2 const* xs, __half2 acc) {
@@ -79,20 +91,26 @@ __device__ __forceinline__ __half2 rt_acc_word(uint32_t w, __half2 const* xs, __
 }
 
 // this lane's 64 codes of plane row `r`, part `kp`, out of a swizzled tile whose rows are 32*B bytes
+// byte offset(s) of this lane's codes inside a tile: fixed per lane, computed once
 template <int B>
-__device__ __forceinline__ void load_part(uint8_t const* tile, int r, int kp, uint32_t* w) {
+__device__ __forceinline__ void part_offsets(int r, int kp, uint32_t* off) {
+  if constexpr (B == 4) { off[0] = r * 128 + (((2 * kp) ^ r) << 4); off[1] = r * 128 + (((2 * kp + 1) ^ r) << 4); }
+  else if constexpr (B == 2) { off[0] = r * 64 + ((kp ^ ((r >> 1) & 3)) << 4); off[1] = 0; }
+  else { off[0] = r * 32 + ((((kp >> 1) ^ ((r >> 2) & 1))) << 4) + (kp & 1) * 8; off[1] = 0; }
+}
+template <int B>
+__device__ __forceinline__ void load_part(uint32_t tile, uint32_t const* off, uint32_t* w) {
   if constexpr (B == 4) {
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
-      uint4 const v = lds128(tile + r * 128 + (((2 * kp + j) ^ r) << 4));
+      uint4 const v = lds128_a(tile + off[j]);
       w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
     }
   } else if constexpr (B == 2) {
-    uint4 const v = lds128(tile + r * 64 + ((kp ^ ((r >> 1) & 3)) << 4));
+    uint4 const v = lds128_a(tile + off[0]);
     w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
   } else {
-    uint8_t const* p = tile + r * 32 + ((((kp >> 1) ^ ((r >> 2) & 1))) << 4) + (kp & 1) * 8;
-    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[0]), "=r"(w[1]) : "r"(smem_u32(p)));
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[0]), "=r"(w[1]) : "r"(tile + off[0]));
   }
 }
 
@@ -173,12 +191,16 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   uint8_t* mylo = lo_ring + size_t(warp) * STAGES * LO_TILE;
   uint8_t* myhi = hi_ring + size_t(warp) * STAGES * HI_TILE;
 
-  auto issue = [&](int q) {                                // q counts this warp's tiles
-    int const st = q % STAGES, tile = t0 + q, bi = tile / ns, sl = tile % ns;
-    int const row0 = (blockIdx.x + bi * gridDim.x) * kRows;
+  static_assert((STAGES & (STAGES - 1)) == 0, "ring depth is a power of two");
+  int const b_first = ntiles > 0 ? t0 / ns : 0, s_first = ntiles > 0 ? t0 % ns : 0;
+  int is_b = b_first, is_s = s_first;                      // (block, slice) of the next tile to request (lane 0 only)
+  auto issue = [&](int q) {                                // called with q = 0, 1, 2, ... in order
+    int const st = q & (STAGES - 1);
+    int const row0 = (blockIdx.x + is_b * gridDim.x) * kRows;
     mbar_expect_tx(&mybars[st], LO_TILE + HI_TILE);
-    tma_tile_3d(mylo + st * LO_TILE, &map_lo, sl * (kSlice * LO / 8), row0, e, &mybars[st]);
-    if constexpr (HI != 0) tma_tile_3d(myhi + st * HI_TILE, &map_hi, sl * (kSlice * HI / 8), row0, e, &mybars[st]);
+    tma_tile_3d(mylo + st * LO_TILE, &map_lo, is_s * (kSlice * LO / 8), row0, e, &mybars[st]);
+    if constexpr (HI != 0) tma_tile_3d(myhi + st * HI_TILE, &map_hi, is_s * (kSlice * HI / 8), row0, e, &mybars[st]);
+    if (++is_s == ns) { is_s = 0; ++is_b; }
   };
   if (lane == 0) {
 #pragma unroll
@@ -249,20 +271,23 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   constexpr int NSC = MODE == 0 ? NQ : 5;
   uint32_t cur[NSC], nxt[NSC];
   int const gs = d.group_size, kg = MODE == 0 ? k / gs : 0;
-  auto fetch = [&](int q, uint32_t* dst) {
-    int const tile = t0 + q, bi = tile / ns, s = tile % ns;
+  int f_b = b_first, f_s = s_first;                          // (block, slice) of the next tile to fetch the scale channel for
+  int const gshift = 31 - __clz(gs > 0 ? gs : 1);           // group size is a power of two
+  uint16_t const* const sp_e = MODE == 0 ? reinterpret_cast<uint16_t const*>(d.scale) + size_t(e) * kg * n : nullptr;
+  uint16_t const* const zp_e = (MODE == 0 && d.zero) ? reinterpret_cast<uint16_t const*>(d.zero) + size_t(e) * kg * n : nullptr;
+  auto fetch = [&](uint32_t* dst) {                          // called once per tile, in order
+    int const bi = f_b, s = f_s;
+    if (++f_s == ns) { f_s = 0; ++f_b; }
     int const row = (blockIdx.x + bi * gridDim.x) * kRows + r;
 #pragma unroll
     for (int i = 0; i < NSC; ++i) dst[i] = 0u;
     if (row >= n) return;
     if constexpr (MODE == 0) {
-      uint16_t const* sp = reinterpret_cast<uint16_t const*>(d.scale);
-      uint16_t const* zp = reinterpret_cast<uint16_t const*>(d.zero);
       int const k0 = s * kSlice + kp * kPart;
 #pragma unroll
       for (int j = 0; j < NQ; ++j) {
-        size_t const gi = (size_t(e) * kg + size_t(k0 + j * Q) / gs) * n + row;
-        uint32_t const sv = __ldg(sp + gi), zv = zp ? uint32_t(__ldg(zp + gi)) : 0u;
+        uint32_t const gi = uint32_t((k0 + j * Q) >> gshift) * uint32_t(n) + uint32_t(row);   // < 2^32: one expert's plane
+        uint32_t const sv = __ldg(sp_e + gi), zv = zp_e ? uint32_t(__ldg(zp_e + gi)) : 0u;
         dst[j] = sv | (zv << 16);
       }
     } else {
@@ -280,12 +305,16 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   };
 #pragma unroll
   for (int i = 0; i < NSC; ++i) nxt[i] = 0u;
-  if (ntiles > 0) fetch(0, nxt);
+  if (ntiles > 0) fetch(nxt);
 
   float const coff = float(d.code_offset);
   bool dead = false;
-  int q = 0, cur_b = ntiles > 0 ? t0 / ns : 0;
+  int q = 0, cur_b = b_first, c_b = b_first, c_s = s_first;
   float tot = 0.f;
+  uint32_t offl[2], offh[2];
+  part_offsets<LO>(r, kp, offl);
+  part_offsets<(HI ? HI : 1)>(r, kp, offh);
+  uint32_t const lo_a = smem_u32(mylo), hi_a = smem_u32(myhi), xlo_a = smem_u32(xlo), xhi_a = smem_u32(xhi), sxq_a = smem_u32(sxq);
   // a warp's sum for one block goes to slot (block + warp): runs are contiguous and ordered, so slots never collide
   auto flush = [&](int bi) {
     float v = tot;
@@ -297,20 +326,21 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   for (; q < ntiles; ++q) {
     {
       {
-        int const st = q % STAGES;
-        int const tile = t0 + q, bi = tile / ns, s = tile % ns;
+        int const st = q & (STAGES - 1);
+        int const bi = c_b, s = c_s;
+        if (++c_s == ns) { c_s = 0; ++c_b; }
         if (bi != cur_b) { flush(cur_b); cur_b = bi; }
 #pragma unroll
         for (int i = 0; i < NSC; ++i) cur[i] = nxt[i];
-        if (q + 1 < ntiles) fetch(q + 1, nxt);
-        if (!mbar_wait_bounded(&mybars[st], unsigned(q / STAGES) & 1u, a.status, kWaitStageTimeout)) { dead = true; break; }
+        if (q + 1 < ntiles) fetch(nxt);
+        if (!mbar_wait_bounded(&mybars[st], unsigned(q / STAGES) & 1u, a.status, kWaitStageTimeout)) { dead = true; break; }   // STAGES is a power of two
         int const pt = s * (kSlice / kPart) + kp;
         uint32_t wl[NWL], wh[NWH];
-        load_part<LO>(mylo + st * LO_TILE, r, kp, wl);
-        if constexpr (HI != 0) load_part<(HI ? HI : 1)>(myhi + st * HI_TILE, r, kp, wh);
+        load_part<LO>(lo_a + st * LO_TILE, offl, wl);
+        if constexpr (HI != 0) load_part<(HI ? HI : 1)>(hi_a + st * HI_TILE, offh, wh);
         float usum[NU];
         {
-          uint8_t const* xp = xlo + size_t(pt) * kPartStride;
+          uint32_t const xp = xlo_a + uint32_t(pt) * kPartStride;
 #pragma unroll
           for (int u = 0; u < NU; ++u) {
             __half2 acc = __float2half2_rn(0.f);
@@ -319,19 +349,19 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
               __half2 xs[NPL];
 #pragma unroll
               for (int v = 0; v < NPL / 4; ++v) {
-                uint4 const xv = lds128(xp + wi * (NPL * 4) + v * 16);
+                uint4 const xv = lds128_a(xp + wi * (NPL * 4) + v * 16);
                 xs[4 * v] = u32_as_h2(xv.x); xs[4 * v + 1] = u32_as_h2(xv.y); xs[4 * v + 2] = u32_as_h2(xv.z); xs[4 * v + 3] = u32_as_h2(xv.w);
               }
               acc = rt_acc_word<LO>(wl[wi], xs, acc);
             }
             if constexpr (HI != 0 && !kCrossHi) {
-              uint8_t const* xq = xhi + size_t(pt) * kPartStride;
+              uint32_t const xq = xhi_a + uint32_t(pt) * kPartStride;
 #pragma unroll
               for (int wi = u * (U / CWH); wi < (u + 1) * (U / CWH); ++wi) {
                 __half2 xs[NPH];
 #pragma unroll
                 for (int v = 0; v < NPH / 4; ++v) {
-                  uint4 const xv = lds128(xq + wi * (NPH * 4) + v * 16);
+                  uint4 const xv = lds128_a(xq + wi * (NPH * 4) + v * 16);
                   xs[4 * v] = u32_as_h2(xv.x); xs[4 * v + 1] = u32_as_h2(xv.y); xs[4 * v + 2] = u32_as_h2(xv.z); xs[4 * v + 3] = u32_as_h2(xv.w);
                 }
                 acc = rt_acc_word<(HI ? HI : 1)>(wh[wi], xs, acc);
@@ -340,13 +370,13 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
             usum[u] = h2_sum(acc);
           }
           if constexpr (kCrossHi) {                     // the low half-lane of a high word is run 2w, the high one run 2w+1
-            uint8_t const* xq = xhi + size_t(pt) * kPartStride;
+            uint32_t const xq = xhi_a + uint32_t(pt) * kPartStride;
 #pragma unroll
             for (int wi = 0; wi < NWH; ++wi) {
               __half2 xs[NPH];
 #pragma unroll
               for (int v = 0; v < NPH / 4; ++v) {
-                uint4 const xv = lds128(xq + wi * (NPH * 4) + v * 16);
+                uint4 const xv = lds128_a(xq + wi * (NPH * 4) + v * 16);
                 xs[4 * v] = u32_as_h2(xv.x); xs[4 * v + 1] = u32_as_h2(xv.y); xs[4 * v + 2] = u32_as_h2(xv.z); xs[4 * v + 3] = u32_as_h2(xv.w);
               }
               float2 const f = __half22float2(rt_acc_word<(HI ? HI : 1)>(wh[wi], xs, __float2half2_rn(0.f)));
@@ -360,7 +390,7 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
           float gsum = 0.f;
 #pragma unroll
           for (int u = j * (NU / NQ); u < (j + 1) * (NU / NQ); ++u) gsum += usum[u];
-          float const sx = sxq[pt * NQ + j];
+          float const sx = lds_f32(sxq_a + uint32_t(pt * NQ + j) * 4);
           if constexpr (MODE == 0) {
             float2 const sz = __half22float2(u32_as_h2(cur[j]));
             tot = fmaf(sz.x, fmaf(fm, gsum, coff * sx), tot);
@@ -414,7 +444,7 @@ struct RtMaps { CUtensorMap lo, hi; };
 
 template <int LO, int HI, int MODE, int QT, int NQ>
 int launch_rowthread(PlaneGemvDesc const& d, cudaStream_t stream) {
-  constexpr int STAGES = (LO + HI >= 5) ? 4 : (LO + HI == 4 ? 6 : 8);     // about the same bytes in flight for every tile size
+  constexpr int STAGES = (LO + HI >= 5) ? 4 : 8;     // a power of two; 64-96 KB in flight per SM for the wide tiles
   constexpr int Q = kPart / NQ;
   constexpr int LO_TILE = kRows * 32 * LO, HI_TILE = HI ? kRows * 32 * HI : 0;
   auto kern = rowthread_gemv_kernel<LO, HI, MODE, QT, NQ, STAGES>;
