@@ -132,8 +132,13 @@ def cfg5(reps):
                 def run():
                     qb.gemv_plane(a, low, None, scale, zero, bits, 0, gs, row_offsets=off, max_rows=mr)
                 wb = active * n * k * bits // 8
-                _emit(f"cfg5 W{bits}A16 gs64 {nm} tokens={tokens} (rows {rows}, active experts {active})",
+                _emit(f"cfg5 W{bits}A16 gs64 {nm} tokens={tokens} (rows {rows}, active experts {active}) [CUDA-core GEMV]",
                       _time_graph(run, reps), wb, {"scale_zero_bytes": active * 2 * (k // gs) * n * 2, "note": "weights L2-resident across replays"})
+
+                def run_tc():
+                    qb.gemm_plane(a, low, None, scale, zero, bits, 0, gs, row_offsets=off)
+                _emit(f"cfg5 W{bits}A16 gs64 {nm} tokens={tokens} (rows {rows}, active experts {active}) [tensor-core grouped GEMM]",
+                      _time_graph(run_tc, reps), wb, {"scale_zero_bytes": active * 2 * (k // gs) * n * 2, "note": "weights L2-resident across replays"})
 
 
 def cfg4(reps):

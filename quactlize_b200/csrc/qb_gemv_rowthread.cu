@@ -127,7 +127,8 @@ __device__ __forceinline__ uint32_t bits_at(uint32_t const* u, int bit) {
 }
 
 // LO/HI plane bits; MODE 0 fp16 scale(+zero) planes with NQ = 64/min(gs,64) runs per part, MODE 1 packed units of QT
-template <int LO, int HI, int MODE, int QT, int NQ, int STAGES>
+// MR activation rows share every weight tile (1, or up to 4 rows of one expert)
+template <int LO, int HI, int MODE, int QT, int NQ, int STAGES, int MR>
 __global__ void __launch_bounds__(512, 1)
 rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_constant__ CUtensorMap map_hi, RtArgs a) {
   constexpr int Q = kPart / NQ;                       // codes per run: one scale group (or 64 codes of a wider one)
@@ -148,20 +149,55 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int const kp = lane >> 3, r = lane & 7;
 
-  // ---- which activation row / expert ---------------------------------------------------------------------------------
-  // grid.y is the activation row; a ragged launch looks its expert up in the cumulative offsets (one probe per thread)
-  int e = 0;
-  int const arow = blockIdx.y;
+  // ---- which activation rows / expert ---------------------------------------------------------------------------------
+  // grid.y is a group of up to MR activation rows of one expert.  MR == 1: the row itself, whose expert a ragged launch
+  // looks up in the cumulative offsets (one probe per thread).  MR > 1, ragged: group y of the list "ceil(rows_e / MR)
+  // groups per expert, in expert order", located by a block-wide scan of the per-expert group counts.
+  int e = 0, arow = 0, nrows = 1;
   if (d.offsets) {
-    volatile int* s_expert = reinterpret_cast<volatile int*>(smem);      // a ring slot, not yet in use
-    if (threadIdx.x == 0) *s_expert = -1;
+    volatile int* sh = reinterpret_cast<volatile int*>(smem);            // ring space, not yet in use
+    if (threadIdx.x < 4) sh[threadIdx.x] = -1;
     __syncthreads();
-    for (int t = threadIdx.x; t < d.experts; t += blockDim.x)
-      if (arow >= d.offsets[t] && arow < d.offsets[t + 1]) *s_expert = t;
-    __syncthreads();
-    e = *s_expert;
-    __syncthreads();                                  // everyone has read it before the first copy may land there
-    if (e < 0) return;                                // uniform for the CTA: a row beyond the last offset
+    if constexpr (MR == 1) {
+      arow = blockIdx.y;
+      for (int t = threadIdx.x; t < d.experts; t += blockDim.x)
+        if (arow >= d.offsets[t] && arow < d.offsets[t + 1]) sh[0] = t;
+      __syncthreads();
+      e = sh[0];
+    } else {
+      volatile int* cnt = sh + 8;                                          // [experts] inclusive scan of group counts
+      for (int t = threadIdx.x; t < d.experts; t += blockDim.x) cnt[t] = (d.offsets[t + 1] - d.offsets[t] + MR - 1) / MR;
+      __syncthreads();
+      if (warp == 0) {                                                     // inclusive scan, 32 experts per step
+        int carry = 0;
+        for (int base = 0; base < d.experts; base += 32) {
+          int v = base + lane < d.experts ? cnt[base + lane] : 0;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) { int const u = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += u; }
+          v += carry;
+          if (base + lane < d.experts) cnt[base + lane] = v;
+          carry = __shfl_sync(0xffffffffu, v, 31);
+        }
+      }
+      __syncthreads();
+      for (int t = threadIdx.x; t < d.experts; t += blockDim.x) {
+        int const hi = cnt[t], lo = t ? cnt[t - 1] : 0;
+        if (int(blockIdx.y) >= lo && int(blockIdx.y) < hi) { sh[0] = t; sh[1] = int(blockIdx.y) - lo; }
+      }
+      __syncthreads();
+      e = sh[0];
+      if (e >= 0) {
+        int const r0 = d.offsets[e], r1 = d.offsets[e + 1];
+        arow = r0 + sh[1] * MR;
+        nrows = min(MR, r1 - arow);
+      }
+    }
+    __syncthreads();                                  // everyone has read the scratch before the first copy may land there
+    if (e < 0) return;                                // uniform for the CTA: a group beyond the last expert
+  } else {
+    arow = blockIdx.y * MR;
+    nrows = min(MR, d.m_rows - arow);
+    if (nrows <= 0) return;
   }
   int const k = d.k, n = d.n;
 
@@ -170,13 +206,14 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   int const nparts = k / kPart;
   uint8_t* lo_ring = smem;                                              // [W][STAGES][LO_TILE]
   uint8_t* hi_ring = lo_ring + size_t(W) * STAGES * LO_TILE;             // [W][STAGES][HI_TILE]
-  uint8_t* xlo = hi_ring + size_t(W) * STAGES * HI_TILE;                 // [nparts][kPartStride]
-  uint8_t* xhi = xlo + size_t(nparts) * kPartStride;                     // same, if HI
-  float* sxq = reinterpret_cast<float*>(xhi + (HI ? size_t(nparts) * kPartStride : 0));   // [k/Q]
-  uint16_t* xraw = reinterpret_cast<uint16_t*>(sxq + k / Q);             // [k] raw activations (prologue only)
+  uint32_t const xrow = uint32_t(nparts) * kPartStride;                  // bytes of one activation row in pattern order
+  uint8_t* xlo = hi_ring + size_t(W) * STAGES * HI_TILE;                 // [MR][nparts][kPartStride]
+  uint8_t* xhi = xlo + size_t(MR) * xrow;                                // same, if HI
+  float* sxq = reinterpret_cast<float*>(xhi + (HI ? size_t(MR) * xrow : 0));   // [MR][k/Q]
+  uint16_t* xraw = reinterpret_cast<uint16_t*>(sxq + MR * (k / Q));      // [k] raw activations (prologue only, one row at a time)
   float* red = reinterpret_cast<float*>(xraw + k);                       // [16]
   uint64_t* bars = reinterpret_cast<uint64_t*>(red + 16);                // [W][STAGES]
-  float* part = reinterpret_cast<float*>(bars + W * STAGES);             // [blocks of this CTA + 16][kRows]
+  float* part = reinterpret_cast<float*>(bars + W * STAGES);             // [blocks of this CTA + 16][MR][kRows]
   (void)xhi;
 
   // ---- this warp's share of the work ------------------------------------------------------------------------------------
@@ -209,63 +246,69 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     for (int q = 0; q < STAGES && q < ntiles; ++q) issue(q);          // the weight stream starts before the activations are ready
   }
-  for (int i = threadIdx.x; i < (nb_c + 16) * kRows; i += blockDim.x) part[i] = 0.f;
+  for (int i = threadIdx.x; i < (nb_c + 16) * MR * kRows; i += blockDim.x) part[i] = 0.f;
 
-  // ---- CTA prologue: activations into pattern order --------------------------------------------------------------------
-  // pass 1: raw 16-bit activations to shared memory, max |x|, and the sum of x over every Q-code run (lanes hold
-  // consecutive 8-element pieces, so a run is Q/8 neighbouring lanes)
-  size_t const xoff = size_t(arow) * k;
-  float mx = 0.f;
-  for (int i = threadIdx.x * 8; i < k; i += blockDim.x * 8) {            // k % 256 == 0: whole warps in or out
-    uint4 const v = __ldg(reinterpret_cast<uint4 const*>(reinterpret_cast<uint16_t const*>(d.act) + xoff + i));
-    *reinterpret_cast<uint4*>(xraw + i) = v;
-    uint32_t const w4[4] = {v.x, v.y, v.z, v.w};
-    float p = 0.f;
+  // ---- CTA prologue: activations into pattern order, one activation row at a time ---------------------------------------
+  float fm[MR];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      uint32_t const h = (w4[j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
-      float const f = d.act_bf16 ? __uint_as_float(h << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(h)));
-      mx = fmaxf(mx, fabsf(f));
-      p += f;
+  for (int m = 0; m < MR; ++m) {
+    fm[m] = 0.f;
+    if (m >= nrows) continue;                              // uniform for the CTA
+    // pass 1: raw 16-bit activations to shared memory, max |x|, and the sum of x over every Q-code run (lanes hold
+    // consecutive 8-element pieces, so a run is Q/8 neighbouring lanes)
+    size_t const xoff = size_t(arow + m) * k;
+    float mx = 0.f;
+    for (int i = threadIdx.x * 8; i < k; i += blockDim.x * 8) {          // k % 256 == 0: whole warps in or out
+      uint4 const v = __ldg(reinterpret_cast<uint4 const*>(reinterpret_cast<uint16_t const*>(d.act) + xoff + i));
+      *reinterpret_cast<uint4*>(xraw + i) = v;
+      uint32_t const w4[4] = {v.x, v.y, v.z, v.w};
+      float p = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint32_t const h = (w4[j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
+        float const f = d.act_bf16 ? __uint_as_float(h << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(h)));
+        mx = fmaxf(mx, fabsf(f));
+        p += f;
+      }
+#pragma unroll
+      for (int o = 1; o < Q / 8; o <<= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
+      if ((lane & (Q / 8 - 1)) == 0) sxq[m * (k / Q) + i / Q] = p;
     }
+    mx = warp_max(mx);
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    mx = 0.f;
 #pragma unroll
-    for (int o = 1; o < Q / 8; o <<= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
-    if ((lane & (Q / 8 - 1)) == 0) sxq[i / Q] = p;
-  }
-  mx = warp_max(mx);
-  if (lane == 0) red[warp] = mx;
-  __syncthreads();
-  mx = 0.f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) if (i < int(blockDim.x >> 5)) mx = fmaxf(mx, red[i]);
-  int const ex = pow2_scale_exponent(mx, HI ? 15 - LO : 15);
-  float const fm = ldexpf(1.f, 24 - ex);
-  auto xval = [&](int c) -> float {
-    uint32_t const h = xraw[c];
-    return d.act_bf16 ? __uint_as_float(h << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(h)));
-  };
-  // pass 2: one half2 operand per code pair, multiplier 2^(ex - shift) built from its exponent bits
-  for (int t = threadIdx.x; t < k / 2; t += blockDim.x) {
-    constexpr int PER = 8 / LO;
-    int const word = t / NPL, p = t % NPL, h = p / PER, o = p % PER;
-    int const c0 = word * CWL + h * PER + o;
-    float const m = __int_as_float((127 + ex - o * LO) << 23);
-    __half2 const v = __floats2half2_rn(xval(c0) * m, xval(c0 + 16 / LO) * m);
-    int const pt = (word * CWL) / kPart;
-    *reinterpret_cast<__half2*>(xlo + size_t(pt) * kPartStride + size_t(t - pt * (kPart / 2)) * 4) = v;
-  }
-  if constexpr (HI != 0) {
+    for (int i = 0; i < 16; ++i) if (i < int(blockDim.x >> 5)) mx = fmaxf(mx, red[i]);
+    int const ex = pow2_scale_exponent(mx, HI ? 15 - LO : 15);
+    fm[m] = ldexpf(1.f, 24 - ex);
+    auto xval = [&](int c) -> float {
+      uint32_t const h = xraw[c];
+      return d.act_bf16 ? __uint_as_float(h << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(h)));
+    };
+    // pass 2: one half2 operand per code pair, multiplier 2^(ex - shift) built from its exponent bits
     for (int t = threadIdx.x; t < k / 2; t += blockDim.x) {
-      constexpr int HB = HI ? HI : 1, PER = 8 / HB;
-      int const word = t / NPH, p = t % NPH, h = p / PER, o = p % PER;
-      int const c0 = word * CWH + h * PER + o;
-      float const m = __int_as_float((127 + ex + LO - o * HB) << 23);
-      __half2 const v = __floats2half2_rn(xval(c0) * m, xval(c0 + 16 / HB) * m);
-      int const pt = (word * CWH) / kPart;
-      *reinterpret_cast<__half2*>(xhi + size_t(pt) * kPartStride + size_t(t - pt * (kPart / 2)) * 4) = v;
+      constexpr int PER = 8 / LO;
+      int const word = t / NPL, p = t % NPL, h = p / PER, o = p % PER;
+      int const c0 = word * CWL + h * PER + o;
+      float const mul = __int_as_float((127 + ex - o * LO) << 23);
+      __half2 const v = __floats2half2_rn(xval(c0) * mul, xval(c0 + 16 / LO) * mul);
+      int const pt = (word * CWL) / kPart;
+      *reinterpret_cast<__half2*>(xlo + size_t(m) * xrow + size_t(pt) * kPartStride + size_t(t - pt * (kPart / 2)) * 4) = v;
     }
+    if constexpr (HI != 0) {
+      for (int t = threadIdx.x; t < k / 2; t += blockDim.x) {
+        constexpr int HB = HI ? HI : 1, PER = 8 / HB;
+        int const word = t / NPH, p = t % NPH, h = p / PER, o = p % PER;
+        int const c0 = word * CWH + h * PER + o;
+        float const mul = __int_as_float((127 + ex + LO - o * HB) << 23);
+        __half2 const v = __floats2half2_rn(xval(c0) * mul, xval(c0 + 16 / HB) * mul);
+        int const pt = (word * CWH) / kPart;
+        *reinterpret_cast<__half2*>(xhi + size_t(m) * xrow + size_t(pt) * kPartStride + size_t(t - pt * (kPart / 2)) * 4) = v;
+      }
+    }
+    __syncthreads();                                       // xraw and red are reused by the next row
   }
-  __syncthreads();
 
   // ---- scale channel of one tile, fetched one tile ahead -----------------------------------------------------------------
   constexpr int NSC = MODE == 0 ? NQ : 5;
@@ -310,110 +353,127 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   float const coff = float(d.code_offset);
   bool dead = false;
   int q = 0, cur_b = b_first, c_b = b_first, c_s = s_first;
-  float tot = 0.f;
+  float tot[MR];
+#pragma unroll
+  for (int m = 0; m < MR; ++m) tot[m] = 0.f;
   uint32_t offl[2], offh[2];
   part_offsets<LO>(r, kp, offl);
   part_offsets<(HI ? HI : 1)>(r, kp, offh);
   uint32_t const lo_a = smem_u32(mylo), hi_a = smem_u32(myhi), xlo_a = smem_u32(xlo), xhi_a = smem_u32(xhi), sxq_a = smem_u32(sxq);
-  // a warp's sum for one block goes to slot (block + warp): runs are contiguous and ordered, so slots never collide
+  uint32_t const sx_row = uint32_t(k / Q) * 4;
+  // a warp's sums for one block go to slot (block + warp): runs are contiguous and ordered, so slots never collide
   auto flush = [&](int bi) {
-    float v = tot;
-    v += __shfl_xor_sync(0xffffffffu, v, 8);
-    v += __shfl_xor_sync(0xffffffffu, v, 16);
-    if (lane < kRows) part[(bi + warp) * kRows + lane] = v;
-    tot = 0.f;
+#pragma unroll
+    for (int m = 0; m < MR; ++m) {
+      float v = tot[m];
+      v += __shfl_xor_sync(0xffffffffu, v, 8);
+      v += __shfl_xor_sync(0xffffffffu, v, 16);
+      if (lane < kRows) part[((bi + warp) * MR + m) * kRows + lane] = v;
+      tot[m] = 0.f;
+    }
   };
   for (; q < ntiles; ++q) {
+    int const st = q & (STAGES - 1);
+    int const bi = c_b, s = c_s;
+    if (++c_s == ns) { c_s = 0; ++c_b; }
+    if (bi != cur_b) { flush(cur_b); cur_b = bi; }
+#pragma unroll
+    for (int i = 0; i < NSC; ++i) cur[i] = nxt[i];
+    if (q + 1 < ntiles) fetch(nxt);
+    if (!mbar_wait_bounded(&mybars[st], unsigned(q / STAGES) & 1u, a.status, kWaitStageTimeout)) { dead = true; break; }
+    int const pt = s * (kSlice / kPart) + kp;
+    uint32_t wl[NWL], wh[NWH];
+    load_part<LO>(lo_a + st * LO_TILE, offl, wl);
+    if constexpr (HI != 0) load_part<(HI ? HI : 1)>(hi_a + st * HI_TILE, offh, wh);
+    // Once the loads above have returned, the slot can be refilled while the rows are multiplied.  The mov reads one word of
+    // every load instruction, so it cannot issue before they have completed for the whole warp; the copy is issued after it.
     {
-      {
-        int const st = q & (STAGES - 1);
-        int const bi = c_b, s = c_s;
-        if (++c_s == ns) { c_s = 0; ++c_b; }
-        if (bi != cur_b) { flush(cur_b); cur_b = bi; }
+      uint32_t dep = wl[0] ^ wl[NWL - 1] ^ (HI ? wh[0] : 0u), sink;
+      asm volatile("mov.u32 %0, %1;" : "=r"(sink) : "r"(dep) : "memory");
+      __syncwarp();
+      if (lane == 0 && q + STAGES < ntiles) issue(q + STAGES);
+    }
+    // scale channel of this lane's NQ runs, decoded once for all rows: weight = sv * (code + off) + zv
+    float sv[NQ], zv[NQ], ov[NQ];
 #pragma unroll
-        for (int i = 0; i < NSC; ++i) cur[i] = nxt[i];
-        if (q + 1 < ntiles) fetch(nxt);
-        if (!mbar_wait_bounded(&mybars[st], unsigned(q / STAGES) & 1u, a.status, kWaitStageTimeout)) { dead = true; break; }   // STAGES is a power of two
-        int const pt = s * (kSlice / kPart) + kp;
-        uint32_t wl[NWL], wh[NWH];
-        load_part<LO>(lo_a + st * LO_TILE, offl, wl);
-        if constexpr (HI != 0) load_part<(HI ? HI : 1)>(hi_a + st * HI_TILE, offh, wh);
-        float usum[NU];
-        {
-          uint32_t const xp = xlo_a + uint32_t(pt) * kPartStride;
+    for (int j = 0; j < NQ; ++j) {
+      if constexpr (MODE == 0) {
+        float2 const sz = __half22float2(u32_as_h2(cur[j]));
+        sv[j] = sz.x; zv[j] = sz.y; ov[j] = coff * sz.x;
+      } else {
+        using F = kq::Fmt<QT>;
+        using UU = kq::Unit<QT>;
+        int const grp = kp * NQ + j;                     // group inside the superblock
+        float2 const dd = __half22float2(u32_as_h2(cur[0]));         // (d, dmin); dmin lane meaningless without a min
+        uint32_t const sraw = bits_at<5>(cur, UU::bit_of(grp, 0)) & ((1u << F::kScaleBits) - 1u);
+        int sc = int(sraw);
+        if constexpr (F::kSignedScale) sc = int(int8_t(sraw));
+        sc -= F::kScaleBias;
+        sv[j] = dd.x * float(sc);
+        ov[j] = -float(F::kCodeBias) * sv[j];
+        zv[j] = 0.f;
+        if constexpr (F::kHasMin) {
+          uint32_t const mraw = bits_at<5>(cur, UU::bit_of(grp, 1)) & ((1u << F::kMinBits) - 1u);
+          zv[j] = -dd.y * float(mraw);
+        }
+      }
+    }
 #pragma unroll
-          for (int u = 0; u < NU; ++u) {
-            __half2 acc = __float2half2_rn(0.f);
+    for (int m = 0; m < MR; ++m) {
+      if (m >= nrows) continue;                          // uniform for the CTA
+      float usum[NU];
+      uint32_t const xp = xlo_a + uint32_t(m) * xrow + uint32_t(pt) * kPartStride;
+      uint32_t const xq = xhi_a + uint32_t(m) * xrow + uint32_t(pt) * kPartStride;
+      (void)xq;
 #pragma unroll
-            for (int wi = u * (U / CWL); wi < (u + 1) * (U / CWL); ++wi) {
-              __half2 xs[NPL];
+      for (int u = 0; u < NU; ++u) {
+        __half2 acc = __float2half2_rn(0.f);
 #pragma unroll
-              for (int v = 0; v < NPL / 4; ++v) {
-                uint4 const xv = lds128_a(xp + wi * (NPL * 4) + v * 16);
-                xs[4 * v] = u32_as_h2(xv.x); xs[4 * v + 1] = u32_as_h2(xv.y); xs[4 * v + 2] = u32_as_h2(xv.z); xs[4 * v + 3] = u32_as_h2(xv.w);
-              }
-              acc = rt_acc_word<LO>(wl[wi], xs, acc);
-            }
-            if constexpr (HI != 0 && !kCrossHi) {
-              uint32_t const xq = xhi_a + uint32_t(pt) * kPartStride;
+        for (int wi = u * (U / CWL); wi < (u + 1) * (U / CWL); ++wi) {
+          __half2 xs[NPL];
 #pragma unroll
-              for (int wi = u * (U / CWH); wi < (u + 1) * (U / CWH); ++wi) {
-                __half2 xs[NPH];
-#pragma unroll
-                for (int v = 0; v < NPH / 4; ++v) {
-                  uint4 const xv = lds128_a(xq + wi * (NPH * 4) + v * 16);
-                  xs[4 * v] = u32_as_h2(xv.x); xs[4 * v + 1] = u32_as_h2(xv.y); xs[4 * v + 2] = u32_as_h2(xv.z); xs[4 * v + 3] = u32_as_h2(xv.w);
-                }
-                acc = rt_acc_word<(HI ? HI : 1)>(wh[wi], xs, acc);
-              }
-            }
-            usum[u] = h2_sum(acc);
+          for (int v = 0; v < NPL / 4; ++v) {
+            uint4 const xv = lds128_a(xp + wi * (NPL * 4) + v * 16);
+            xs[4 * v] = u32_as_h2(xv.x); xs[4 * v + 1] = u32_as_h2(xv.y); xs[4 * v + 2] = u32_as_h2(xv.z); xs[4 * v + 3] = u32_as_h2(xv.w);
           }
-          if constexpr (kCrossHi) {                     // the low half-lane of a high word is run 2w, the high one run 2w+1
-            uint32_t const xq = xhi_a + uint32_t(pt) * kPartStride;
+          acc = rt_acc_word<LO>(wl[wi], xs, acc);
+        }
+        if constexpr (HI != 0 && !kCrossHi) {
 #pragma unroll
-            for (int wi = 0; wi < NWH; ++wi) {
-              __half2 xs[NPH];
+          for (int wi = u * (U / CWH); wi < (u + 1) * (U / CWH); ++wi) {
+            __half2 xs[NPH];
 #pragma unroll
-              for (int v = 0; v < NPH / 4; ++v) {
-                uint4 const xv = lds128_a(xq + wi * (NPH * 4) + v * 16);
-                xs[4 * v] = u32_as_h2(xv.x); xs[4 * v + 1] = u32_as_h2(xv.y); xs[4 * v + 2] = u32_as_h2(xv.z); xs[4 * v + 3] = u32_as_h2(xv.w);
-              }
-              float2 const f = __half22float2(rt_acc_word<(HI ? HI : 1)>(wh[wi], xs, __float2half2_rn(0.f)));
-              usum[2 * wi] += f.x; usum[2 * wi + 1] += f.y;
+            for (int v = 0; v < NPH / 4; ++v) {
+              uint4 const xv = lds128_a(xq + wi * (NPH * 4) + v * 16);
+              xs[4 * v] = u32_as_h2(xv.x); xs[4 * v + 1] = u32_as_h2(xv.y); xs[4 * v + 2] = u32_as_h2(xv.z); xs[4 * v + 3] = u32_as_h2(xv.w);
             }
+            acc = rt_acc_word<(HI ? HI : 1)>(wh[wi], xs, acc);
           }
         }
-        // runs -> scale groups
+        usum[u] = h2_sum(acc);
+      }
+      if constexpr (kCrossHi) {                         // the low half-lane of a high word is run 2w, the high one run 2w+1
 #pragma unroll
-        for (int j = 0; j < NQ; ++j) {
-          float gsum = 0.f;
+        for (int wi = 0; wi < NWH; ++wi) {
+          __half2 xs[NPH];
 #pragma unroll
-          for (int u = j * (NU / NQ); u < (j + 1) * (NU / NQ); ++u) gsum += usum[u];
-          float const sx = lds_f32(sxq_a + uint32_t(pt * NQ + j) * 4);
-          if constexpr (MODE == 0) {
-            float2 const sz = __half22float2(u32_as_h2(cur[j]));
-            tot = fmaf(sz.x, fmaf(fm, gsum, coff * sx), tot);
-            tot = fmaf(sz.y, sx, tot);
-          } else {
-            using F = kq::Fmt<QT>;
-            using UU = kq::Unit<QT>;
-            int const grp = kp * NQ + j;                 // group inside the superblock
-            float2 const dd = __half22float2(u32_as_h2(cur[0]));     // (d, dmin); dmin lane meaningless without a min
-            uint32_t const sraw = bits_at<5>(cur, UU::bit_of(grp, 0)) & ((1u << F::kScaleBits) - 1u);
-            int sc = int(sraw);
-            if constexpr (F::kSignedScale) sc = int(int8_t(sraw));
-            sc -= F::kScaleBias;
-            float const sv = dd.x * float(sc);
-            tot = fmaf(sv, fmaf(fm, gsum, -float(F::kCodeBias) * sx), tot);
-            if constexpr (F::kHasMin) {
-              uint32_t const mraw = bits_at<5>(cur, UU::bit_of(grp, 1)) & ((1u << F::kMinBits) - 1u);
-              tot = fmaf(-dd.y * float(mraw), sx, tot);
-            }
+          for (int v = 0; v < NPH / 4; ++v) {
+            uint4 const xv = lds128_a(xq + wi * (NPH * 4) + v * 16);
+            xs[4 * v] = u32_as_h2(xv.x); xs[4 * v + 1] = u32_as_h2(xv.y); xs[4 * v + 2] = u32_as_h2(xv.z); xs[4 * v + 3] = u32_as_h2(xv.w);
           }
+          float2 const f = __half22float2(rt_acc_word<(HI ? HI : 1)>(wh[wi], xs, __float2half2_rn(0.f)));
+          usum[2 * wi] += f.x; usum[2 * wi + 1] += f.y;
         }
-        __syncwarp();
-        if (lane == 0 && q + STAGES < ntiles) issue(q + STAGES);
+      }
+      // runs -> scale groups
+#pragma unroll
+      for (int j = 0; j < NQ; ++j) {
+        float gsum = 0.f;
+#pragma unroll
+        for (int u = j * (NU / NQ); u < (j + 1) * (NU / NQ); ++u) gsum += usum[u];
+        float const sx = lds_f32(sxq_a + uint32_t(m) * sx_row + uint32_t(pt * NQ + j) * 4);
+        tot[m] = fmaf(sv[j] * fm[m], gsum, tot[m]);
+        tot[m] = fmaf(ov[j] + zv[j], sx, tot[m]);
       }
     }
   }
@@ -423,16 +483,16 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
       (void)mbar_wait_bounded(&mybars[i % STAGES], unsigned(i / STAGES) & 1u, nullptr, 0, 250000000ull);
   __syncthreads();
   // ---- every block's contributions, added in warp order (fixed: results do not depend on timing) ------------------------------
-  for (int o = threadIdx.x; o < nb_c * kRows; o += blockDim.x) {
-    int const bi = o / kRows, rr = o % kRows;
+  for (int o = threadIdx.x; o < nb_c * MR * kRows; o += blockDim.x) {
+    int const bi = o / (MR * kRows), m = (o / kRows) % MR, rr = o % kRows;
     int const row = (blockIdx.x + bi * gridDim.x) * kRows + rr;
-    if (row >= n) continue;
+    if (row >= n || m >= nrows) continue;
     float sum = 0.f;
     for (int w2 = 0; w2 < 16; ++w2) {
       int const u0 = int((long long)w2 * T / 16), u1 = int((long long)(w2 + 1) * T / 16);
-      if (u0 < (bi + 1) * ns && u1 > bi * ns) sum += part[(bi + w2) * kRows + rr];
+      if (u0 < (bi + 1) * ns && u1 > bi * ns) sum += part[((bi + w2) * MR + m) * kRows + rr];
     }
-    size_t const oi = size_t(arow) * n + row;
+    size_t const oi = size_t(arow + m) * n + row;
     if (d.out_kind == 1) reinterpret_cast<float*>(d.out)[oi] = sum;
     else if (d.out_kind == 0) reinterpret_cast<__half*>(d.out)[oi] = __float2half_rn(sum);
     else reinterpret_cast<__nv_bfloat16*>(d.out)[oi] = __float2bfloat16_rn(sum);
@@ -442,13 +502,14 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
 struct RtPlan { int gx, rc; size_t smem; };
 struct RtMaps { CUtensorMap lo, hi; };
 
-template <int LO, int HI, int MODE, int QT, int NQ>
-int launch_rowthread(PlaneGemvDesc const& d, cudaStream_t stream) {
+template <int LO, int HI, int MODE, int QT, int NQ, int MR>
+int launch_rowthread_mr(PlaneGemvDesc const& d, cudaStream_t stream) {
   constexpr int STAGES = (LO + HI >= 5) ? 4 : 8;     // a power of two; 64-96 KB in flight per SM for the wide tiles
   constexpr int Q = kPart / NQ;
   constexpr int LO_TILE = kRows * 32 * LO, HI_TILE = HI ? kRows * 32 * HI : 0;
-  auto kern = rowthread_gemv_kernel<LO, HI, MODE, QT, NQ, STAGES>;
-  int const gy = d.m_rows;                                    // one grid row per activation row, ragged or not
+  auto kern = rowthread_gemv_kernel<LO, HI, MODE, QT, NQ, STAGES, MR>;
+  // grid rows: one per group of up to MR activation rows of one expert (ragged: an upper bound, surplus CTAs exit at once)
+  int const gy = MR == 1 ? d.m_rows : (d.offsets ? d.m_rows / MR + d.experts : (d.m_rows + MR - 1) / MR);
   if (gy <= 0 || gy > 65535) return 40;
   int const E = d.experts > 0 ? d.experts : 1;
   int dev = 0;
@@ -465,14 +526,14 @@ int launch_rowthread(PlaneGemvDesc const& d, cudaStream_t stream) {
     auto it = plans.find(key);
     if (it == plans.end()) {
       int const nblocks = (d.n + kRows - 1) / kRows, sms = rt_sm_count();
-      int const act_rows = gy;
+      int const act_rows = MR == 1 ? gy : std::max(1, (d.m_rows + MR - 1) / MR);    // groups that do work
       int const share = std::max(1, sms / std::max(1, std::min(act_rows, sms)));   // CTAs per activation row: one wave in all
       p.gx = std::max(1, std::min(nblocks, share));
       int per = std::min(512, (nblocks + p.gx - 1) / p.gx);            // blocks per CTA, evened; bounded by the partial-sum table
       p.gx = (nblocks + per - 1) / per;
       int const nparts = d.k / kPart;
-      p.smem = 1024 + size_t(16) * STAGES * (LO_TILE + HI_TILE) + size_t(nparts) * kPartStride * (HI ? 2 : 1) +
-               size_t(d.k / Q) * 4 + size_t(d.k) * 2 + 16 * 4 + size_t(16) * STAGES * 8 + size_t(per + 16) * kRows * 4;
+      p.smem = 1024 + size_t(16) * STAGES * (LO_TILE + HI_TILE) + size_t(MR) * nparts * kPartStride * (HI ? 2 : 1) +
+               size_t(MR) * (d.k / Q) * 4 + size_t(d.k) * 2 + 16 * 4 + size_t(16) * STAGES * 8 + size_t(per + 16) * MR * kRows * 4;
       p.rc = p.smem > 227 * 1024 ? 40 : 0;
       // one ceiling for every shape of this instantiation: plans of other shapes are cached and never set it again
       if (!p.rc && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) { (void)cudaGetLastError(); p.rc = 40; }
@@ -524,6 +585,18 @@ int launch_rowthread(PlaneGemvDesc const& d, cudaStream_t stream) {
   if (!a.status) return kRuntimeError;
   kern<<<dim3(p.gx, gy), 512, p.smem, stream>>>(m.lo, m.hi, a);
   return 0;
+}
+
+// Rows per weight pass: several rows of one expert (or of a dense batch) share every tile when there are enough of them;
+// a long K may leave no room for four rows of activations, then every row streams the weights itself.
+template <int LO, int HI, int MODE, int QT, int NQ>
+int launch_rowthread(PlaneGemvDesc const& d, cudaStream_t stream) {
+  bool const many = d.offsets ? d.m_rows >= 2 * std::max(1, d.experts) : d.m_rows >= 2;
+  if (many) {
+    int const rc = launch_rowthread_mr<LO, HI, MODE, QT, NQ, 4>(d, stream);
+    if (rc != 40) return rc;
+  }
+  return launch_rowthread_mr<LO, HI, MODE, QT, NQ, 1>(d, stream);
 }
 
 }  // namespace

@@ -175,7 +175,7 @@ def test_scale_first_gemv_dense(qtype, n, k):
 
 def test_scale_first_gemv_moe(qtype):
     f = kq.fmt(qtype)
-    n, k, rows = 64, 1024, [2, 0, 3, 1]
+    n, k, rows = 64, 1024, [2, 0, 5, 4]                 # enough rows per expert for the four-rows-per-pass kernel
     e = len(rows)
     blocks = synth.kquant_blocks(qtype, e * n * k // 256, seed=qtype).reshape(e, n * k // 256, -1)
     low, high, scale, zero = kq.prepare_gemv(blocks, n, k, qtype)
@@ -214,11 +214,13 @@ def test_generic_plane_gemv_dense(bits, gs, n, k, dtype):
     _wait_ok()
 
 
+@pytest.mark.parametrize("rows", [[0, 3, 1, 0, 0, 8, 2, 1, 0, 0, 4, 0, 1, 1, 0, 2], [5, 0, 9, 4, 1, 8, 2, 3, 0, 6, 4, 7, 1, 5, 0, 2]],
+                         ids=["row_per_pass", "four_rows_per_pass"])
 @pytest.mark.parametrize("bits", [2, 1])
-def test_generic_plane_gemv_decode_moe(bits):
-    # Qwen3-30B-A3B-like decode shape at reduced expert count: ragged rows, empty experts
+def test_generic_plane_gemv_decode_moe(bits, rows):
+    # Qwen3-30B-A3B-like decode shape at reduced expert count: ragged rows, empty experts; the second row list has enough
+    # rows per expert for the kernel that shares every weight tile among up to four rows
     e, n, k, gs = 16, 768, 2048, 64
-    rows = [0, 3, 1, 0, 0, 8, 2, 1, 0, 0, 4, 0, 1, 1, 0, 2]
     low, scale, zero = synth.group_planes(e, n, k, bits, gs, seed=bits)
     a = torch.from_numpy(synth.activations(sum(rows), k, seed=1, dtype=np.float32)).to(torch.bfloat16)
     off = np.concatenate([[0], np.cumsum(rows)]).astype(np.int32)
