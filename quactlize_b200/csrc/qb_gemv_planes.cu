@@ -405,9 +405,19 @@ int launch_plane_cpl(PlaneGemvDesc const& d, cudaStream_t s) {
 
 int enqueue_plane_gemv(PlaneGemvDesc const& d, cudaStream_t s) {
   if (d.k <= 0 || d.k % 256 || d.n <= 0) return 40;
-  // the row-thread kernel covers the common shapes; QUACTLIZE_B200_PLANE_GEMV=segment keeps the kernel below for comparison
-  static bool const segment_only = [] { char const* v = std::getenv("QUACTLIZE_B200_PLANE_GEMV"); return v && v[0] == 's'; }();
-  if (!segment_only) {
+  // Kernel choice: the tensor-core small-batch kernel when several activation rows can share a weight pass, else the
+  // row-thread kernel, else the segment-per-warp kernel below.  QUACTLIZE_B200_PLANE_GEMV = mma | rowthread | segment
+  // forces one of them (for comparisons).
+  static int const forced = [] {
+    char const* v = std::getenv("QUACTLIZE_B200_PLANE_GEMV");
+    return !v ? 0 : v[0] == 'm' ? 1 : v[0] == 'r' ? 2 : v[0] == 's' ? 3 : 0;
+  }();
+  bool const batch = d.offsets ? d.m_rows >= 2 * std::max(1, d.experts) : d.m_rows >= 2;
+  if (forced == 1 || (forced == 0 && batch)) {
+    int const rc = enqueue_rowmma_gemv(d, s);
+    if (rc != 40) return rc;
+  }
+  if (forced != 3) {
     int const rc = enqueue_rowthread_gemv(d, s);
     if (rc != 40) return rc;
   }

@@ -1,0 +1,446 @@
+// Small-batch GEMV over scale-first bit planes on the tensor cores (mma.sync m16n8k16): up to 8 activation rows of one
+// expert (or of a dense batch) share every weight tile, and the per-row multiply-accumulate work of the CUDA-core
+// kernel (qb_gemv_rowthread.cu) collapses into one MMA per 16 weight rows x 16 codes x 8 activation rows.
+//
+//   out[t, r] = sum_k a[t, k] * ( (u[r,k] + off) * s[r, k/gs] + z[r, k/gs] ),   u = low-plane code, gs >= 32
+//
+// Serves the MoE decode shapes of the reference's grouped / split-K family at a handful of rows per expert
+// (quactlize/include/moe_grouped_ppu.cuh:69-361) and small dense batches of the scale-first GEMV
+// (quactlize/include/gemv_lowbit/gemv_kernel.hpp:44-246).
+//
+// The weights never leave their packed form: (word & mask) read as fp16 IS code * 2^shift * 2^-24, and that register is
+// an A-fragment register as it stands; the power of two goes into the B fragment, which is the activation row in
+// "pattern order" prepared once per CTA in shared memory.  Lane (g, t) of a warp owns weight rows g and g+8 of a
+// 16-row tile and the t-th word (or part of a word) of every step along K, so the 16 codes of one MMA come from the
+// four lanes of a quad and always lie inside one scale group; products are accumulated in fp32 by the MMA, scaled per
+// (weight row, group) and added to running sums.  Tiles arrive by tiled TMA into per-warp mbarrier rings; every wait is
+// bounded.  Work split, partial sums and their fixed-order reduction are those of the row-thread kernel.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <map>
+#include <mutex>
+
+#include "qb_device.cuh"
+#include "qb_internal.hpp"
+#include "qb_runtime.hpp"
+#include "qb_tma.hpp"
+
+namespace qb {
+
+namespace {
+
+constexpr int kTRows = 16;           // weight rows of a tile
+constexpr int kTSlice = 256;         // codes of a tile along K
+constexpr int kCols = 8;             // activation rows per group (the n of m16n8k16)
+constexpr int kXPart = 64;           // codes per run of the pattern-order activation array
+constexpr int kXPartStride = 144;    // bytes between runs (128 + 16: neighbouring runs on different banks)
+
+struct MmaArgs {
+  PlaneGemvDesc d;
+  int ns, nblocks;                   // K slices per block, 16-row blocks
+  unsigned int* status;
+};
+
+__device__ __forceinline__ void tma_tile3(void* dst, CUtensorMap const* map, int c0, int c1, int c2, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float2 lds_f32x2(uint32_t addr) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+  return v;
+}
+// D(16x8, fp32) += A(16x16, fp16, row) * B(16x8, fp16, col)
+__device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// byte offset of 32-bit word `w` of plane row `rr` inside a TMA-swizzled tile whose rows are 32*LO bytes
+template <int LO>
+__device__ __forceinline__ uint32_t word_offset(int rr, int w) {
+  if constexpr (LO == 4) return uint32_t(rr * 128 + ((((w >> 2) ^ rr) & 7) << 4) + (w & 3) * 4);
+  else if constexpr (LO == 2) return uint32_t(rr * 64 + ((((w >> 2) ^ (rr >> 1)) & 3) << 4) + (w & 3) * 4);
+  else return uint32_t(rr * 32 + ((((w >> 2) ^ (rr >> 2)) & 1) << 4) + (w & 3) * 4);
+}
+
+// LO plane bits; WL distinct words per step across a quad (4, 2 or 1); GQ = min(group size, 256) codes
+template <int LO, int WL, int GQ, int STAGES>
+__global__ void __launch_bounds__(512, 1)
+rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, MmaArgs a) {
+  constexpr int CW = 32 / LO;                         // codes per word
+  constexpr int NP = 16 / LO;                         // half2 operands ("patterns") per word
+  constexpr int PER = 8 / LO;                         // codes per byte
+  constexpr int L = 4 / WL;                           // lanes of a quad that share a word
+  constexpr int S = WL * CW;                          // codes per step
+  constexpr int NSTEP = kTSlice / S;
+  constexpr int MSTEP = WL * NP / 8;                  // MMAs per step
+  constexpr int NGT = kTSlice / GQ;                   // scale groups per tile (1, 2, 4 or 8)
+  constexpr int NGR = NGT > 4 ? NGT / 4 : 1;          // scale registers per row and lane
+  constexpr int TILE = kTRows * 32 * LO;
+  constexpr int XPAD = LO == 4 ? 24 : 8;              // skew between activation rows: B-fragment loads spread over the banks
+  static_assert(S <= GQ && GQ % S == 0, "the codes of one MMA must lie inside one scale group");
+  static_assert((STAGES & (STAGES - 1)) == 0, "ring depth is a power of two");
+
+  PlaneGemvDesc const& d = a.d;
+  extern __shared__ uint8_t smem_dyn[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int const g = lane >> 2, t = lane & 3;
+
+  // ---- which group of activation rows / which expert (as in the row-thread kernel, 8 rows per group) ----------------------
+  int e = 0, arow = 0, nrows = 1;
+  if (d.offsets) {
+    volatile int* sh = reinterpret_cast<volatile int*>(smem);            // ring space, not yet in use
+    if (threadIdx.x < 4) sh[threadIdx.x] = -1;
+    __syncthreads();
+    volatile int* cnt = sh + 8;                                          // [experts] inclusive scan of group counts
+    for (int x = threadIdx.x; x < d.experts; x += blockDim.x) cnt[x] = (d.offsets[x + 1] - d.offsets[x] + kCols - 1) / kCols;
+    __syncthreads();
+    if (warp == 0) {
+      int carry = 0;
+      for (int base = 0; base < d.experts; base += 32) {
+        int v = base + lane < d.experts ? cnt[base + lane] : 0;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { int const u = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += u; }
+        v += carry;
+        if (base + lane < d.experts) cnt[base + lane] = v;
+        carry = __shfl_sync(0xffffffffu, v, 31);
+      }
+    }
+    __syncthreads();
+    for (int x = threadIdx.x; x < d.experts; x += blockDim.x) {
+      int const hi = cnt[x], lo = x ? cnt[x - 1] : 0;
+      if (int(blockIdx.y) >= lo && int(blockIdx.y) < hi) { sh[0] = x; sh[1] = int(blockIdx.y) - lo; }
+    }
+    __syncthreads();
+    e = sh[0];
+    if (e >= 0) {
+      int const r0 = d.offsets[e], r1 = d.offsets[e + 1];
+      arow = r0 + sh[1] * kCols;
+      nrows = min(kCols, r1 - arow);
+    }
+    __syncthreads();                                  // the scratch has been read before the first copy may land there
+    if (e < 0) return;                                // uniform for the CTA
+  } else {
+    arow = blockIdx.y * kCols;
+    nrows = min(kCols, d.m_rows - arow);
+    if (nrows <= 0) return;
+  }
+  int const k = d.k, n = d.n;
+
+  // ---- shared memory carve-up -----------------------------------------------------------------------------------------
+  constexpr int W = 16;
+  int const nparts = k / kXPart;
+  uint32_t const xrow = uint32_t(nparts) * kXPartStride + XPAD;          // bytes of one activation row in pattern order
+  uint8_t* ring = smem;                                                  // [W][STAGES][TILE]
+  uint8_t* xpat = ring + size_t(W) * STAGES * TILE;                      // [8][xrow]
+  float* sxq = reinterpret_cast<float*>(xpat + size_t(kCols) * xrow);    // [k/GQ][8]
+  float* fmv = sxq + (k / GQ) * kCols;                                   // [8] 2^(24-ex) per activation row
+  uint16_t* xraw = reinterpret_cast<uint16_t*>(fmv + kCols);             // [k] (prologue only)
+  float* red = reinterpret_cast<float*>(xraw + k);                       // [16]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(red + 16);                // [W][STAGES]
+  float* part = reinterpret_cast<float*>(bars + W * STAGES);             // [blocks of this CTA + 16][16 rows][8 cols]
+
+  // ---- this warp's contiguous run of tiles ----------------------------------------------------------------------------------
+  int const ns = a.ns;
+  int const nb_c = blockIdx.x < a.nblocks ? (a.nblocks - 1 - blockIdx.x) / gridDim.x + 1 : 0;
+  int const T = nb_c * ns;
+  int const t0 = int((long long)warp * T / 16), t1 = int((long long)(warp + 1) * T / 16);
+  int const ntiles = t1 - t0;
+  uint64_t* mybars = bars + warp * STAGES;
+  uint8_t* myring = ring + size_t(warp) * STAGES * TILE;
+  int const b_first = ntiles > 0 ? t0 / ns : 0, s_first = ntiles > 0 ? t0 % ns : 0;
+  int is_b = b_first, is_s = s_first;
+  auto issue = [&](int q) {
+    int const st = q & (STAGES - 1);
+    int const row0 = (blockIdx.x + is_b * gridDim.x) * kTRows;
+    mbar_expect_tx(&mybars[st], TILE);
+    tma_tile3(myring + st * TILE, &map_lo, is_s * (kTSlice * LO / 8), row0, e, &mybars[st]);
+    if (++is_s == ns) { is_s = 0; ++is_b; }
+  };
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) mbar_init(&mybars[s], 1);
+    mbar_init_fence();
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    for (int q = 0; q < STAGES && q < ntiles; ++q) issue(q);
+  }
+  for (int i = threadIdx.x; i < (nb_c + 16) * kTRows * kCols; i += blockDim.x) part[i] = 0.f;
+
+  // ---- CTA prologue: every activation row of the group into pattern order --------------------------------------------------
+  for (int m = 0; m < nrows; ++m) {
+    size_t const xoff = size_t(arow + m) * k;
+    float mx = 0.f;
+    for (int i = threadIdx.x * 8; i < k; i += blockDim.x * 8) {          // k % 256 == 0: whole warps in or out
+      uint4 const v = __ldg(reinterpret_cast<uint4 const*>(reinterpret_cast<uint16_t const*>(d.act) + xoff + i));
+      *reinterpret_cast<uint4*>(xraw + i) = v;
+      uint32_t const w4[4] = {v.x, v.y, v.z, v.w};
+      float p = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint32_t const h = (w4[j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
+        float const f = d.act_bf16 ? __uint_as_float(h << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(h)));
+        mx = fmaxf(mx, fabsf(f));
+        p += f;
+      }
+#pragma unroll
+      for (int o = 1; o < GQ / 8; o <<= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
+      if ((lane & (GQ / 8 - 1)) == 0) sxq[(i / GQ) * kCols + m] = p;
+    }
+    mx = warp_max(mx);
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    mx = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) mx = fmaxf(mx, red[i]);
+    int const ex = pow2_scale_exponent(mx, 15);
+    if (threadIdx.x == 0) fmv[m] = ldexpf(1.f, 24 - ex);
+    for (int x = threadIdx.x; x < k / 2; x += blockDim.x) {              // one half2 operand per code pair
+      int const word = x / NP, p = x % NP, h = p / PER, o = p % PER;
+      int const c0 = word * CW + h * PER + o;
+      float const mul = __int_as_float((127 + ex - o * LO) << 23);
+      uint32_t const h0 = xraw[c0], h1 = xraw[c0 + 16 / LO];
+      float const f0 = d.act_bf16 ? __uint_as_float(h0 << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(h0)));
+      float const f1 = d.act_bf16 ? __uint_as_float(h1 << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(h1)));
+      int const pt = (word * CW) / kXPart;
+      *reinterpret_cast<__half2*>(xpat + size_t(m) * xrow + size_t(pt) * kXPartStride + size_t(x - pt * (kXPart / 2)) * 4) =
+          __floats2half2_rn(f0 * mul, f1 * mul);
+    }
+    __syncthreads();                                       // xraw and red are reused by the next row
+  }
+
+  // ---- scale channel of one tile, fetched one tile ahead: lane t of a quad holds groups t (and t+4) of rows g and g+8 ----------
+  uint32_t cur[2 * NGR], nxt[2 * NGR];
+  int const gs = d.group_size, kg = k / gs;
+  int const gshift = 31 - __clz(gs);
+  uint16_t const* const sp_e = reinterpret_cast<uint16_t const*>(d.scale) + size_t(e) * kg * n;
+  uint16_t const* const zp_e = d.zero ? reinterpret_cast<uint16_t const*>(d.zero) + size_t(e) * kg * n : nullptr;
+  int f_b = b_first, f_s = s_first;
+  auto fetch = [&](uint32_t* dst) {
+    int const bi = f_b, s = f_s;
+    if (++f_s == ns) { f_s = 0; ++f_b; }
+    int const row = (blockIdx.x + bi * gridDim.x) * kTRows + g;
+#pragma unroll
+    for (int i = 0; i < 2 * NGR; ++i) dst[i] = 0u;
+#pragma unroll
+    for (int u = 0; u < NGR; ++u) {
+      int const jg = t + 4 * u;
+      if (jg >= NGT) continue;
+      uint32_t const grp = uint32_t(s * kTSlice + jg * GQ) >> gshift;
+#pragma unroll
+      for (int hrow = 0; hrow < 2; ++hrow) {
+        int const rr = row + 8 * hrow;
+        if (rr >= n) continue;
+        uint32_t const gi = grp * uint32_t(n) + uint32_t(rr);
+        uint32_t const sv = __ldg(sp_e + gi), zv = zp_e ? uint32_t(__ldg(zp_e + gi)) : 0u;
+        dst[2 * u + hrow] = sv | (zv << 16);
+      }
+    }
+  };
+#pragma unroll
+  for (int i = 0; i < 2 * NGR; ++i) nxt[i] = 0u;
+  if (ntiles > 0) fetch(nxt);
+
+  // ---- per-lane constants of the fragment addressing ------------------------------------------------------------------------
+  constexpr uint32_t M1 = ((1u << LO) - 1u) * 0x00010001u;
+  int const wsel = t / L, lsel = t % L;                      // which word of the step, which share of its patterns
+  uint32_t const ring_a = smem_u32(myring), xpat_a = smem_u32(xpat) + uint32_t(g) * xrow, sxq_a = smem_u32(sxq) + uint32_t(t) * 8;
+  float const coff = float(d.code_offset);
+  float totA[4] = {0.f, 0.f, 0.f, 0.f}, totB[4] = {0.f, 0.f, 0.f, 0.f};
+  bool dead = false;
+  int q = 0, cur_b = b_first, c_b = b_first, c_s = s_first;
+  float const fm0 = fmv[2 * t], fm1 = fmv[2 * t + 1];
+  // a warp's sums for one block go to slot (block + warp): runs are contiguous and ordered, so slots never collide
+  auto flush = [&](int bi) {
+    float* p0 = part + (size_t(bi + warp) * kTRows + g) * kCols + 2 * t;
+    *reinterpret_cast<float2*>(p0) = make_float2(fmaf(totA[0], fm0, totB[0]), fmaf(totA[1], fm1, totB[1]));
+    *reinterpret_cast<float2*>(p0 + 8 * kCols) = make_float2(fmaf(totA[2], fm0, totB[2]), fmaf(totA[3], fm1, totB[3]));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { totA[i] = 0.f; totB[i] = 0.f; }
+  };
+  for (; q < ntiles; ++q) {
+    int const st = q & (STAGES - 1);
+    int const bi = c_b, s = c_s;
+    if (++c_s == ns) { c_s = 0; ++c_b; }
+    if (bi != cur_b) { flush(cur_b); cur_b = bi; }
+#pragma unroll
+    for (int i = 0; i < 2 * NGR; ++i) cur[i] = nxt[i];
+    if (q + 1 < ntiles) fetch(nxt);
+    if (!mbar_wait_bounded(&mybars[st], unsigned(q / STAGES) & 1u, a.status, kWaitStageTimeout)) { dead = true; break; }
+    uint32_t const tile_a = ring_a + st * TILE;
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < NSTEP; ++j) {
+      int const w = j * WL + wsel;                           // word of the row's 256 codes this lane reads in this step
+      uint32_t const w_lo = lds32(tile_a + word_offset<LO>(g, w));
+      uint32_t const w_hi = lds32(tile_a + word_offset<LO>(g + 8, w));
+      // pattern-order activations of that word: run (s*4 + code/64), word inside the run, then this lane's patterns
+      int const code0 = j * S + wsel * CW;
+      uint32_t const xw = xpat_a + uint32_t(s * (kTSlice / kXPart) + code0 / kXPart) * kXPartStride + uint32_t((code0 % kXPart) / CW) * (NP * 4);
+#pragma unroll
+      for (int i = 0; i < MSTEP; ++i) {
+        int const p = i * 2 * L + 2 * lsel;                  // this lane's two patterns of MMA i (compile-time when L == 1)
+        int const h = p / PER, o = p % PER;
+        uint32_t const src_lo = w_lo >> (8 * h), src_hi = w_hi >> (8 * h);
+        uint32_t const mA = M1 << (o * LO), mB = M1 << ((o + 1) * LO);
+        uint2 const b = lds64(xw + uint32_t(p) * 4);
+        mma16816(c, src_lo & mA, src_hi & mA, src_lo & mB, src_hi & mB, b.x, b.y);
+      }
+      if (((j + 1) * S) % GQ == 0) {                         // a scale group is complete (compile-time condition)
+        int const jg = (j * S) / GQ;
+        uint32_t const raw_lo = __shfl_sync(0xffffffffu, cur[2 * (jg >> 2)], (lane & ~3) | (jg & 3));
+        uint32_t const raw_hi = __shfl_sync(0xffffffffu, cur[2 * (jg >> 2) + 1], (lane & ~3) | (jg & 3));
+        float2 const lo = __half22float2(u32_as_h2(raw_lo)), hi = __half22float2(u32_as_h2(raw_hi));   // (scale, zero)
+        float2 const sx = lds_f32x2(sxq_a + uint32_t(s * NGT + jg) * (kCols * 4));                     // sums of x, columns 2t, 2t+1
+        totA[0] = fmaf(lo.x, c[0], totA[0]); totA[1] = fmaf(lo.x, c[1], totA[1]);
+        totA[2] = fmaf(hi.x, c[2], totA[2]); totA[3] = fmaf(hi.x, c[3], totA[3]);
+        float const oz_lo = fmaf(coff, lo.x, lo.y), oz_hi = fmaf(coff, hi.x, hi.y);
+        totB[0] = fmaf(oz_lo, sx.x, totB[0]); totB[1] = fmaf(oz_lo, sx.y, totB[1]);
+        totB[2] = fmaf(oz_hi, sx.x, totB[2]); totB[3] = fmaf(oz_hi, sx.y, totB[3]);
+        c[0] = c[1] = c[2] = c[3] = 0.f;
+      }
+    }
+    __syncwarp();                                            // every lane's loads of this tile were consumed by its MMAs
+    if (lane == 0 && q + STAGES < ntiles) issue(q + STAGES);
+  }
+  if (ntiles > 0 && !dead) flush(cur_b);
+  if (dead)                                                  // let copies already in flight land before the CTA's memory is reused
+    for (int i = q + 1; i < ntiles && i < q + STAGES; ++i)
+      (void)mbar_wait_bounded(&mybars[i % STAGES], unsigned(i / STAGES) & 1u, nullptr, 0, 250000000ull);
+  __syncthreads();
+  // ---- every block's contributions, added in warp order (fixed: results do not depend on timing) ------------------------------
+  for (int o = threadIdx.x; o < nb_c * kTRows * kCols; o += blockDim.x) {
+    int const bi = o / (kTRows * kCols), col = (o / kTRows) % kCols, rr = o % kTRows;     // consecutive threads: consecutive rows
+    int const row = (blockIdx.x + bi * gridDim.x) * kTRows + rr;
+    if (row >= n || col >= nrows) continue;
+    float sum = 0.f;
+    for (int w2 = 0; w2 < 16; ++w2) {
+      int const u0 = int((long long)w2 * T / 16), u1 = int((long long)(w2 + 1) * T / 16);
+      if (u0 < (bi + 1) * ns && u1 > bi * ns) sum += part[(size_t(bi + w2) * kTRows + rr) * kCols + col];
+    }
+    size_t const oi = size_t(arow + col) * n + row;
+    if (d.out_kind == 1) reinterpret_cast<float*>(d.out)[oi] = sum;
+    else if (d.out_kind == 0) reinterpret_cast<__half*>(d.out)[oi] = __float2half_rn(sum);
+    else reinterpret_cast<__nv_bfloat16*>(d.out)[oi] = __float2bfloat16_rn(sum);
+  }
+}
+
+struct MmaPlan { int gx, rc; size_t smem; };
+
+template <int LO, int WL, int GQ>
+int launch_rowmma(PlaneGemvDesc const& d, cudaStream_t stream) {
+  constexpr int TILE = kTRows * 32 * LO;
+  constexpr int STAGES = LO == 1 ? 8 : 4;             // 64-128 KB in flight per SM (32 KB for the 1-bit plane)
+  constexpr int XPAD = LO == 4 ? 24 : 8;
+  auto kern = rowmma_gemv_kernel<LO, WL, GQ, STAGES>;
+  // grid rows: one per group of up to 8 activation rows of one expert (ragged: an upper bound, surplus CTAs exit at once)
+  int const gy = d.offsets ? std::min(d.m_rows, d.m_rows / kCols + d.experts) : (d.m_rows + kCols - 1) / kCols;
+  if (gy <= 0 || gy > 65535) return 40;
+  int const E = d.experts > 0 ? d.experts : 1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  struct Key { int n, k, gy, rows, dev; bool operator<(Key const& o) const {
+    return n != o.n ? n < o.n : k != o.k ? k < o.k : gy != o.gy ? gy < o.gy : rows != o.rows ? rows < o.rows : dev < o.dev; } };
+  static std::map<Key, MmaPlan> plans;
+  static std::mutex mu;
+  MmaPlan p{};
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    Key const key{d.n, d.k, gy, d.m_rows, dev};
+    auto it = plans.find(key);
+    if (it == plans.end()) {
+      int const nblocks = (d.n + kTRows - 1) / kTRows, sms = rt_sm_count();
+      // groups that do work: between rows/8 and one per expert with rows; a ragged launch cannot know, assume the mean
+      int const groups = d.offsets ? std::max(1, std::min(d.m_rows, (d.m_rows / kCols + std::min(d.experts, d.m_rows) + 1) / 2))
+                                   : (d.m_rows + kCols - 1) / kCols;
+      int const share = std::max(1, sms / std::max(1, std::min(groups, sms)));
+      p.gx = std::max(1, std::min(nblocks, share));
+      int const per = std::min(256, (nblocks + p.gx - 1) / p.gx);
+      p.gx = (nblocks + per - 1) / per;
+      int const nparts = d.k / kXPart;
+      p.smem = 1024 + size_t(16) * STAGES * TILE + size_t(kCols) * (size_t(nparts) * kXPartStride + XPAD) +
+               size_t(d.k / GQ) * kCols * 4 + kCols * 4 + size_t(d.k) * 2 + 16 * 4 + size_t(16) * STAGES * 8 +
+               size_t(per + 16) * kTRows * kCols * 4;
+      p.rc = p.smem > 227 * 1024 ? 40 : 0;
+      if (!p.rc && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) { (void)cudaGetLastError(); p.rc = 40; }
+      it = plans.emplace(key, p).first;
+    }
+    p = it->second;
+  }
+  if (p.rc) return p.rc;
+  struct MKey { void const* lo; int n, k, e; bool operator<(MKey const& o) const {
+    return lo != o.lo ? lo < o.lo : n != o.n ? n < o.n : k != o.k ? k < o.k : e < o.e; } };
+  static std::map<MKey, CUtensorMap> maps;
+  static std::mutex mmu;
+  CUtensorMap m;
+  {
+    std::lock_guard<std::mutex> lk(mmu);
+    MKey const key{d.low, d.n, d.k, E};
+    auto it = maps.find(key);
+    if (it == maps.end()) {
+      if (maps.size() > 4096) maps.clear();
+      CUtensorMap nm;
+      cuuint64_t const rb = cuuint64_t(d.k) * LO / 8;
+      cuuint64_t dims[3] = {rb, cuuint64_t(d.n), cuuint64_t(E)};
+      cuuint64_t str[2] = {rb, rb * d.n};
+      cuuint32_t box[3] = {cuuint32_t(kTSlice * LO / 8), cuuint32_t(kTRows), 1};
+      if (!tma_make_map(&nm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.low, dims, str, box, tma_row_swizzle(kTSlice * LO / 8))) return kRuntimeError;
+      it = maps.emplace(key, nm).first;
+    }
+    m = it->second;
+  }
+  MmaArgs a{};
+  a.d = d;
+  a.ns = d.k / kTSlice; a.nblocks = (d.n + kTRows - 1) / kTRows;
+  a.status = rt_device_status_ptr();
+  if (!a.status) return kRuntimeError;
+  kern<<<dim3(p.gx, gy), 512, p.smem, stream>>>(m, a);
+  return 0;
+}
+
+}  // namespace
+
+// 0 launched; 40 = this form does not cover the shape (scale-first planes without a high plane, group size >= 32, n >= 16)
+int enqueue_rowmma_gemv(PlaneGemvDesc const& d, cudaStream_t s) {
+  if (d.scale_mode != 0 || d.hi_bits != 0 || d.k <= 0 || d.k % 256 || d.n < 16) return 40;
+  auto aligned = [](void const* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  if (!aligned(d.low) || !aligned(d.act)) return 40;
+  int const gs = d.group_size;
+  if (gs < 32 || (gs & (gs - 1)) || d.k % gs) return 40;
+  int const gq = gs >= 256 ? 256 : gs;
+  switch (d.lo_bits * 1000 + gq) {
+    case 4032: return launch_rowmma<4, 4, 32>(d, s);
+    case 4064: return launch_rowmma<4, 4, 64>(d, s);
+    case 4128: return launch_rowmma<4, 4, 128>(d, s);
+    case 4256: return launch_rowmma<4, 4, 256>(d, s);
+    case 2032: return launch_rowmma<2, 2, 32>(d, s);
+    case 2064: return launch_rowmma<2, 4, 64>(d, s);
+    case 2128: return launch_rowmma<2, 4, 128>(d, s);
+    case 2256: return launch_rowmma<2, 4, 256>(d, s);
+    case 1032: return launch_rowmma<1, 1, 32>(d, s);
+    case 1064: return launch_rowmma<1, 2, 64>(d, s);
+    case 1128: return launch_rowmma<1, 4, 128>(d, s);
+    case 1256: return launch_rowmma<1, 4, 256>(d, s);
+    default: return 40;
+  }
+}
+
+}  // namespace qb

@@ -509,7 +509,7 @@ int launch_rowthread_mr(PlaneGemvDesc const& d, cudaStream_t stream) {
   constexpr int LO_TILE = kRows * 32 * LO, HI_TILE = HI ? kRows * 32 * HI : 0;
   auto kern = rowthread_gemv_kernel<LO, HI, MODE, QT, NQ, STAGES, MR>;
   // grid rows: one per group of up to MR activation rows of one expert (ragged: an upper bound, surplus CTAs exit at once)
-  int const gy = MR == 1 ? d.m_rows : (d.offsets ? d.m_rows / MR + d.experts : (d.m_rows + MR - 1) / MR);
+  int const gy = MR == 1 ? d.m_rows : (d.offsets ? std::min(d.m_rows, d.m_rows / MR + d.experts) : (d.m_rows + MR - 1) / MR);
   if (gy <= 0 || gy > 65535) return 40;
   int const E = d.experts > 0 ? d.experts : 1;
   int dev = 0;
