@@ -23,6 +23,7 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <cstdlib>
 #include <map>
 #include <mutex>
 
@@ -389,6 +390,12 @@ int enqueue_native_gemv(uint8_t const* blocks, __half const* x, float* out, int 
   a.status = rt_device_status_ptr();
   int const rows_hint = offsets ? max_rows : m_rows;
   bool const aligned = (reinterpret_cast<uintptr_t>(blocks) % 16 == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0);
+  // several activation rows per weight pass: the tensor-core kernel (QUACTLIZE_B200_Q4K_SMALLM=off keeps the CUDA-core ones)
+  static bool const no_mma = [] { char const* v = std::getenv("QUACTLIZE_B200_Q4K_SMALLM"); return v && v[0] == 'o'; }();
+  bool const batch = offsets ? m_rows >= 2 * a.experts : m_rows >= 2;
+  if (qtype == 12 && !per_row_x && !force_generic && aligned && a.status && batch && !no_mma) {
+    if (enqueue_q4k_mma(blocks, x, out, offsets, n, bpr, a.experts, m_rows, a.status, stream)) return 0;
+  }
   if (qtype == 12 && !per_row_x && !force_generic && aligned && a.status && rows_hint <= 2) {
     // one or two activation rows: the single-row kernel, once per row (the second pass hits L2)
     if (enqueue_q4k_gemv1(blocks, x, out, offsets, n, bpr, a.experts, m_rows, max_rows, a.status, stream)) return 0;

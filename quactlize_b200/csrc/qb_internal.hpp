@@ -13,6 +13,8 @@ int enqueue_native_gemv(uint8_t const* blocks, __half const* x, float* out, int 
                         bool force_generic, cudaStream_t stream);
 bool enqueue_q4k_gemv1(uint8_t const* blocks, __half const* x, float* out, int const* offsets, int n, int bpr,
                        int experts, int rows, int max_rows, unsigned int* status, cudaStream_t stream);
+bool enqueue_q4k_mma(uint8_t const* blocks, __half const* x, float* out, int const* offsets, int n, int bpr, int experts,
+                     int rows, unsigned int* status, cudaStream_t stream);   // tensor-core small-batch form
 bool enqueue_dequantize(uint8_t const* blocks, __half* out, int count, int qtype, cudaStream_t s);
 bool enqueue_prepass(uint8_t const* sblocks, uint16_t const* d, uint16_t const* dmin, int count, int qtype, int zmul,
                      __half* scale, __half* zero, cudaStream_t s);
