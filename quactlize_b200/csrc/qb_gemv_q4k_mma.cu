@@ -283,7 +283,7 @@ __global__ void __launch_bounds__(512, 1) q4k_mma_kernel(const __grid_constant__
     float sum = 0.f;
     for (int w2 = 0; w2 < 16; ++w2) {
       int const u0 = int((long long)w2 * T / 16), u1 = int((long long)(w2 + 1) * T / 16);
-      if (u0 < (bi + 1) * bpr && u1 > bi * bpr) sum += part[(size_t(bi + w2) * kQRows + rr) * kQCols + col];
+      if (u1 > u0 && u0 < (bi + 1) * bpr && u1 > bi * bpr) sum += part[(size_t(bi + w2) * kQRows + rr) * kQCols + col];
     }
     a.out[size_t(arow + col) * n + row] = sum;
   }

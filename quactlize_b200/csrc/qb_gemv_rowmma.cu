@@ -334,7 +334,7 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, MmaArgs a) {
     float sum = 0.f;
     for (int w2 = 0; w2 < 16; ++w2) {
       int const u0 = int((long long)w2 * T / 16), u1 = int((long long)(w2 + 1) * T / 16);
-      if (u0 < (bi + 1) * ns && u1 > bi * ns) sum += part[(size_t(bi + w2) * kTRows + rr) * kCols + col];
+      if (u1 > u0 && u0 < (bi + 1) * ns && u1 > bi * ns) sum += part[(size_t(bi + w2) * kTRows + rr) * kCols + col];
     }
     size_t const oi = size_t(arow + col) * n + row;
     if (d.out_kind == 1) reinterpret_cast<float*>(d.out)[oi] = sum;

@@ -490,7 +490,7 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
     float sum = 0.f;
     for (int w2 = 0; w2 < 16; ++w2) {
       int const u0 = int((long long)w2 * T / 16), u1 = int((long long)(w2 + 1) * T / 16);
-      if (u0 < (bi + 1) * ns && u1 > bi * ns) sum += part[((bi + w2) * MR + m) * kRows + rr];
+      if (u1 > u0 && u0 < (bi + 1) * ns && u1 > bi * ns) sum += part[((bi + w2) * MR + m) * kRows + rr];
     }
     size_t const oi = size_t(arow + m) * n + row;
     if (d.out_kind == 1) reinterpret_cast<float*>(d.out)[oi] = sum;

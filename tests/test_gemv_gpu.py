@@ -214,6 +214,18 @@ def test_generic_plane_gemv_dense(bits, gs, n, k, dtype):
     _wait_ok()
 
 
+@pytest.mark.parametrize("bits,gs,n,k", [(4, 128, 4096, 4096), (4, 128, 2048, 4096), (4, 128, 64, 3072), (4, 128, 64, 8192),
+                                         (2, 16, 64, 14336), (2, 64, 256, 14336), (1, 64, 1536, 2048), (4, 32, 72, 1024)])
+def test_generic_plane_gemv_single_row_shapes(bits, gs, n, k):
+    # one activation row through the row-thread kernel: several row blocks per CTA, K split over few / all warps, ragged
+    # last stage of a ring (K not a multiple of 1024), n not a multiple of 8
+    low, scale, zero = synth.group_planes(1, n, k, bits, gs, seed=bits + n)
+    x = synth.activations(1, k, seed=4)
+    out = qb.gemv_plane(_cuda(x), _cuda(low), None, _cuda(scale), _cuda(zero), bits, 0, gs, out_dtype=torch.float32)
+    assert kq.max_rel(out.cpu().numpy(), kq.planes_matmul(x, low, None, scale, zero, bits, 0, gs)) < TOL
+    _wait_ok()
+
+
 @pytest.mark.parametrize("rows", [[0, 3, 1, 0, 0, 8, 2, 1, 0, 0, 4, 0, 1, 1, 0, 2], [5, 0, 9, 4, 1, 8, 2, 3, 0, 6, 4, 7, 1, 5, 0, 2]],
                          ids=["row_per_pass", "four_rows_per_pass"])
 @pytest.mark.parametrize("bits", [2, 1])
