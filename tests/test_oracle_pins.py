@@ -129,3 +129,33 @@ def test_real_q4k_blocks_gold():
     import gguf
     off = gguf.quants.dequantize(blocks, gguf.GGMLQuantizationType.Q4_K).reshape(n, k)
     assert np.array_equal(off.astype(np.float32), kq.dequantize_f32(blocks, 12).reshape(n, k))
+
+
+# ---- canonical K-pack carrier: SHA-256 goldens of the reference (tests/test_reference_gguf_kpack.py:29-66) ----------------
+
+KPACK_SHA256 = {
+    10: ("17c5bc5ffa2c3796060988b43dcbe6b8ab15f1e0cfff8d1fc203163b511cf834", "e3b0c44298fc1c149afbf4c8996fb92427ae41e4649b934ca495991b7852b855",
+         "8e74ce7f1c0a324e377025b52d041fe951adb73382476027c962c18f18182b06"),
+    11: ("25d1cd007ac3b09944ee3fe7907f8a6c28b1648a805b125d72646ee2a4442673", "aeb7f677e045094859431309010b14a87131d0cd0227f263472145d0d2b12065",
+         "681e897a5308d65fb365262bc53445b179a2ef685d951c430285a8ebb789a580"),
+    12: ("3d4096663c410cf9fe53640b326327d3bc25af58c52a183a9fa9bd0c35652452", "e3b0c44298fc1c149afbf4c8996fb92427ae41e4649b934ca495991b7852b855",
+         "1a9546a67e9b7a15374150f1c418d00f98b5aa48f25fe21f0231013e805f338a"),
+    13: ("53f75fa3c1661bd764addd82ef2c183247a6244645d90e5ebc780f9ed6a41fe2", "c59f97a90cac811b5c7f5ac46cadc1f53a3ddd1a580ec8423c5f9d5584a1a4f4",
+         "316e801f5b78e98e736a8640c15eaba740256fa9d14ec52578f45862f571d1ab"),
+    14: ("a38cc40e0b4763215d7799a02ac61ba2f391a537729c04203c9c78275f54b27e", "c32f0a1246d31041c5cc6b1f316d7ce445f4f1dd41933ab309709989ed938ea7",
+         "b679c272d8da7aec284aa4b9ee41aba5960c2e7861a70e264604ee7e5f8d1285"),
+}
+
+
+def test_kpack_carrier_matches_reference_sha256(qtype):
+    """The reference binds its K-pack carrier to exact bytes with SHA-256 digests over a deterministic byte pattern
+    (n=256, k=512, raw byte i = (i*73 + qtype*19 + 7) & 0xFF); the oracle's planes and units reproduce all three."""
+    import hashlib
+    f = kq.fmt(qtype)
+    n, k = 256, 512
+    rows = n * (k // 256)
+    raw = ((np.arange(rows * f.block_bytes, dtype=np.int64) * 73 + qtype * 19 + 7) & 0xFF).astype(np.uint8).reshape(rows, f.block_bytes)
+    low, high, units = kq.prepare_kpack(raw, n, k, qtype)
+    got = tuple(hashlib.sha256(np.ascontiguousarray(t).tobytes()).hexdigest() for t in (low, high, units))
+    assert got == KPACK_SHA256[qtype]
+    assert np.array_equal(kq.recover_from_kpack(low, high, units, n, k, qtype), raw)
