@@ -427,9 +427,7 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
       (void)xq;
 #pragma unroll
       for (int u = 0; u < NU; ++u) {
-        // one short chain of HFMA2 per word, joined afterwards: the words of a run do not wait for each other
         __half2 acc = __float2half2_rn(0.f);
-        __half2 accw[U / CWL];
 #pragma unroll
         for (int wi = u * (U / CWL); wi < (u + 1) * (U / CWL); ++wi) {
           __half2 xs[NPL];
@@ -438,10 +436,8 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
             uint4 const xv = lds128_a(xp + wi * (NPL * 4) + v * 16);
             xs[4 * v] = u32_as_h2(xv.x); xs[4 * v + 1] = u32_as_h2(xv.y); xs[4 * v + 2] = u32_as_h2(xv.z); xs[4 * v + 3] = u32_as_h2(xv.w);
           }
-          accw[wi - u * (U / CWL)] = rt_acc_word<LO>(wl[wi], xs, __float2half2_rn(0.f));
+          acc = rt_acc_word<LO>(wl[wi], xs, acc);
         }
-#pragma unroll
-        for (int w2 = 0; w2 < U / CWL; ++w2) acc = __hadd2(acc, accw[w2]);
         if constexpr (HI != 0 && !kCrossHi) {
 #pragma unroll
           for (int wi = u * (U / CWH); wi < (u + 1) * (U / CWH); ++wi) {
