@@ -20,14 +20,27 @@
 using namespace qb;
 
 namespace {
+// Two tensor-core tactics are compiled (CTA tile 256 x 256 and 128 x 128, K stage 64); a null or empty name lets the launcher
+// choose by rows per expert, a known name forces that tile, an unknown name is declined with a message and the default runs.
 constexpr char const* kTensorConfig = "256x256x64:tcgen05";
-quactlize_ppu_config_v1 const kDenseConfigs[] = {{false, kTensorConfig, 256, 256, 128, 256, 3}, {true, "gemv_lowbit", 0, 0, 0, 0, 0}};
-quactlize_ppu_config_v1 const kGroupedConfigs[] = {{false, kTensorConfig, 256, 256, 128, 256, 3}, {true, "vecdot_moe", 0, 0, 0, 0, 0}};
+constexpr char const* kTensorConfigSmall = "128x128x64:tcgen05";
+quactlize_ppu_config_v1 const kDenseConfigs[] = {{false, kTensorConfig, 256, 256, 128, 256, 3}, {false, kTensorConfigSmall, 128, 128, 128, 128, 4},
+                                                 {true, "gemv_lowbit", 0, 0, 0, 0, 0}};
+quactlize_ppu_config_v1 const kGroupedConfigs[] = {{false, kTensorConfig, 256, 256, 128, 256, 3}, {false, kTensorConfigSmall, 128, 128, 128, 128, 4},
+                                                   {true, "vecdot_moe", 0, 0, 0, 0, 0}};
 
-bool tensor_name_ok(char const* name) { return !name || !name[0] || std::strcmp(name, kTensorConfig) == 0; }
-void decline(char const* name) {
-  if (!tensor_name_ok(name))
-    std::fprintf(stderr, "[quactlize_b200] tensor config '%s' is not compiled in; running default '%s'\n", name, kTensorConfig);
+int tile_of(char const* name) {                    // 0 = default choice, 128 / 256 = forced tile, -1 = unknown name
+  if (!name || !name[0]) return 0;
+  if (std::strcmp(name, kTensorConfig) == 0) return 256;
+  if (std::strcmp(name, kTensorConfigSmall) == 0) return 128;
+  return -1;
+}
+bool tensor_name_ok(char const* name) { return tile_of(name) >= 0; }
+int decline(char const* name) {                    // the tile to run
+  int const t = tile_of(name);
+  if (t >= 0) return t;
+  std::fprintf(stderr, "[quactlize_b200] tensor config '%s' is not compiled in; running the default choice\n", name);
+  return 0;
 }
 bool shape_ok(int n, int k) { return n > 0 && n % 256 == 0 && k > 0 && k % 256 == 0; }
 int converter_offset(int qtype) { return (qtype == 12 || qtype == 13 || qtype == 14) ? -8 : 0; }
@@ -41,12 +54,12 @@ int unit_sb_bytes(int qtype) { return qtype == 10 ? 20 : qtype == 11 ? 14 : qtyp
 int64_t plane_elems(int n, int k, int experts, int qtype) { return int64_t(experts) * (k / kq::group_size(qtype)) * n; }
 
 GemmDesc kq_desc(void const* act, uint8_t const* low, uint8_t const* high, void const* scale, void const* zero, void* out,
-                 int rows, int n, int k, int qtype, int experts, int const* offsets, int code_offset) {
+                 int rows, int n, int k, int qtype, int experts, int const* offsets, int code_offset, int tile) {
   GemmDesc d{};
   d.act = act; d.low = low; d.high = kq::hi_bits(qtype) ? high : nullptr; d.scale = scale; d.zero = zero; d.out = out;
   d.offsets = offsets; d.total_rows = rows; d.n = n; d.k = k; d.experts = experts;
   d.group_size = kq::group_size(qtype); d.lo_bits = kq::lo_bits(qtype); d.hi_bits = kq::hi_bits(qtype);
-  d.code_offset = code_offset; d.act_bf16 = 0;
+  d.code_offset = code_offset; d.act_bf16 = 0; d.tile = tile;
   return d;
 }
 
@@ -60,7 +73,7 @@ bool make_offsets(int const* rows_per_expert, int experts, int total_rows, int* 
 // host-pointer scale-first GEMM (dense: experts == 0)
 int host_planes_gemm(uint16_t const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale, uint16_t const* zero,
                      uint16_t* out, int rows, int n, int k, int qtype, int experts, int const* rows_per_expert,
-                     int code_offset, char const* what) {
+                     int code_offset, int tile, char const* what) {
   rt_clear_error();
   int const we = experts > 0 ? experts : 1;
   size_t const lo_b = size_t(we) * n * k * kq::lo_bits(qtype) / 8, hi_b = size_t(we) * n * k * kq::hi_bits(qtype) / 8;
@@ -74,7 +87,7 @@ int host_planes_gemm(uint16_t const* act, uint8_t const* low, uint8_t const* hig
   if (experts > 0) doff.from_host(offs);
   if (!rt_ok()) return kRuntimeError;
   GemmDesc d = kq_desc(da.p, dl.as<uint8_t>(), dh.as<uint8_t>(), ds.p, zero ? dz.p : nullptr, dout.p, rows, n, k, qtype,
-                       experts, doff.as<int>(), code_offset);
+                       experts, doff.as<int>(), code_offset, tile);
   int const rc = enqueue_mixed_gemm(d, nullptr);
   if (rc) return rc;
   if (!rt_check_launch(what) || !rt_sync(nullptr, what) || !rt_device_status_ok(nullptr, what)) return kRuntimeError;
@@ -84,7 +97,7 @@ int host_planes_gemm(uint16_t const* act, uint8_t const* low, uint8_t const* hig
 // device-pointer fully-quantized GEMM: units -> fp16 planes in the workspace -> GEMM
 int dev_units_gemm(uint16_t const* act, uint8_t const* low, uint8_t const* high, uint8_t const* units, int const* offsets,
                    uint16_t* out, int rows, int n, int k, int experts, int qtype, void* workspace, int64_t workspace_bytes,
-                   cudaStream_t s, char const* what) {
+                   cudaStream_t s, int tile, char const* what) {
   int const we = experts > 0 ? experts : 1;
   int64_t const pe = plane_elems(n, k, we, qtype);
   if (!workspace || workspace_bytes < pe * 4) return 37;
@@ -94,14 +107,15 @@ int dev_units_gemm(uint16_t const* act, uint8_t const* low, uint8_t const* high,
   // the reference's placed-code convention (quactlize/formats.py:315-321): int4-low codes are converted as (low - 8) and
   // the zero plane carries the matching correction, which keeps |zero| small and its fp16 rounding with it
   if (!enqueue_prepass_unit(units, sc, zr, we, n, k / 256, qtype, placed_zmul(qtype), s)) return 33;
-  GemmDesc d = kq_desc(act, low, high, sc, zr, out, rows, n, k, qtype, experts, offsets, converter_offset(qtype));
+  GemmDesc d = kq_desc(act, low, high, sc, zr, out, rows, n, k, qtype, experts, offsets, converter_offset(qtype), tile);
   int const rc = enqueue_mixed_gemm(d, s);
   if (rc) return rc;
   return rt_check_launch(what) ? 0 : kRuntimeError;
 }
 
 int host_units_gemm(uint16_t const* act, uint8_t const* low, uint8_t const* high, uint8_t const* units,
-                    int const* rows_per_expert, uint16_t* out, int rows, int n, int k, int experts, int qtype, char const* what) {
+                    int const* rows_per_expert, uint16_t* out, int rows, int n, int k, int experts, int qtype, int tile,
+                    char const* what) {
   rt_clear_error();
   int const we = experts > 0 ? experts : 1;
   size_t const lo_b = size_t(we) * n * k * kq::lo_bits(qtype) / 8, hi_b = size_t(we) * n * k * kq::hi_bits(qtype) / 8;
@@ -116,7 +130,7 @@ int host_units_gemm(uint16_t const* act, uint8_t const* low, uint8_t const* high
   if (experts > 0) doff.from_host(offs);
   if (!rt_ok()) return kRuntimeError;
   int const rc = dev_units_gemm(da.as<uint16_t>(), dl.as<uint8_t>(), dh.as<uint8_t>(), du.as<uint8_t>(), doff.as<int>(),
-                                dout.as<uint16_t>(), rows, n, k, experts, qtype, ws.p, pe * 4, nullptr, what);
+                                dout.as<uint16_t>(), rows, n, k, experts, qtype, ws.p, pe * 4, nullptr, tile, what);
   if (rc) return rc;
   if (!rt_sync(nullptr, what) || !rt_device_status_ok(nullptr, what)) return kRuntimeError;
   return rt_copy_out(dout.p, out, size_t(rows) * n * 2, nullptr) ? 0 : kRuntimeError;
@@ -128,11 +142,11 @@ bool fq_ok(int k, int qtype) { return kq::raw_bytes(qtype) != 0 && (k / 256) % s
 // ---- config inventory (quactlize/include/quactlize_ppu_config.h:42-119) ------------------------------------------------
 extern "C" int32_t quactlize_ppu_list_configs(quactlize_ppu_config_v1 const** configs) {
   if (configs) *configs = kDenseConfigs;
-  return 2;
+  return 3;
 }
 extern "C" int32_t quactlize_ppu_list_grouped_configs(quactlize_ppu_config_v1 const** configs) {
   if (configs) *configs = kGroupedConfigs;
-  return 2;
+  return 3;
 }
 extern "C" int32_t quactlize_ppu_dense_lowbit_config_valid_v1(int m, int n, int k, int group_size, int qtype, char const* name) {
   return tensor_name_ok(name) && kq::raw_bytes(qtype) != 0 && m > 0 && shape_ok(n, k) && group_size == kq::group_size(qtype);
@@ -149,9 +163,10 @@ extern "C" int32_t quactlize_ppu_grouped_fully_quantized_config_valid_v1(int tot
                                                                          int max_rows, int qtype, char const* name) {
   return quactlize_ppu_grouped_lowbit_config_valid_v1(total_rows, n, k, group_size, experts, max_rows, qtype, name) && fq_ok(k, qtype);
 }
-static int32_t list_one(quactlize_ppu_config_v2* configs, int32_t capacity, bool valid) {
+static int32_t list_one(quactlize_ppu_config_v2* configs, int32_t capacity, bool valid) {   // both tactics run every valid shape
   if (valid && configs && capacity > 0) configs[0] = {false, kTensorConfig, 256, 256, 64, 128, 256, 3};
-  return valid ? 1 : 0;
+  if (valid && configs && capacity > 1) configs[1] = {false, kTensorConfigSmall, 128, 128, 64, 128, 128, 4};
+  return valid ? 2 : 0;
 }
 extern "C" int32_t quactlize_ppu_list_valid_dense_lowbit_configs_v2(quactlize_ppu_config_v2* c, int32_t cap, int m, int n, int k, int gs, int qtype) {
   return list_one(c, cap, quactlize_ppu_dense_lowbit_config_valid_v1(m, n, k, gs, qtype, nullptr));
@@ -171,8 +186,8 @@ extern "C" int quactlize_ppu_dense_lowbit_config_v1(uint16_t const* act, uint8_t
   if (!act || !low || !scale || !zero || !out || m <= 0 || !shape_ok(n, k)) return 30;
   if (kq::raw_bytes(qtype) == 0) return 33;
   if (group_size != kq::group_size(qtype) || (kq::hi_bits(qtype) && !high)) return 32;
-  decline(config_name);
-  return host_planes_gemm(act, low, high, scale, zero, out, m, n, k, qtype, 0, nullptr, converter_offset(qtype), "scale-first dense GEMM");
+  int const tile = decline(config_name);
+  return host_planes_gemm(act, low, high, scale, zero, out, m, n, k, qtype, 0, nullptr, converter_offset(qtype), tile, "scale-first dense GEMM");
 }
 extern "C" int quactlize_ppu_dense_lowbit(uint16_t const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale,
                                           uint16_t const* zero, uint16_t* out, int m, int n, int k, int group_size, int qtype) {
@@ -185,8 +200,8 @@ extern "C" int quactlize_ppu_dense_fully_quantized_config_v1(uint16_t const* act
                                                              char const* config_name) {
   if (!act || !low || !units || !out || m <= 0 || !shape_ok(n, k)) return 30;
   if (!fq_ok(k, qtype) || (kq::hi_bits(qtype) && !high)) return 33;
-  decline(config_name);
-  return host_units_gemm(act, low, high, units, nullptr, out, m, n, k, 0, qtype, "fully-quantized dense GEMM");
+  int const tile = decline(config_name);
+  return host_units_gemm(act, low, high, units, nullptr, out, m, n, k, 0, qtype, tile, "fully-quantized dense GEMM");
 }
 extern "C" int quactlize_ppu_dense_fully_quantized(uint16_t const* act, uint8_t const* low, uint8_t const* high,
                                                    uint8_t const* units, uint16_t* out, int m, int n, int k, int qtype) {
@@ -202,9 +217,9 @@ extern "C" int quactlize_ppu_dense_fully_quantized_dev_v2(uint16_t const* act, u
                                                           char const* config_name) {
   int64_t const need = quactlize_ppu_dense_fully_quantized_workspace_bytes_v1(m, n, k, qtype);
   if (!act || !low || !units || !out || !workspace || need < 0 || workspace_bytes < need || (kq::hi_bits(qtype) && !high)) return 30;
-  decline(config_name);
+  int const tile = decline(config_name);
   return dev_units_gemm(act, low, high, units, nullptr, out, m, n, k, 0, qtype, workspace, workspace_bytes,
-                        static_cast<cudaStream_t>(stream), "fully-quantized dense GEMM enqueue");
+                        static_cast<cudaStream_t>(stream), tile, "fully-quantized dense GEMM enqueue");
 }
 extern "C" int quactlize_ppu_dense_fully_quantized_dev_v1(uint16_t const* act, uint8_t const* low, uint8_t const* high,
                                                           uint8_t const* units, uint16_t* out, int m, int n, int k, int qtype,
@@ -220,9 +235,9 @@ extern "C" int quactlize_ppu_grouped_lowbit_config_v1(uint16_t const* act, uint8
   if (!act || !low || !scale || !rows_per_expert || !out || total_rows <= 0 || experts <= 0 || !shape_ok(n, k)) return 30;
   if (kq::raw_bytes(qtype) == 0) return 33;
   if (group_size != kq::group_size(qtype) || (kq::hi_bits(qtype) && !high)) return 32;
-  decline(config_name);
+  int const tile = decline(config_name);
   return host_planes_gemm(act, low, high, scale, nullptr, out, total_rows, n, k, qtype, experts, rows_per_expert,
-                          centred_offset(qtype), "scale-first grouped GEMM");
+                          centred_offset(qtype), tile, "scale-first grouped GEMM");
 }
 extern "C" int quactlize_ppu_grouped_lowbit(uint16_t const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale,
                                             int const* rows_per_expert, uint16_t* out, int total_rows, int n, int k,
@@ -241,9 +256,9 @@ extern "C" int quactlize_ppu_grouped_lowbit_dev_v2(uint16_t const* act, uint8_t 
   int64_t const need = quactlize_ppu_grouped_lowbit_workspace_bytes_v1(max_rows, n, k, group_size, experts, qtype);
   if (!act || !low || !scale || !offsets || !out || total_rows <= 0 || need < 0 || workspace_bytes < need ||
       (kq::hi_bits(qtype) && !high)) return 30;
-  decline(config_name);
+  int const tile = decline(config_name);
   rt_clear_error();
-  GemmDesc d = kq_desc(act, low, high, scale, nullptr, out, total_rows, n, k, qtype, experts, offsets, centred_offset(qtype));
+  GemmDesc d = kq_desc(act, low, high, scale, nullptr, out, total_rows, n, k, qtype, experts, offsets, centred_offset(qtype), tile);
   int const rc = enqueue_mixed_gemm(d, static_cast<cudaStream_t>(stream));
   if (rc) return rc;
   return rt_check_launch("scale-first grouped GEMM enqueue") ? 0 : kRuntimeError;
@@ -263,8 +278,8 @@ extern "C" int quactlize_ppu_grouped_fully_quantized_config_v1(uint16_t const* a
                                                                char const* config_name) {
   if (!act || !low || !units || !rows_per_expert || !out || total_rows <= 0 || experts <= 0 || !shape_ok(n, k)) return 30;
   if (!fq_ok(k, qtype) || (kq::hi_bits(qtype) && !high)) return 33;
-  decline(config_name);
-  return host_units_gemm(act, low, high, units, rows_per_expert, out, total_rows, n, k, experts, qtype, "fully-quantized grouped GEMM");
+  int const tile = decline(config_name);
+  return host_units_gemm(act, low, high, units, rows_per_expert, out, total_rows, n, k, experts, qtype, tile, "fully-quantized grouped GEMM");
 }
 extern "C" int quactlize_ppu_grouped_fully_quantized(uint16_t const* act, uint8_t const* low, uint8_t const* high,
                                                      uint8_t const* units, int const* rows_per_expert, uint16_t* out,
@@ -283,9 +298,9 @@ extern "C" int quactlize_ppu_grouped_fully_quantized_dev_v2(uint16_t const* act,
   int64_t const need = quactlize_ppu_grouped_fully_quantized_workspace_bytes_v1(max_rows, n, k, experts, qtype);
   if (!act || !low || !units || !offsets || !out || !workspace || total_rows <= 0 || need < 0 || workspace_bytes < need ||
       (kq::hi_bits(qtype) && !high)) return 30;
-  decline(config_name);
+  int const tile = decline(config_name);
   return dev_units_gemm(act, low, high, units, offsets, out, total_rows, n, k, experts, qtype, workspace, workspace_bytes,
-                        static_cast<cudaStream_t>(stream), "fully-quantized grouped GEMM enqueue");
+                        static_cast<cudaStream_t>(stream), tile, "fully-quantized grouped GEMM enqueue");
 }
 extern "C" int quactlize_ppu_grouped_fully_quantized_dev_v1(uint16_t const* act, uint8_t const* low, uint8_t const* high,
                                                             uint8_t const* units, int const* offsets, uint16_t* out,

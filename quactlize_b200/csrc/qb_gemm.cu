@@ -529,7 +529,7 @@ int enqueue_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
   int const key = d.lo_bits * 10 + d.hi_bits;
   // 256 x 256 CTA tiles (four accumulators = all 512 TMEM columns) for prefill-sized problems; small ones keep 128 x 128
   int const avg_rows = d.experts > 0 ? d.total_rows / d.experts : d.total_rows;
-  bool const big = avg_rows >= 192;
+  bool const big = d.tile == 256 || (d.tile == 0 && avg_rows >= 192);
 #define QB_GEMM_CASE(K, L, H) case K: return d.act_bf16 ? (big ? launch_mixed_gemm<L, H, true, 2, 2>(d, stream) : launch_mixed_gemm<L, H, true, 1, 1>(d, stream)) \
                                                         : (big ? launch_mixed_gemm<L, H, false, 2, 2>(d, stream) : launch_mixed_gemm<L, H, false, 1, 1>(d, stream));
   switch (key) {

@@ -51,6 +51,7 @@ struct GemmDesc {
   void* out;                  // act dtype [total_rows][n]
   int const* offsets;         // cumulative device int [experts+1] (grouped)
   int total_rows, n, k, experts, group_size, lo_bits, hi_bits, code_offset, act_bf16;
+  int tile;                   // 0 = chosen from the problem size, 128 / 256 = that CTA tile (the two compiled tactics)
 };
 int enqueue_mixed_gemm(GemmDesc const& d, cudaStream_t stream);    // 0 ok, 30/33 refused, 41 runtime
 

@@ -69,6 +69,22 @@ def test_argument_refusals_need_no_device():
     assert cfg[0].enable_cuda_kernel and cfg[0].name == b"vecdot_moe"
 
 
+def test_tensor_tactic_inventory():
+    """Two tensor-core tactics are compiled; both are listed as valid for every valid shape and recognised by name."""
+    L = _lib.lib()
+    cfg = (_lib.ConfigV2 * 4)()
+    assert L.quactlize_ppu_list_valid_dense_lowbit_configs_v2(cfg, 4, 64, 4096, 4096, 32, 12) == 2
+    names = [cfg[i].name for i in range(2)]
+    assert names == [b"256x256x64:tcgen05", b"128x128x64:tcgen05"]
+    assert (cfg[0].tile_m, cfg[0].tile_n, cfg[1].tile_m, cfg[1].tile_n) == (256, 256, 128, 128)
+    assert L.quactlize_ppu_list_valid_dense_lowbit_configs_v2(cfg, 4, 64, 4000, 4096, 32, 12) == 0       # n not a tile multiple
+    for name in names:
+        assert L.quactlize_ppu_dense_lowbit_config_valid_v1(64, 4096, 4096, 32, 12, name) == 1
+        assert L.quactlize_ppu_grouped_fully_quantized_config_valid_v1(64, 4096, 4096, 32, 8, 64, 12, name) == 1
+    assert L.quactlize_ppu_dense_lowbit_config_valid_v1(64, 4096, 4096, 32, 12, b"64x64x64:other") == 0
+    assert L.quactlize_ppu_list_configs(None) == 3 and L.quactlize_ppu_list_grouped_configs(None) == 3
+
+
 def _eq(a, b):
     a = a.numpy() if isinstance(a, torch.Tensor) else np.asarray(a)
     b = np.asarray(b)
@@ -123,3 +139,18 @@ def test_shape_contract_errors():
         qb.gguf_prepare_gemv(blocks[:, :100].contiguous(), 8, 512, 12)
     with pytest.raises(RuntimeError):
         qb.gguf_dequantize(blocks, 9)
+
+
+def test_header_is_c_and_a_c_caller_can_load_the_library(tmp_path):
+    """The boundary is a C ABI: a C program that includes the header, dlopens the library and calls host-only entries."""
+    import shutil
+    import subprocess
+    if shutil.which("gcc") is None:
+        pytest.skip("no C compiler")
+    here = os.path.dirname(os.path.abspath(__file__))
+    exe = tmp_path / "c_abi_probe"
+    subprocess.run(["gcc", "-std=c11", "-Wall", "-Werror", "-I", os.path.join(os.path.dirname(here), "include"),
+                    os.path.join(here, "c_abi_probe.c"), "-o", str(exe), "-ldl"], check=True)
+    r = subprocess.run([str(exe), _lib.LIB_PATH], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert r.stdout.startswith("ok 8192 ")
