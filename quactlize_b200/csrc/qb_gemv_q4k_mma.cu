@@ -155,13 +155,18 @@ __global__ void __launch_bounds__(512, 1) q4k_mma_kernel(const __grid_constant__
   uint64_t* mybars = bars + warp * STAGES;
   uint8_t* myring = ring + size_t(warp) * STAGES * kQTile;
   int const b_first = ntiles > 0 ? t0 / bpr : 0, s_first = ntiles > 0 ? t0 % bpr : 0;
-  int is_b = b_first, is_s = s_first;
+  // next tile to request (lane 0 only): addresses and coordinates live in registers and advance by additions
+  int is_s = s_first;
+  int is_row0 = (blockIdx.x + b_first * gridDim.x) * kQRows;
+  int const row_step = gridDim.x * kQRows;
+  uint32_t const bar_a = smem_u32(mybars), ring_issue_a = smem_u32(myring);
+  uint64_t const map_p = reinterpret_cast<uint64_t>(&map_b);
   auto issue = [&](int q) {
-    int const st = q & (STAGES - 1);
-    int const row0 = (blockIdx.x + is_b * gridDim.x) * kQRows;
-    mbar_expect_tx(&mybars[st], kQTile);
-    q_tma3(myring + st * kQTile, &map_b, is_s * kQBlock, row0, e, &mybars[st]);
-    if (++is_s == bpr) { is_s = 0; ++is_b; }
+    uint32_t const st = uint32_t(q) & (STAGES - 1), bar = bar_a + st * 8;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "n"(kQTile) : "memory");
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(ring_issue_a + st * kQTile), "l"(map_p), "r"(bar), "r"(is_s * kQBlock), "r"(is_row0), "r"(e) : "memory");
+    if (++is_s == bpr) { is_s = 0; is_row0 += row_step; }
   };
   if (lane == 0) {
 #pragma unroll

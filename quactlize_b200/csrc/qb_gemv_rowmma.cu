@@ -168,13 +168,18 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, MmaArgs a) {
   uint64_t* mybars = bars + warp * STAGES;
   uint8_t* myring = ring + size_t(warp) * STAGES * TILE;
   int const b_first = ntiles > 0 ? t0 / ns : 0, s_first = ntiles > 0 ? t0 % ns : 0;
-  int is_b = b_first, is_s = s_first;
+  // next tile to request (lane 0 only): addresses and coordinates live in registers and advance by additions
+  int is_s = s_first;
+  int is_row0 = (blockIdx.x + b_first * gridDim.x) * kTRows;
+  int const row_step = gridDim.x * kTRows;
+  uint32_t const bar_a = smem_u32(mybars), ring_issue_a = smem_u32(myring);
+  uint64_t const map_p = reinterpret_cast<uint64_t>(&map_lo);
   auto issue = [&](int q) {
-    int const st = q & (STAGES - 1);
-    int const row0 = (blockIdx.x + is_b * gridDim.x) * kTRows;
-    mbar_expect_tx(&mybars[st], TILE);
-    tma_tile3(myring + st * TILE, &map_lo, is_s * (kTSlice * LO / 8), row0, e, &mybars[st]);
-    if (++is_s == ns) { is_s = 0; ++is_b; }
+    uint32_t const st = uint32_t(q) & (STAGES - 1), bar = bar_a + st * 8;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "n"(TILE) : "memory");
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(ring_issue_a + st * TILE), "l"(map_p), "r"(bar), "r"(is_s * (kTSlice * LO / 8)), "r"(is_row0), "r"(e) : "memory");
+    if (++is_s == ns) { is_s = 0; is_row0 += row_step; }
   };
   if (lane == 0) {
 #pragma unroll

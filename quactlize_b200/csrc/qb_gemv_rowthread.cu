@@ -230,14 +230,21 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
 
   static_assert((STAGES & (STAGES - 1)) == 0, "ring depth is a power of two");
   int const b_first = ntiles > 0 ? t0 / ns : 0, s_first = ntiles > 0 ? t0 % ns : 0;
-  int is_b = b_first, is_s = s_first;                      // (block, slice) of the next tile to request (lane 0 only)
+  // next tile to request (lane 0 only): everything the copy needs is kept in registers and advanced by additions
+  int is_s = s_first;
+  int is_row0 = (blockIdx.x + b_first * gridDim.x) * kRows;
+  int const row_step = gridDim.x * kRows;
+  uint32_t const bar_a = smem_u32(mybars), ring_lo_a = smem_u32(mylo), ring_hi_a = smem_u32(myhi);
+  uint64_t const map_lo_p = reinterpret_cast<uint64_t>(&map_lo), map_hi_p = reinterpret_cast<uint64_t>(&map_hi);
   auto issue = [&](int q) {                                // called with q = 0, 1, 2, ... in order
-    int const st = q & (STAGES - 1);
-    int const row0 = (blockIdx.x + is_b * gridDim.x) * kRows;
-    mbar_expect_tx(&mybars[st], LO_TILE + HI_TILE);
-    tma_tile_3d(mylo + st * LO_TILE, &map_lo, is_s * (kSlice * LO / 8), row0, e, &mybars[st]);
-    if constexpr (HI != 0) tma_tile_3d(myhi + st * HI_TILE, &map_hi, is_s * (kSlice * HI / 8), row0, e, &mybars[st]);
-    if (++is_s == ns) { is_s = 0; ++is_b; }
+    uint32_t const st = uint32_t(q) & (STAGES - 1), bar = bar_a + st * 8;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "n"(LO_TILE + HI_TILE) : "memory");
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(ring_lo_a + st * LO_TILE), "l"(map_lo_p), "r"(bar), "r"(is_s * (kSlice * LO / 8)), "r"(is_row0), "r"(e) : "memory");
+    if constexpr (HI != 0)
+      asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                   ::"r"(ring_hi_a + st * HI_TILE), "l"(map_hi_p), "r"(bar), "r"(is_s * (kSlice * HI / 8)), "r"(is_row0), "r"(e) : "memory");
+    if (++is_s == ns) { is_s = 0; is_row0 += row_step; }
   };
   if (lane == 0) {
 #pragma unroll
@@ -314,14 +321,11 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   constexpr int NSC = MODE == 0 ? NQ : 5;
   uint32_t cur[NSC], nxt[NSC];
   int const gs = d.group_size, kg = MODE == 0 ? k / gs : 0;
-  int f_b = b_first, f_s = s_first;                          // (block, slice) of the next tile to fetch the scale channel for
   int const gshift = 31 - __clz(gs > 0 ? gs : 1);           // group size is a power of two
   uint16_t const* const sp_e = MODE == 0 ? reinterpret_cast<uint16_t const*>(d.scale) + size_t(e) * kg * n : nullptr;
   uint16_t const* const zp_e = (MODE == 0 && d.zero) ? reinterpret_cast<uint16_t const*>(d.zero) + size_t(e) * kg * n : nullptr;
-  auto fetch = [&](uint32_t* dst) {                          // called once per tile, in order
-    int const bi = f_b, s = f_s;
-    if (++f_s == ns) { f_s = 0; ++f_b; }
-    int const row = (blockIdx.x + bi * gridDim.x) * kRows + r;
+  // scale channel of (row, slice s); called once per tile, in order
+  auto fetch = [&](int row, int s, uint32_t* dst) {
 #pragma unroll
     for (int i = 0; i < NSC; ++i) dst[i] = 0u;
     if (row >= n) return;
@@ -346,13 +350,14 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
       }
     }
   };
+  int const row_first = (blockIdx.x + b_first * gridDim.x) * kRows + r;
 #pragma unroll
   for (int i = 0; i < NSC; ++i) nxt[i] = 0u;
-  if (ntiles > 0) fetch(nxt);
+  if (ntiles > 0) fetch(row_first, s_first, nxt);
 
   float const coff = float(d.code_offset);
   bool dead = false;
-  int q = 0, cur_b = b_first, c_b = b_first, c_s = s_first;
+  int q = 0;
   float tot[MR];
 #pragma unroll
   for (int m = 0; m < MR; ++m) tot[m] = 0.f;
@@ -372,14 +377,15 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
       tot[m] = 0.f;
     }
   };
-  for (; q < ntiles; ++q) {
-    int const st = q & (STAGES - 1);
-    int const bi = c_b, s = c_s;
-    if (++c_s == ns) { c_s = 0; ++c_b; }
-    if (bi != cur_b) { flush(cur_b); cur_b = bi; }
+  int row = row_first;                                       // this lane's weight row in the current block
+  for (int bi = b_first, s_begin = s_first; q < ntiles; ++bi, s_begin = 0, row += row_step) {
+   int const s_end = min(ns, s_begin + (ntiles - q));
+   for (int s = s_begin; s < s_end; ++s, ++q) {
+    uint32_t const st = uint32_t(q) & (STAGES - 1);
 #pragma unroll
     for (int i = 0; i < NSC; ++i) cur[i] = nxt[i];
-    if (q + 1 < ntiles) fetch(nxt);
+    if (s + 1 < s_end) fetch(row, s + 1, nxt);               // next slice of this block ...
+    else if (q + 1 < ntiles) fetch(row + row_step, 0, nxt);   // ... or the first slice of the next one
     if (!mbar_wait_bounded(&mybars[st], unsigned(q / STAGES) & 1u, a.status, kWaitStageTimeout)) { dead = true; break; }
     int const pt = s * (kSlice / kPart) + kp;
     uint32_t wl[NWL], wh[NWH];
@@ -420,7 +426,7 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
     }
 #pragma unroll
     for (int m = 0; m < MR; ++m) {
-      if (m >= nrows) continue;                          // uniform for the CTA
+      if (MR > 1 && m >= nrows) continue;                // uniform for the CTA
       float usum[NU];
       uint32_t const xp = xlo_a + uint32_t(m) * xrow + uint32_t(pt) * kPartStride;
       uint32_t const xq = xhi_a + uint32_t(m) * xrow + uint32_t(pt) * kPartStride;
@@ -476,8 +482,10 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
         tot[m] = fmaf(ov[j] + zv[j], sx, tot[m]);
       }
     }
+   }
+   if (dead) break;
+   flush(bi);
   }
-  if (ntiles > 0 && !dead) flush(cur_b);
   if (dead)                                               // let copies already in flight land before the CTA's memory is reused
     for (int i = q + 1; i < ntiles && i < q + STAGES; ++i)
       (void)mbar_wait_bounded(&mybars[i % STAGES], unsigned(i / STAGES) & 1u, nullptr, 0, 250000000ull);
