@@ -52,6 +52,11 @@ __device__ __forceinline__ void tma_tile3(void* dst, CUtensorMap const* map, int
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
                ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return v;
+}
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
@@ -84,7 +89,8 @@ __device__ __forceinline__ uint32_t word_offset(int rr, int w) {
 // LO plane bits; WL distinct words per step across a quad (4, 2 or 1); GQ = min(group size, 256) codes
 template <int LO, int WL, int GQ, int STAGES>
 __global__ void __launch_bounds__(512, 1)
-rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, MmaArgs a) {
+rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_constant__ CUtensorMap map_sc,
+                   const __grid_constant__ CUtensorMap map_zr, MmaArgs a) {
   constexpr int CW = 32 / LO;                         // codes per word
   constexpr int NP = 16 / LO;                         // half2 operands ("patterns") per word
   constexpr int PER = 8 / LO;                         // codes per byte
@@ -95,6 +101,8 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, MmaArgs a) {
   constexpr int NGT = kTSlice / GQ;                   // scale groups per tile (1, 2, 4 or 8)
   constexpr int NGR = NGT > 4 ? NGT / 4 : 1;          // scale registers per row and lane
   constexpr int TILE = kTRows * 32 * LO;
+  // fp16 scale, then zero: [group][16 rows], copied with the tile; each half 128-byte aligned (destination of a tiled copy)
+  constexpr int SC_HALF = NGT * kTRows * 2 < 128 ? 128 : NGT * kTRows * 2, SC_TILE = 2 * SC_HALF;
   constexpr int XPAD = LO == 4 ? 24 : 8;              // skew between activation rows: B-fragment loads spread over the banks
   static_assert(S <= GQ && GQ % S == 0, "the codes of one MMA must lie inside one scale group");
   static_assert((STAGES & (STAGES - 1)) == 0, "ring depth is a power of two");
@@ -151,7 +159,8 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, MmaArgs a) {
   int const nparts = k / kXPart;
   uint32_t const xrow = uint32_t(nparts) * kXPartStride + XPAD;          // bytes of one activation row in pattern order
   uint8_t* ring = smem;                                                  // [W][STAGES][TILE]
-  uint8_t* xpat = ring + size_t(W) * STAGES * TILE;                      // [8][xrow]
+  uint8_t* sc_ring = ring + size_t(W) * STAGES * TILE;                   // [W][STAGES][SC_TILE]
+  uint8_t* xpat = sc_ring + size_t(W) * STAGES * SC_TILE;                // [8][xrow]
   float* sxq = reinterpret_cast<float*>(xpat + size_t(kCols) * xrow);    // [k/GQ][8]
   float* fmv = sxq + (k / GQ) * kCols;                                   // [8] 2^(24-ex) per activation row
   uint16_t* xraw = reinterpret_cast<uint16_t*>(fmv + kCols);             // [k] (prologue only)
@@ -167,6 +176,7 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, MmaArgs a) {
   int const ntiles = t1 - t0;
   uint64_t* mybars = bars + warp * STAGES;
   uint8_t* myring = ring + size_t(warp) * STAGES * TILE;
+  uint8_t* mysc = sc_ring + size_t(warp) * STAGES * SC_TILE;
   int const b_first = ntiles > 0 ? t0 / ns : 0, s_first = ntiles > 0 ? t0 % ns : 0;
   // next tile to request (lane 0 only): addresses and coordinates live in registers and advance by additions
   int is_s = s_first;
@@ -174,9 +184,23 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, MmaArgs a) {
   int const row_step = gridDim.x * kTRows;
   uint32_t const bar_a = smem_u32(mybars), ring_issue_a = smem_u32(myring);
   uint64_t const map_p = reinterpret_cast<uint64_t>(&map_lo);
+  uint64_t const map_sc_p = reinterpret_cast<uint64_t>(&map_sc), map_zr_p = reinterpret_cast<uint64_t>(&map_zr);
+  // the scale channel of a tile (fp16 scale and zero of its 16 rows and 256/gs groups) travels with it on the same mbarrier;
+  // per-lane global loads of the scales queue behind the ring and were the largest stall of this kernel
+  uint32_t const sc_issue_a = smem_u32(mysc);
+  int const gs = d.group_size;
+  int const gshift = 31 - __clz(gs);
+  bool const has_zero = d.zero != nullptr;
+  uint32_t const tx_bytes = TILE + uint32_t(NGT * kTRows * 2) * (has_zero ? 2u : 1u);   // the boxes' bytes, not the padded halves
   auto issue = [&](int q) {
     uint32_t const st = uint32_t(q) & (STAGES - 1), bar = bar_a + st * 8;
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "n"(TILE) : "memory");
+    int const gy = (is_s * kTSlice) >> gshift;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(tx_bytes) : "memory");
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(sc_issue_a + st * SC_TILE), "l"(map_sc_p), "r"(bar), "r"(is_row0), "r"(gy), "r"(e) : "memory");
+    if (has_zero)
+      asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                   ::"r"(sc_issue_a + st * SC_TILE + SC_HALF), "l"(map_zr_p), "r"(bar), "r"(is_row0), "r"(gy), "r"(e) : "memory");
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
                  ::"r"(ring_issue_a + st * TILE), "l"(map_p), "r"(bar), "r"(is_s * (kTSlice * LO / 8)), "r"(is_row0), "r"(e) : "memory");
     if (++is_s == ns) { is_s = 0; is_row0 += row_step; }
@@ -232,41 +256,10 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, MmaArgs a) {
     __syncthreads();                                       // xraw and red are reused by the next row
   }
 
-  // ---- scale channel of one tile, fetched one tile ahead: lane t of a quad holds groups t (and t+4) of rows g and g+8 ----------
-  uint32_t cur[2 * NGR], nxt[2 * NGR];
-  int const gs = d.group_size, kg = k / gs;
-  int const gshift = 31 - __clz(gs);
-  uint16_t const* const sp_e = reinterpret_cast<uint16_t const*>(d.scale) + size_t(e) * kg * n;
-  uint16_t const* const zp_e = d.zero ? reinterpret_cast<uint16_t const*>(d.zero) + size_t(e) * kg * n : nullptr;
-  int f_b = b_first, f_s = s_first;
-  auto fetch = [&](uint32_t* dst) {
-    int const bi = f_b, s = f_s;
-    if (++f_s == ns) { f_s = 0; ++f_b; }
-    int const row = (blockIdx.x + bi * gridDim.x) * kTRows + g;
-#pragma unroll
-    for (int i = 0; i < 2 * NGR; ++i) dst[i] = 0u;
-#pragma unroll
-    for (int u = 0; u < NGR; ++u) {
-      int const jg = t + 4 * u;
-      if (jg >= NGT) continue;
-      uint32_t const grp = uint32_t(s * kTSlice + jg * GQ) >> gshift;
-#pragma unroll
-      for (int hrow = 0; hrow < 2; ++hrow) {
-        int const rr = row + 8 * hrow;
-        if (rr >= n) continue;
-        uint32_t const gi = grp * uint32_t(n) + uint32_t(rr);
-        uint32_t const sv = __ldg(sp_e + gi), zv = zp_e ? uint32_t(__ldg(zp_e + gi)) : 0u;
-        dst[2 * u + hrow] = sv | (zv << 16);
-      }
-    }
-  };
-#pragma unroll
-  for (int i = 0; i < 2 * NGR; ++i) nxt[i] = 0u;
-  if (ntiles > 0) fetch(nxt);
-
   // ---- per-lane constants of the fragment addressing ------------------------------------------------------------------------
   constexpr uint32_t M1 = ((1u << LO) - 1u) * 0x00010001u;
   int const wsel = t / L, lsel = t % L;                      // which word of the step, which share of its patterns
+  uint32_t const sc_a = smem_u32(mysc) + uint32_t(g) * 2;    // this lane's rows g (and g + 8) of the staged scales
   uint32_t const ring_a = smem_u32(myring), xpat_a = smem_u32(xpat) + uint32_t(g) * xrow, sxq_a = smem_u32(sxq) + uint32_t(t) * 8;
   float const coff = float(d.code_offset);
   float totA[4] = {0.f, 0.f, 0.f, 0.f}, totB[4] = {0.f, 0.f, 0.f, 0.f};
@@ -286,12 +279,10 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, MmaArgs a) {
     int const bi = c_b, s = c_s;
     if (++c_s == ns) { c_s = 0; ++c_b; }
     if (bi != cur_b) { flush(cur_b); cur_b = bi; }
-#pragma unroll
-    for (int i = 0; i < 2 * NGR; ++i) cur[i] = nxt[i];
-    if (q + 1 < ntiles) fetch(nxt);
     if (!mbar_wait_bounded(&mybars[st], unsigned(q / STAGES) & 1u, a.status, kWaitStageTimeout)) { dead = true; break; }
     uint32_t const tile_a = ring_a + st * TILE;
     float c[4] = {0.f, 0.f, 0.f, 0.f};
+    uint32_t dep = 0u;
 #pragma unroll
     for (int j = 0; j < NSTEP; ++j) {
       int const w = j * WL + wsel;                           // word of the row's 256 codes this lane reads in this step
@@ -311,8 +302,10 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, MmaArgs a) {
       }
       if (((j + 1) * S) % GQ == 0) {                         // a scale group is complete (compile-time condition)
         int const jg = (j * S) / GQ;
-        uint32_t const raw_lo = __shfl_sync(0xffffffffu, cur[2 * (jg >> 2)], (lane & ~3) | (jg & 3));
-        uint32_t const raw_hi = __shfl_sync(0xffffffffu, cur[2 * (jg >> 2) + 1], (lane & ~3) | (jg & 3));
+        uint32_t const sat = sc_a + st * SC_TILE + jg * (kTRows * 2);
+        uint32_t const raw_lo = lds_u16(sat) | (has_zero ? lds_u16(sat + SC_HALF) << 16 : 0u);
+        uint32_t const raw_hi = lds_u16(sat + 16) | (has_zero ? lds_u16(sat + SC_HALF + 16) << 16 : 0u);
+        dep ^= raw_lo ^ raw_hi;
         float2 const lo = __half22float2(u32_as_h2(raw_lo)), hi = __half22float2(u32_as_h2(raw_hi));   // (scale, zero)
         float2 const sx = lds_f32x2(sxq_a + uint32_t(s * NGT + jg) * (kCols * 4));                     // sums of x, columns 2t, 2t+1
         totA[0] = fmaf(lo.x, c[0], totA[0]); totA[1] = fmaf(lo.x, c[1], totA[1]);
@@ -322,6 +315,10 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, MmaArgs a) {
         totB[2] = fmaf(oz_hi, sx.x, totB[2]); totB[3] = fmaf(oz_hi, sx.y, totB[3]);
         c[0] = c[1] = c[2] = c[3] = 0.f;
       }
+    }
+    {                                                        // the scale loads have returned before the slot is refilled
+      uint32_t sink;
+      asm volatile("mov.u32 %0, %1;" : "=r"(sink) : "r"(dep) : "memory");
     }
     __syncwarp();                                            // every lane's loads of this tile were consumed by its MMAs
     if (lane == 0 && q + STAGES < ntiles) issue(q + STAGES);
@@ -355,6 +352,7 @@ int launch_rowmma(PlaneGemvDesc const& d, cudaStream_t stream) {
   constexpr int TILE = kTRows * 32 * LO;
   constexpr int STAGES = LO == 1 ? 8 : 4;             // 64-128 KB in flight per SM (32 KB for the 1-bit plane)
   constexpr int XPAD = LO == 4 ? 24 : 8;
+  constexpr int SC_TILE = 2 * std::max(128, (kTSlice / GQ) * kTRows * 2);
   auto kern = rowmma_gemv_kernel<LO, WL, GQ, STAGES>;
   // grid rows: one per group of up to 8 activation rows of one expert (ragged: an upper bound, surplus CTAs exit at once)
   int const gy = d.offsets ? std::min(d.m_rows, d.m_rows / kCols + d.experts) : (d.m_rows + kCols - 1) / kCols;
@@ -381,7 +379,7 @@ int launch_rowmma(PlaneGemvDesc const& d, cudaStream_t stream) {
       int const per = std::min(256, (nblocks + p.gx - 1) / p.gx);
       p.gx = (nblocks + per - 1) / per;
       int const nparts = d.k / kXPart;
-      p.smem = 1024 + size_t(16) * STAGES * TILE + size_t(kCols) * (size_t(nparts) * kXPartStride + XPAD) +
+      p.smem = 1024 + size_t(16) * STAGES * (TILE + SC_TILE) + size_t(kCols) * (size_t(nparts) * kXPartStride + XPAD) +
                size_t(d.k / GQ) * kCols * 4 + kCols * 4 + size_t(d.k) * 2 + 16 * 4 + size_t(16) * STAGES * 8 +
                size_t(per + 16) * kTRows * kCols * 4;
       p.rc = p.smem > 227 * 1024 ? 40 : 0;
@@ -391,23 +389,34 @@ int launch_rowmma(PlaneGemvDesc const& d, cudaStream_t stream) {
     p = it->second;
   }
   if (p.rc) return p.rc;
-  struct MKey { void const* lo; int n, k, e; bool operator<(MKey const& o) const {
-    return lo != o.lo ? lo < o.lo : n != o.n ? n < o.n : k != o.k ? k < o.k : e < o.e; } };
-  static std::map<MKey, CUtensorMap> maps;
+  struct MKey { void const* lo; void const* sc; void const* zr; int n, k, e, gs; bool operator<(MKey const& o) const {
+    return lo != o.lo ? lo < o.lo : sc != o.sc ? sc < o.sc : zr != o.zr ? zr < o.zr : n != o.n ? n < o.n : k != o.k ? k < o.k :
+           e != o.e ? e < o.e : gs < o.gs; } };
+  struct Maps { CUtensorMap lo, sc, zr; };
+  static std::map<MKey, Maps> maps;
   static std::mutex mmu;
-  CUtensorMap m;
+  Maps m;
   {
     std::lock_guard<std::mutex> lk(mmu);
-    MKey const key{d.low, d.n, d.k, E};
+    MKey const key{d.low, d.scale, d.zero, d.n, d.k, E, d.group_size};
     auto it = maps.find(key);
     if (it == maps.end()) {
       if (maps.size() > 4096) maps.clear();
-      CUtensorMap nm;
+      Maps nm;
       cuuint64_t const rb = cuuint64_t(d.k) * LO / 8;
       cuuint64_t dims[3] = {rb, cuuint64_t(d.n), cuuint64_t(E)};
       cuuint64_t str[2] = {rb, rb * d.n};
       cuuint32_t box[3] = {cuuint32_t(kTSlice * LO / 8), cuuint32_t(kTRows), 1};
-      if (!tma_make_map(&nm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.low, dims, str, box, tma_row_swizzle(kTSlice * LO / 8))) return kRuntimeError;
+      if (!tma_make_map(&nm.lo, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.low, dims, str, box, tma_row_swizzle(kTSlice * LO / 8))) return kRuntimeError;
+      {                                                     // fp16 [E][k/gs][n]: a box is 16 rows x the groups of one slice
+        cuuint64_t const kg = cuuint64_t(d.k / d.group_size);
+        cuuint64_t sdims[3] = {cuuint64_t(d.n), kg, cuuint64_t(E)};
+        cuuint64_t sstr[2] = {cuuint64_t(d.n) * 2, cuuint64_t(d.n) * 2 * kg};
+        cuuint32_t sbox[3] = {cuuint32_t(kTRows), cuuint32_t(kTSlice / GQ), 1};
+        if (!tma_make_map(&nm.sc, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, d.scale, sdims, sstr, sbox, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
+        nm.zr = nm.sc;
+        if (d.zero && !tma_make_map(&nm.zr, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, d.zero, sdims, sstr, sbox, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
+      }
       it = maps.emplace(key, nm).first;
     }
     m = it->second;
@@ -417,7 +426,7 @@ int launch_rowmma(PlaneGemvDesc const& d, cudaStream_t stream) {
   a.ns = d.k / kTSlice; a.nblocks = (d.n + kTRows - 1) / kTRows;
   a.status = rt_device_status_ptr();
   if (!a.status) return kRuntimeError;
-  kern<<<dim3(p.gx, gy), 512, p.smem, stream>>>(m, a);
+  kern<<<dim3(p.gx, gy), 512, p.smem, stream>>>(m.lo, m.sc, m.zr, a);
   return 0;
 }
 
@@ -425,9 +434,9 @@ int launch_rowmma(PlaneGemvDesc const& d, cudaStream_t stream) {
 
 // 0 launched; 40 = this form does not cover the shape (scale-first planes without a high plane, group size >= 32, n >= 16)
 int enqueue_rowmma_gemv(PlaneGemvDesc const& d, cudaStream_t s) {
-  if (d.scale_mode != 0 || d.hi_bits != 0 || d.k <= 0 || d.k % 256 || d.n < 16) return 40;
+  if (d.scale_mode != 0 || d.hi_bits != 0 || d.k <= 0 || d.k % 256 || d.n < 16 || d.n % 8) return 40;   // scale rows are copied in 16-byte units
   auto aligned = [](void const* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
-  if (!aligned(d.low) || !aligned(d.act)) return 40;
+  if (!aligned(d.low) || !aligned(d.act) || !aligned(d.scale) || (d.zero && !aligned(d.zero))) return 40;
   int const gs = d.group_size;
   if (gs < 32 || (gs & (gs - 1)) || d.k % gs) return 40;
   int const gq = gs >= 256 ? 256 : gs;

@@ -70,6 +70,18 @@ __device__ __forceinline__ uint4 lds128_a(uint32_t addr) {
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
 }
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return v;
+}
+// bytes one ring stage keeps for a tile's scale channel: fp16 scale and zero of 8 rows x up to 4 * NQ groups (two halves),
+// or the packed units of 8 rows
+template <int MODE, int QT, int NQ>
+constexpr int sc_tile_bytes() {
+  if constexpr (MODE == 0) return NQ <= 2 ? 256 : NQ * 128;      // each half starts 128-byte aligned, as a tiled copy's destination must
+  else return kRows * kq::Unit<QT>::kUnitTotal;                  // an untiled bulk copy needs 16-byte alignment only
+}
 __device__ __forceinline__ float lds_f32(uint32_t addr) {
   float v;
   asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
@@ -130,7 +142,8 @@ __device__ __forceinline__ uint32_t bits_at(uint32_t const* u, int bit) {
 // MR activation rows share every weight tile (1, or up to 4 rows of one expert)
 template <int LO, int HI, int MODE, int QT, int NQ, int STAGES, int MR>
 __global__ void __launch_bounds__(512, 1)
-rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_constant__ CUtensorMap map_hi, RtArgs a) {
+rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_constant__ CUtensorMap map_hi,
+                      const __grid_constant__ CUtensorMap map_sc, const __grid_constant__ CUtensorMap map_zr, RtArgs a) {
   constexpr int Q = kPart / NQ;                       // codes per run: one scale group (or 64 codes of a wider one)
   constexpr int NWL = kPart * LO / 32;                // low-plane words per part: 8 / 4 / 2
   constexpr int NWH = HI ? kPart * HI / 32 : 1;       // high-plane words per part: 4 / 2
@@ -139,6 +152,7 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   constexpr int U = Q < 32 ? Q : 32;                  // codes per fp16 accumulation run (then fp32)
   constexpr int NU = kPart / U;
   constexpr int LO_TILE = kRows * 32 * LO, HI_TILE = HI ? kRows * 32 * HI : 0;
+  constexpr int SC_TILE = sc_tile_bytes<MODE, QT, NQ>(), SC_HALF = SC_TILE / 2;   // scale channel of one tile, copied with it
   static_assert(CWL <= U, "a low-plane word must not straddle accumulation runs");
   constexpr bool kCrossHi = HI && CWH > U;            // a high word spans two runs (1-bit plane, 16-code groups)
   static_assert(!kCrossHi || CWH == 2 * U, "a high-plane word may span at most two runs");
@@ -207,7 +221,8 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   uint8_t* lo_ring = smem;                                              // [W][STAGES][LO_TILE]
   uint8_t* hi_ring = lo_ring + size_t(W) * STAGES * LO_TILE;             // [W][STAGES][HI_TILE]
   uint32_t const xrow = uint32_t(nparts) * kPartStride;                  // bytes of one activation row in pattern order
-  uint8_t* xlo = hi_ring + size_t(W) * STAGES * HI_TILE;                 // [MR][nparts][kPartStride]
+  uint8_t* sc_ring = hi_ring + size_t(W) * STAGES * HI_TILE;             // [W][STAGES][SC_TILE]
+  uint8_t* xlo = sc_ring + size_t(W) * STAGES * SC_TILE;                 // [MR][nparts][kPartStride]
   uint8_t* xhi = xlo + size_t(MR) * xrow;                                // same, if HI
   float* sxq = reinterpret_cast<float*>(xhi + (HI ? size_t(MR) * xrow : 0));   // [MR][k/Q]
   uint16_t* xraw = reinterpret_cast<uint16_t*>(sxq + MR * (k / Q));      // [k] raw activations (prologue only, one row at a time)
@@ -227,6 +242,7 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   uint64_t* mybars = bars + warp * STAGES;
   uint8_t* mylo = lo_ring + size_t(warp) * STAGES * LO_TILE;
   uint8_t* myhi = hi_ring + size_t(warp) * STAGES * HI_TILE;
+  uint8_t* mysc = sc_ring + size_t(warp) * STAGES * SC_TILE;
 
   static_assert((STAGES & (STAGES - 1)) == 0, "ring depth is a power of two");
   int const b_first = ntiles > 0 ? t0 / ns : 0, s_first = ntiles > 0 ? t0 % ns : 0;
@@ -234,11 +250,34 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   int is_s = s_first;
   int is_row0 = (blockIdx.x + b_first * gridDim.x) * kRows;
   int const row_step = gridDim.x * kRows;
-  uint32_t const bar_a = smem_u32(mybars), ring_lo_a = smem_u32(mylo), ring_hi_a = smem_u32(myhi);
+  uint32_t const bar_a = smem_u32(mybars), ring_lo_a = smem_u32(mylo), ring_hi_a = smem_u32(myhi), ring_sc_a = smem_u32(mysc);
   uint64_t const map_lo_p = reinterpret_cast<uint64_t>(&map_lo), map_hi_p = reinterpret_cast<uint64_t>(&map_hi);
+  uint64_t const map_sc_p = reinterpret_cast<uint64_t>(&map_sc), map_zr_p = reinterpret_cast<uint64_t>(&map_zr);
+  // The scale channel of a tile travels with it, on the same mbarrier: the scale (and zero) values of the tile's 8 rows
+  // and its 256/gs groups as one box of each fp16 plane, or the 8 rows' packed units as one contiguous bulk copy.  (A
+  // per-lane global load of the scales, even one tile ahead, cost 40% of the kernel's time: it queues behind the ring.)
+  int const gs = d.group_size;
+  int const gshift = 31 - __clz(gs > 0 ? gs : 1);           // group size is a power of two
+  bool const has_zero = MODE == 0 && d.zero != nullptr;
+  using UnitT = kq::Unit<(MODE == 1 ? QT : 12)>;
+  int const sc_groups = MODE == 0 ? max(1, kSlice >> gshift) : 0;
+  uint32_t const tx_bytes = LO_TILE + HI_TILE + (MODE == 0 ? uint32_t(sc_groups) * 16u * (has_zero ? 2u : 1u) : uint32_t(kRows * UnitT::kUnitTotal));
+  uint8_t const* const un_e = MODE == 1 ? d.units + size_t(e) * ((k / 256) / UnitT::kSbPerUnit) * n * UnitT::kUnitTotal : nullptr;
   auto issue = [&](int q) {                                // called with q = 0, 1, 2, ... in order
     uint32_t const st = uint32_t(q) & (STAGES - 1), bar = bar_a + st * 8;
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "n"(LO_TILE + HI_TILE) : "memory");
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(tx_bytes) : "memory");
+    if constexpr (MODE == 0) {
+      int const gy = (is_s * kSlice) >> gshift;
+      asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                   ::"r"(ring_sc_a + st * SC_TILE), "l"(map_sc_p), "r"(bar), "r"(is_row0), "r"(gy), "r"(e) : "memory");
+      if (has_zero)
+        asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                     ::"r"(ring_sc_a + st * SC_TILE + SC_HALF), "l"(map_zr_p), "r"(bar), "r"(is_row0), "r"(gy), "r"(e) : "memory");
+    } else {
+      uint8_t const* src = un_e + (size_t(is_s / UnitT::kSbPerUnit) * n + is_row0) * UnitT::kUnitTotal;
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(ring_sc_a + st * SC_TILE), "l"(src), "n"(kRows * UnitT::kUnitTotal), "r"(bar) : "memory");
+    }
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
                  ::"r"(ring_lo_a + st * LO_TILE), "l"(map_lo_p), "r"(bar), "r"(is_s * (kSlice * LO / 8)), "r"(is_row0), "r"(e) : "memory");
     if constexpr (HI != 0)
@@ -317,43 +356,16 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
     __syncthreads();                                       // xraw and red are reused by the next row
   }
 
-  // ---- scale channel of one tile, fetched one tile ahead -----------------------------------------------------------------
+  // ---- where this lane finds its runs' scales inside the staged scale channel (fixed per lane) -----------------------------
+  uint32_t sc_off[MODE == 0 ? NQ : 1];
+  if constexpr (MODE == 0) {
+#pragma unroll
+    for (int j = 0; j < NQ; ++j) sc_off[j] = uint32_t(gs <= kSlice ? (kp * kPart + j * Q) >> gshift : 0) * 16u + uint32_t(r) * 2u;
+  } else {
+    sc_off[0] = uint32_t(r) * UnitT::kUnitTotal;
+  }
   constexpr int NSC = MODE == 0 ? NQ : 5;
-  uint32_t cur[NSC], nxt[NSC];
-  int const gs = d.group_size, kg = MODE == 0 ? k / gs : 0;
-  int const gshift = 31 - __clz(gs > 0 ? gs : 1);           // group size is a power of two
-  uint16_t const* const sp_e = MODE == 0 ? reinterpret_cast<uint16_t const*>(d.scale) + size_t(e) * kg * n : nullptr;
-  uint16_t const* const zp_e = (MODE == 0 && d.zero) ? reinterpret_cast<uint16_t const*>(d.zero) + size_t(e) * kg * n : nullptr;
-  // scale channel of (row, slice s); called once per tile, in order
-  auto fetch = [&](int row, int s, uint32_t* dst) {
-#pragma unroll
-    for (int i = 0; i < NSC; ++i) dst[i] = 0u;
-    if (row >= n) return;
-    if constexpr (MODE == 0) {
-      int const k0 = s * kSlice + kp * kPart;
-#pragma unroll
-      for (int j = 0; j < NQ; ++j) {
-        uint32_t const gi = uint32_t((k0 + j * Q) >> gshift) * uint32_t(n) + uint32_t(row);   // < 2^32: one expert's plane
-        uint32_t const sv = __ldg(sp_e + gi), zv = zp_e ? uint32_t(__ldg(zp_e + gi)) : 0u;
-        dst[j] = sv | (zv << 16);
-      }
-    } else {
-      using UU = kq::Unit<QT>;
-      int const nu = (k / 256) / UU::kSbPerUnit;
-      uint16_t const* u16 = reinterpret_cast<uint16_t const*>(
-          d.units + ((size_t(e) * nu + s / UU::kSbPerUnit) * n + row) * UU::kUnitTotal + (s % UU::kSbPerUnit) * UU::kSbBytes);
-#pragma unroll
-      for (int i = 0; i < (UU::kSbBytes + 3) / 4; ++i) {
-        uint32_t const lo16 = __ldg(u16 + 2 * i);
-        uint32_t const hi16 = (4 * i + 2 < UU::kSbBytes) ? uint32_t(__ldg(u16 + 2 * i + 1)) : 0u;
-        dst[i] = lo16 | (hi16 << 16);
-      }
-    }
-  };
-  int const row_first = (blockIdx.x + b_first * gridDim.x) * kRows + r;
-#pragma unroll
-  for (int i = 0; i < NSC; ++i) nxt[i] = 0u;
-  if (ntiles > 0) fetch(row_first, s_first, nxt);
+  uint32_t const sc_a = smem_u32(mysc);
 
   float const coff = float(d.code_offset);
   bool dead = false;
@@ -377,24 +389,39 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
       tot[m] = 0.f;
     }
   };
-  int row = row_first;                                       // this lane's weight row in the current block
-  for (int bi = b_first, s_begin = s_first; q < ntiles; ++bi, s_begin = 0, row += row_step) {
+  for (int bi = b_first, s_begin = s_first; q < ntiles; ++bi, s_begin = 0) {
    int const s_end = min(ns, s_begin + (ntiles - q));
    for (int s = s_begin; s < s_end; ++s, ++q) {
     uint32_t const st = uint32_t(q) & (STAGES - 1);
-#pragma unroll
-    for (int i = 0; i < NSC; ++i) cur[i] = nxt[i];
-    if (s + 1 < s_end) fetch(row, s + 1, nxt);               // next slice of this block ...
-    else if (q + 1 < ntiles) fetch(row + row_step, 0, nxt);   // ... or the first slice of the next one
     if (!mbar_wait_bounded(&mybars[st], unsigned(q / STAGES) & 1u, a.status, kWaitStageTimeout)) { dead = true; break; }
     int const pt = s * (kSlice / kPart) + kp;
     uint32_t wl[NWL], wh[NWH];
     load_part<LO>(lo_a + st * LO_TILE, offl, wl);
     if constexpr (HI != 0) load_part<(HI ? HI : 1)>(hi_a + st * HI_TILE, offh, wh);
+    uint32_t cur[NSC];                                       // MODE 0: scale | zero << 16 per run; MODE 1: the superblock's scale bytes
+    if constexpr (MODE == 0) {
+#pragma unroll
+      for (int j = 0; j < NQ; ++j) {
+        uint32_t const at = sc_a + st * SC_TILE + sc_off[j];
+        cur[j] = lds_u16(at) | (has_zero ? lds_u16(at + SC_HALF) << 16 : 0u);
+      }
+    } else {
+      uint32_t const at = sc_a + st * SC_TILE + sc_off[0] + uint32_t(s % UnitT::kSbPerUnit) * UnitT::kSbBytes;
+#pragma unroll
+      for (int i = 0; i < NSC; ++i) cur[i] = 0u;
+#pragma unroll
+      for (int i = 0; i < (UnitT::kSbBytes + 3) / 4; ++i) {
+        uint32_t const lo16 = lds_u16(at + 4 * i);
+        uint32_t const hi16 = (4 * i + 2 < UnitT::kSbBytes) ? lds_u16(at + 4 * i + 2) : 0u;
+        cur[i] = lo16 | (hi16 << 16);
+      }
+    }
     // Once the loads above have returned, the slot can be refilled while the rows are multiplied.  The mov reads one word of
     // every load instruction, so it cannot issue before they have completed for the whole warp; the copy is issued after it.
     {
       uint32_t dep = wl[0] ^ wl[NWL - 1] ^ (HI ? wh[0] : 0u), sink;
+#pragma unroll
+      for (int i = 0; i < (MODE == 0 ? NQ : (UnitT::kSbBytes + 3) / 4); ++i) dep ^= cur[i];
       asm volatile("mov.u32 %0, %1;" : "=r"(sink) : "r"(dep) : "memory");
       __syncwarp();
       if (lane == 0 && q + STAGES < ntiles) issue(q + STAGES);
@@ -508,13 +535,14 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
 }
 
 struct RtPlan { int gx, rc; size_t smem; };
-struct RtMaps { CUtensorMap lo, hi; };
+struct RtMaps { CUtensorMap lo, hi, sc, zr; };
 
 template <int LO, int HI, int MODE, int QT, int NQ, int MR>
 int launch_rowthread_mr(PlaneGemvDesc const& d, cudaStream_t stream) {
   constexpr int STAGES = (LO + HI >= 5) ? 4 : 8;     // a power of two; 64-96 KB in flight per SM for the wide tiles
   constexpr int Q = kPart / NQ;
   constexpr int LO_TILE = kRows * 32 * LO, HI_TILE = HI ? kRows * 32 * HI : 0;
+  constexpr int SC_TILE = sc_tile_bytes<MODE, QT, NQ>();
   auto kern = rowthread_gemv_kernel<LO, HI, MODE, QT, NQ, STAGES, MR>;
   // grid rows: one per group of up to MR activation rows of one expert (ragged: an upper bound, surplus CTAs exit at once)
   int const gy = MR == 1 ? d.m_rows : (d.offsets ? std::min(d.m_rows, d.m_rows / MR + d.experts) : (d.m_rows + MR - 1) / MR);
@@ -540,7 +568,7 @@ int launch_rowthread_mr(PlaneGemvDesc const& d, cudaStream_t stream) {
       int per = std::min(512, (nblocks + p.gx - 1) / p.gx);            // blocks per CTA, evened; bounded by the partial-sum table
       p.gx = (nblocks + per - 1) / per;
       int const nparts = d.k / kPart;
-      p.smem = 1024 + size_t(16) * STAGES * (LO_TILE + HI_TILE) + size_t(MR) * nparts * kPartStride * (HI ? 2 : 1) +
+      p.smem = 1024 + size_t(16) * STAGES * (LO_TILE + HI_TILE + SC_TILE) + size_t(MR) * nparts * kPartStride * (HI ? 2 : 1) +
                size_t(MR) * (d.k / Q) * 4 + size_t(d.k) * 2 + 16 * 4 + size_t(16) * STAGES * 8 + size_t(per + 16) * MR * kRows * 4;
       p.rc = p.smem > 227 * 1024 ? 40 : 0;
       // one ceiling for every shape of this instantiation: plans of other shapes are cached and never set it again
@@ -554,14 +582,15 @@ int launch_rowthread_mr(PlaneGemvDesc const& d, cudaStream_t stream) {
     return p.rc;
   }
   // ---- tensor maps: cached per plane pointer -------------------------------------------------------------------------------
-  struct MKey { void const* lo; void const* hi; int n, k, e; bool operator<(MKey const& o) const {
-    return lo != o.lo ? lo < o.lo : hi != o.hi ? hi < o.hi : n != o.n ? n < o.n : k != o.k ? k < o.k : e < o.e; } };
+  struct MKey { void const* lo; void const* hi; void const* sc; void const* zr; int n, k, e, gs; bool operator<(MKey const& o) const {
+    return lo != o.lo ? lo < o.lo : hi != o.hi ? hi < o.hi : sc != o.sc ? sc < o.sc : zr != o.zr ? zr < o.zr :
+           n != o.n ? n < o.n : k != o.k ? k < o.k : e != o.e ? e < o.e : gs < o.gs; } };
   static std::map<MKey, RtMaps> maps;
   static std::mutex mmu;
   RtMaps m;
   {
     std::lock_guard<std::mutex> lk(mmu);
-    MKey const key{d.low, HI ? d.high : nullptr, d.n, d.k, E};
+    MKey const key{d.low, HI ? d.high : nullptr, MODE == 0 ? d.scale : nullptr, MODE == 0 ? d.zero : nullptr, d.n, d.k, E, MODE == 0 ? d.group_size : 0};
     auto it = maps.find(key);
     if (it == maps.end()) {
       if (maps.size() > 4096) maps.clear();
@@ -582,6 +611,15 @@ int launch_rowthread_mr(PlaneGemvDesc const& d, cudaStream_t stream) {
       } else {
         nm.hi = nm.lo;
       }
+      nm.sc = nm.lo; nm.zr = nm.lo;
+      if constexpr (MODE == 0) {                            // fp16 [E][k/gs][n]: a box is 8 rows x the groups of one slice
+        cuuint64_t const kg = cuuint64_t(d.k / d.group_size);
+        cuuint64_t dims[3] = {cuuint64_t(d.n), kg, cuuint64_t(E)};
+        cuuint64_t str[2] = {cuuint64_t(d.n) * 2, cuuint64_t(d.n) * 2 * kg};
+        cuuint32_t box[3] = {cuuint32_t(kRows), cuuint32_t(std::max(1, kSlice / d.group_size)), 1};
+        if (!tma_make_map(&nm.sc, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, d.scale, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
+        if (d.zero && !tma_make_map(&nm.zr, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, d.zero, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
+      }
       it = maps.emplace(key, nm).first;
     }
     m = it->second;
@@ -591,7 +629,7 @@ int launch_rowthread_mr(PlaneGemvDesc const& d, cudaStream_t stream) {
   a.ns = d.k / kSlice; a.nblocks = (d.n + kRows - 1) / kRows;
   a.status = rt_device_status_ptr();
   if (!a.status) return kRuntimeError;
-  kern<<<dim3(p.gx, gy), 512, p.smem, stream>>>(m.lo, m.hi, a);
+  kern<<<dim3(p.gx, gy), 512, p.smem, stream>>>(m.lo, m.hi, m.sc, m.zr, a);
   return 0;
 }
 
@@ -614,9 +652,10 @@ int enqueue_rowthread_gemv(PlaneGemvDesc const& d, cudaStream_t s) {
   if (std::getenv("QUACTLIZE_B200_DEBUG"))
     std::fprintf(stderr, "[quactlize_b200] row-thread GEMV n=%d k=%d rows=%d experts=%d max_rows=%d bits=%d+%d gs=%d mode=%d act=%p low=%p\n",
                  d.n, d.k, d.m_rows, d.experts, d.max_rows, d.lo_bits, d.hi_bits, d.group_size, d.scale_mode, d.act, (void const*)d.low);
-  if (d.k <= 0 || d.k % 256 || d.n < 8) return 40;
+  if (d.k <= 0 || d.k % 256 || d.n < 8 || d.n % 8) return 40;    // the scale channel is copied in 16-byte runs of 8 rows
   auto aligned = [](void const* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   if (!aligned(d.low) || (d.hi_bits && !aligned(d.high)) || !aligned(d.act)) return 40;
+  if (d.scale_mode == 1 ? !aligned(d.units) : (!aligned(d.scale) || (d.zero && !aligned(d.zero)))) return 40;
   if (d.scale_mode == 1) {
     switch (d.qtype) {
       case 10: return launch_rowthread<2, 0, 1, 10, 4>(d, s);
