@@ -160,7 +160,9 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   PlaneGemvDesc const& d = a.d;
   extern __shared__ uint8_t smem_dyn[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
-  int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the warp index is broadcast from lane 0: the compiler then keeps what derives from it (tile counts, ring and barrier
+  // addresses, copy coordinates) in uniform registers and the per-tile bookkeeping off the vector pipes
+  int const warp = __shfl_sync(0xffffffffu, int(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   int const kp = lane >> 3, r = lane & 7;
 
   // ---- which activation rows / expert ---------------------------------------------------------------------------------
