@@ -136,6 +136,7 @@ __global__ void __launch_bounds__(512, 1) q4k_mma_kernel(const __grid_constant__
     nrows = min(cpg, a.m_rows - arow);
     if (nrows <= 0) return;
   }
+  e = __shfl_sync(0xffffffffu, e, 0);                                    // uniform for the compiler too (it was read from shared memory)
   int const n = a.n, bpr = a.bpr, k = bpr * 256;
 
   // ---- shared memory carve-up -----------------------------------------------------------------------------------------
@@ -163,11 +164,14 @@ __global__ void __launch_bounds__(512, 1) q4k_mma_kernel(const __grid_constant__
   int const row_step = gridDim.x * kQRows;
   uint32_t const bar_a = smem_u32(mybars), ring_issue_a = smem_u32(myring);
   uint64_t const map_p = reinterpret_cast<uint64_t>(&map_b);
+  // called with q = 0, 1, 2, ... in order; every lane keeps the (uniform) bookkeeping, lane 0 issues the copies
   auto issue = [&](int q) {
     uint32_t const st = uint32_t(q) & (STAGES - 1), bar = bar_a + st * 8;
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "n"(kQTile) : "memory");
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-                 ::"r"(ring_issue_a + st * kQTile), "l"(map_p), "r"(bar), "r"(is_s * kQBlock), "r"(is_row0), "r"(e) : "memory");
+    if (lane == 0) {
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "n"(kQTile) : "memory");
+      asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                   ::"r"(ring_issue_a + st * kQTile), "l"(map_p), "r"(bar), "r"(is_s * kQBlock), "r"(is_row0), "r"(e) : "memory");
+    }
     if (++is_s == bpr) { is_s = 0; is_row0 += row_step; }
   };
   if (lane == 0) {
@@ -175,8 +179,8 @@ __global__ void __launch_bounds__(512, 1) q4k_mma_kernel(const __grid_constant__
     for (int s = 0; s < STAGES; ++s) mbar_init(&mybars[s], 1);
     mbar_init_fence();
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    for (int q = 0; q < STAGES && q < ntiles; ++q) issue(q);
   }
+  for (int q = 0; q < STAGES && q < ntiles; ++q) issue(q);   // the weight stream starts before the activations are ready
   for (int i = threadIdx.x; i < (nb_c + 16) * kQRows * kQCols; i += blockDim.x) part[i] = 0.f;
 
   // ---- CTA prologue: activations into fragment order -------------------------------------------------------------------------
@@ -275,7 +279,7 @@ __global__ void __launch_bounds__(512, 1) q4k_mma_kernel(const __grid_constant__
       }
     }
     __syncwarp();                                                         // every lane's loads of this tile fed its MMAs
-    if (lane == 0 && q + STAGES < ntiles) issue(q + STAGES);
+    if (q + STAGES < ntiles) issue(q + STAGES);
   }
   if (ntiles > 0 && !dead) flush(cur_b);
   if (dead)

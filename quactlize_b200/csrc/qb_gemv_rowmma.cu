@@ -154,6 +154,7 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
     nrows = min(kCols, d.m_rows - arow);
     if (nrows <= 0) return;
   }
+  e = __shfl_sync(0xffffffffu, e, 0);                 // uniform for the compiler too (it was read from shared memory)
   int const k = d.k, n = d.n;
 
   // ---- shared memory carve-up -----------------------------------------------------------------------------------------
@@ -194,17 +195,20 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
   int const gshift = 31 - __clz(gs);
   bool const has_zero = d.zero != nullptr;
   uint32_t const tx_bytes = TILE + uint32_t(NGT * kTRows * 2) * (has_zero ? 2u : 1u);   // the boxes' bytes, not the padded halves
+  // called with q = 0, 1, 2, ... in order; every lane keeps the (uniform) bookkeeping, lane 0 issues the copies
   auto issue = [&](int q) {
     uint32_t const st = uint32_t(q) & (STAGES - 1), bar = bar_a + st * 8;
     int const gy = (is_s * kTSlice) >> gshift;
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(tx_bytes) : "memory");
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-                 ::"r"(sc_issue_a + st * SC_TILE), "l"(map_sc_p), "r"(bar), "r"(is_row0), "r"(gy), "r"(e) : "memory");
-    if (has_zero)
+    if (lane == 0) {
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(tx_bytes) : "memory");
       asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-                   ::"r"(sc_issue_a + st * SC_TILE + SC_HALF), "l"(map_zr_p), "r"(bar), "r"(is_row0), "r"(gy), "r"(e) : "memory");
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-                 ::"r"(ring_issue_a + st * TILE), "l"(map_p), "r"(bar), "r"(is_s * (kTSlice * LO / 8)), "r"(is_row0), "r"(e) : "memory");
+                   ::"r"(sc_issue_a + st * SC_TILE), "l"(map_sc_p), "r"(bar), "r"(is_row0), "r"(gy), "r"(e) : "memory");
+      if (has_zero)
+        asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                     ::"r"(sc_issue_a + st * SC_TILE + SC_HALF), "l"(map_zr_p), "r"(bar), "r"(is_row0), "r"(gy), "r"(e) : "memory");
+      asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                   ::"r"(ring_issue_a + st * TILE), "l"(map_p), "r"(bar), "r"(is_s * (kTSlice * LO / 8)), "r"(is_row0), "r"(e) : "memory");
+    }
     if (++is_s == ns) { is_s = 0; is_row0 += row_step; }
   };
   if (lane == 0) {
@@ -212,8 +216,8 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
     for (int s = 0; s < STAGES; ++s) mbar_init(&mybars[s], 1);
     mbar_init_fence();
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    for (int q = 0; q < STAGES && q < ntiles; ++q) issue(q);
   }
+  for (int q = 0; q < STAGES && q < ntiles; ++q) issue(q);   // the weight stream starts before the activations are ready
   for (int i = threadIdx.x; i < (nb_c + 16) * kTRows * kCols; i += blockDim.x) part[i] = 0.f;
 
   // ---- CTA prologue: every activation row of the group into pattern order --------------------------------------------------
@@ -323,7 +327,7 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
       asm volatile("mov.u32 %0, %1;" : "=r"(sink) : "r"(dep) : "memory");
     }
     __syncwarp();                                            // every lane's loads of this tile were consumed by its MMAs
-    if (lane == 0 && q + STAGES < ntiles) issue(q + STAGES);
+    if (q + STAGES < ntiles) issue(q + STAGES);
   }
   if (ntiles > 0 && !dead) flush(cur_b);
   if (dead)                                                  // let copies already in flight land before the CTA's memory is reused

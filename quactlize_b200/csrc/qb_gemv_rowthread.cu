@@ -170,6 +170,9 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   // looks up in the cumulative offsets (one probe per thread).  MR > 1, ragged: group y of the list "ceil(rows_e / MR)
   // groups per expert, in expert order", located by a block-wide scan of the per-expert group counts.
   int e = 0, arow = 0, nrows = 1;
+  // Under programmatic dependent launch the activations (and a router's offsets) may be the preceding kernel's output:
+  // nothing of them is read before this wait.  Without the launch attribute it returns at once.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (d.offsets) {
     volatile int* sh = reinterpret_cast<volatile int*>(smem);            // ring space, not yet in use
     if (threadIdx.x < 4) sh[threadIdx.x] = -1;
@@ -215,6 +218,7 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
     nrows = min(MR, d.m_rows - arow);
     if (nrows <= 0) return;
   }
+  e = __shfl_sync(0xffffffffu, e, 0);                 // uniform for the compiler too (it was read from shared memory)
   int const k = d.k, n = d.n;
 
   // ---- shared memory carve-up -----------------------------------------------------------------------------------------
@@ -265,35 +269,51 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   int const sc_groups = MODE == 0 ? max(1, kSlice >> gshift) : 0;
   uint32_t const tx_bytes = LO_TILE + HI_TILE + (MODE == 0 ? uint32_t(sc_groups) * 16u * (has_zero ? 2u : 1u) : uint32_t(kRows * UnitT::kUnitTotal));
   uint8_t const* const un_e = MODE == 1 ? d.units + size_t(e) * ((k / 256) / UnitT::kSbPerUnit) * n * UnitT::kUnitTotal : nullptr;
-  auto issue = [&](int q) {                                // called with q = 0, 1, 2, ... in order
+  // called with q = 0, 1, 2, ... in order; every lane keeps the (uniform) bookkeeping, lane 0 issues the copies
+  auto issue = [&](int q) {
     uint32_t const st = uint32_t(q) & (STAGES - 1), bar = bar_a + st * 8;
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(tx_bytes) : "memory");
-    if constexpr (MODE == 0) {
-      int const gy = (is_s * kSlice) >> gshift;
-      asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-                   ::"r"(ring_sc_a + st * SC_TILE), "l"(map_sc_p), "r"(bar), "r"(is_row0), "r"(gy), "r"(e) : "memory");
-      if (has_zero)
+    int const gy = MODE == 0 ? (is_s * kSlice) >> gshift : 0;
+    if (lane == 0) {
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(tx_bytes) : "memory");
+      if constexpr (MODE == 0) {
         asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-                     ::"r"(ring_sc_a + st * SC_TILE + SC_HALF), "l"(map_zr_p), "r"(bar), "r"(is_row0), "r"(gy), "r"(e) : "memory");
-    } else {
-      uint8_t const* src = un_e + (size_t(is_s / UnitT::kSbPerUnit) * n + is_row0) * UnitT::kUnitTotal;
-      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                   ::"r"(ring_sc_a + st * SC_TILE), "l"(src), "n"(kRows * UnitT::kUnitTotal), "r"(bar) : "memory");
-    }
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-                 ::"r"(ring_lo_a + st * LO_TILE), "l"(map_lo_p), "r"(bar), "r"(is_s * (kSlice * LO / 8)), "r"(is_row0), "r"(e) : "memory");
-    if constexpr (HI != 0)
+                     ::"r"(ring_sc_a + st * SC_TILE), "l"(map_sc_p), "r"(bar), "r"(is_row0), "r"(gy), "r"(e) : "memory");
+        if (has_zero)
+          asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                       ::"r"(ring_sc_a + st * SC_TILE + SC_HALF), "l"(map_zr_p), "r"(bar), "r"(is_row0), "r"(gy), "r"(e) : "memory");
+      } else {
+        uint8_t const* src = un_e + (size_t(is_s / UnitT::kSbPerUnit) * n + is_row0) * UnitT::kUnitTotal;
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(ring_sc_a + st * SC_TILE), "l"(src), "n"(kRows * UnitT::kUnitTotal), "r"(bar) : "memory");
+      }
       asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-                   ::"r"(ring_hi_a + st * HI_TILE), "l"(map_hi_p), "r"(bar), "r"(is_s * (kSlice * HI / 8)), "r"(is_row0), "r"(e) : "memory");
+                   ::"r"(ring_lo_a + st * LO_TILE), "l"(map_lo_p), "r"(bar), "r"(is_s * (kSlice * LO / 8)), "r"(is_row0), "r"(e) : "memory");
+      if constexpr (HI != 0)
+        asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                     ::"r"(ring_hi_a + st * HI_TILE), "l"(map_hi_p), "r"(bar), "r"(is_s * (kSlice * HI / 8)), "r"(is_row0), "r"(e) : "memory");
+    }
     if (++is_s == ns) { is_s = 0; is_row0 += row_step; }
   };
+  // The first activation row is requested BEFORE the weight stream: a load issued after it queues behind the ring's
+  // copies (128 KB per SM) and delays the prologue by a microsecond.
+  constexpr int kPre = 4;                                   // 16-byte pieces per thread held in registers: K <= 16384 is covered
+  uint4 pre[kPre];
+  {
+    uint16_t const* x0 = reinterpret_cast<uint16_t const*>(d.act) + size_t(arow) * k;
+#pragma unroll
+    for (int j = 0; j < kPre; ++j) {
+      int const i = (int(threadIdx.x) + j * 512) * 8;
+      pre[j] = i < k ? __ldg(reinterpret_cast<uint4 const*>(x0 + i)) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) mbar_init(&mybars[s], 1);
     mbar_init_fence();
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    for (int q = 0; q < STAGES && q < ntiles; ++q) issue(q);          // the weight stream starts before the activations are ready
   }
+  for (int q = 0; q < STAGES && q < ntiles; ++q) issue(q);   // the weight stream starts before the activations are converted
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   for (int i = threadIdx.x; i < (nb_c + 16) * MR * kRows; i += blockDim.x) part[i] = 0.f;
 
   // ---- CTA prologue: activations into pattern order, one activation row at a time ---------------------------------------
@@ -306,8 +326,7 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
     // consecutive 8-element pieces, so a run is Q/8 neighbouring lanes)
     size_t const xoff = size_t(arow + m) * k;
     float mx = 0.f;
-    for (int i = threadIdx.x * 8; i < k; i += blockDim.x * 8) {          // k % 256 == 0: whole warps in or out
-      uint4 const v = __ldg(reinterpret_cast<uint4 const*>(reinterpret_cast<uint16_t const*>(d.act) + xoff + i));
+    auto piece = [&](int i, uint4 v) {                     // k % 256 == 0: whole warps in or out
       *reinterpret_cast<uint4*>(xraw + i) = v;
       uint32_t const w4[4] = {v.x, v.y, v.z, v.w};
       float p = 0.f;
@@ -321,7 +340,14 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
 #pragma unroll
       for (int o = 1; o < Q / 8; o <<= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
       if ((lane & (Q / 8 - 1)) == 0) sxq[m * (k / Q) + i / Q] = p;
+    };
+    uint4 const* xg = reinterpret_cast<uint4 const*>(reinterpret_cast<uint16_t const*>(d.act) + xoff);
+#pragma unroll
+    for (int j = 0; j < kPre; ++j) {
+      int const i = (int(threadIdx.x) + j * 512) * 8;
+      if (i < k) piece(i, m == 0 ? pre[j] : __ldg(xg + i / 8));
     }
+    for (int i = (int(threadIdx.x) + kPre * 512) * 8; i < k; i += 512 * 8) piece(i, __ldg(xg + i / 8));
     mx = warp_max(mx);
     if (lane == 0) red[warp] = mx;
     __syncthreads();
@@ -426,7 +452,7 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
       for (int i = 0; i < (MODE == 0 ? NQ : (UnitT::kSbBytes + 3) / 4); ++i) dep ^= cur[i];
       asm volatile("mov.u32 %0, %1;" : "=r"(sink) : "r"(dep) : "memory");
       __syncwarp();
-      if (lane == 0 && q + STAGES < ntiles) issue(q + STAGES);
+      if (q + STAGES < ntiles) issue(q + STAGES);
     }
     // scale channel of this lane's NQ runs, decoded once for all rows: weight = sv * (code + off) + zv
     float sv[NQ], zv[NQ], ov[NQ];
@@ -631,7 +657,16 @@ int launch_rowthread_mr(PlaneGemvDesc const& d, cudaStream_t stream) {
   a.ns = d.k / kSlice; a.nblocks = (d.n + kRows - 1) / kRows;
   a.status = rt_device_status_ptr();
   if (!a.status) return kRuntimeError;
-  kern<<<dim3(p.gx, gy), 512, p.smem, stream>>>(m.lo, m.hi, m.sc, m.zr, a);
+  // Programmatic dependent launch: this kernel may be scheduled while the previous kernel of the stream drains; it reads
+  // activations and offsets only after griddepcontrol.wait.  QUACTLIZE_B200_NO_PDL=1 launches it the plain way.
+  static bool const no_pdl = std::getenv("QUACTLIZE_B200_NO_PDL") != nullptr;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(p.gx, gy); cfg.blockDim = dim3(512); cfg.dynamicSmemBytes = p.smem; cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = no_pdl ? 0 : 1;
+  if (cudaLaunchKernelEx(&cfg, kern, m.lo, m.hi, m.sc, m.zr, a) != cudaSuccess) { (void)cudaGetLastError(); return kRuntimeError; }
   return 0;
 }
 
