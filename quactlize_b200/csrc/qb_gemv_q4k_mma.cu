@@ -21,6 +21,7 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <cstdlib>
 #include <map>
 #include <mutex>
 
@@ -99,6 +100,9 @@ __global__ void __launch_bounds__(512, 1) q4k_mma_kernel(const __grid_constant__
 
   // ---- which group of activation rows / which expert ----------------------------------------------------------------------
   int e = 0, arow = 0, nrows = 1;
+  // Under programmatic dependent launch the activations (and a router's offsets) may be the preceding kernel's output:
+  // nothing of them is read before this wait.  Without the launch attribute it returns at once.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (a.offsets) {
     volatile int* sh = reinterpret_cast<volatile int*>(smem);            // ring space, not yet in use
     if (threadIdx.x < 4) sh[threadIdx.x] = -1;
@@ -174,21 +178,32 @@ __global__ void __launch_bounds__(512, 1) q4k_mma_kernel(const __grid_constant__
     }
     if (++is_s == bpr) { is_s = 0; is_row0 += row_step; }
   };
+  // The first activation row is requested BEFORE the weight stream: a load issued after it queues behind the ring's copies.
+  constexpr int kPre = 4;                                   // 16-byte pieces per thread held in registers (K <= 16384)
+  uint4 pre[kPre];
+  {
+    uint16_t const* x0 = reinterpret_cast<uint16_t const*>(a.x) + size_t(arow) * k;
+#pragma unroll
+    for (int j = 0; j < kPre; ++j) {
+      int const i = (int(threadIdx.x) + j * 512) * 8;
+      pre[j] = i < k ? __ldg(reinterpret_cast<uint4 const*>(x0 + i)) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) mbar_init(&mybars[s], 1);
     mbar_init_fence();
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  for (int q = 0; q < STAGES && q < ntiles; ++q) issue(q);   // the weight stream starts before the activations are ready
+  for (int q = 0; q < STAGES && q < ntiles; ++q) issue(q);   // the weight stream starts before the activations are converted
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   for (int i = threadIdx.x; i < (nb_c + 16) * kQRows * kQCols; i += blockDim.x) part[i] = 0.f;
 
   // ---- CTA prologue: activations into fragment order -------------------------------------------------------------------------
   for (int m = 0; m < nrows; ++m) {
     uint16_t const* xr = reinterpret_cast<uint16_t const*>(a.x) + size_t(arow + m) * k;
     float mx = 0.f;
-    for (int i = threadIdx.x * 8; i < k; i += blockDim.x * 8) {          // k % 256 == 0: whole warps in or out
-      uint4 const v = __ldg(reinterpret_cast<uint4 const*>(xr + i));
+    auto piece = [&](int i, uint4 v) {                                   // k % 256 == 0: whole warps in or out
       uint32_t const w4[4] = {v.x, v.y, v.z, v.w};
       float p = 0.f;
 #pragma unroll
@@ -200,7 +215,13 @@ __global__ void __launch_bounds__(512, 1) q4k_mma_kernel(const __grid_constant__
       p += __shfl_xor_sync(0xffffffffu, p, 1);
       p += __shfl_xor_sync(0xffffffffu, p, 2);
       if ((lane & 3) == 0) sxq[(i / 32) * kQCols + m] = p;
+    };
+#pragma unroll
+    for (int j = 0; j < kPre; ++j) {
+      int const i = (int(threadIdx.x) + j * 512) * 8;
+      if (i < k) piece(i, m == 0 ? pre[j] : __ldg(reinterpret_cast<uint4 const*>(xr + i)));
     }
+    for (int i = (int(threadIdx.x) + kPre * 512) * 8; i < k; i += 512 * 8) piece(i, __ldg(reinterpret_cast<uint4 const*>(xr + i)));
     mx = warp_max(mx);
     if (lane == 0) red[warp] = mx;
     __syncthreads();
@@ -373,8 +394,17 @@ bool enqueue_q4k_mma(uint8_t const* blocks, __half const* x, float* out, int con
   a.blocks = blocks; a.x = x; a.out = out; a.offsets = offsets;
   a.n = n; a.bpr = bpr; a.experts = E; a.m_rows = rows; a.cpg = p.cpg; a.nblocks = (n + kQRows - 1) / kQRows;
   a.status = status;
-  if (p.stages == 4) q4k_mma_kernel<4><<<dim3(p.gx, gy), 512, p.smem, stream>>>(m, a);
-  else q4k_mma_kernel<2><<<dim3(p.gx, gy), 512, p.smem, stream>>>(m, a);
+  // Programmatic dependent launch: this kernel may be scheduled while the previous kernel of the stream drains; it reads
+  // activations and offsets only after griddepcontrol.wait.  QUACTLIZE_B200_NO_PDL=1 launches it the plain way.
+  static bool const no_pdl = std::getenv("QUACTLIZE_B200_NO_PDL") != nullptr;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(p.gx, gy); cfg.blockDim = dim3(512); cfg.dynamicSmemBytes = p.smem; cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = no_pdl ? 0 : 1;
+  cudaError_t const le = p.stages == 4 ? cudaLaunchKernelEx(&cfg, q4k_mma_kernel<4>, m, a) : cudaLaunchKernelEx(&cfg, q4k_mma_kernel<2>, m, a);
+  if (le != cudaSuccess) { (void)cudaGetLastError(); return false; }
   return true;
 }
 

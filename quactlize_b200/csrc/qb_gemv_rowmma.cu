@@ -117,6 +117,9 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
 
   // ---- which group of activation rows / which expert (as in the row-thread kernel, 8 rows per group) ----------------------
   int e = 0, arow = 0, nrows = 1;
+  // Under programmatic dependent launch the activations (and a router's offsets) may be the preceding kernel's output:
+  // nothing of them is read before this wait.  Without the launch attribute it returns at once.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (d.offsets) {
     volatile int* sh = reinterpret_cast<volatile int*>(smem);            // ring space, not yet in use
     if (threadIdx.x < 4) sh[threadIdx.x] = -1;
@@ -211,21 +214,32 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
     }
     if (++is_s == ns) { is_s = 0; is_row0 += row_step; }
   };
+  // The first activation row is requested BEFORE the weight stream: a load issued after it queues behind the ring's copies.
+  constexpr int kPre = 4;                                   // 16-byte pieces per thread held in registers (K <= 16384)
+  uint4 pre[kPre];
+  {
+    uint16_t const* x0 = reinterpret_cast<uint16_t const*>(d.act) + size_t(arow) * k;
+#pragma unroll
+    for (int j = 0; j < kPre; ++j) {
+      int const i = (int(threadIdx.x) + j * 512) * 8;
+      pre[j] = i < k ? __ldg(reinterpret_cast<uint4 const*>(x0 + i)) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) mbar_init(&mybars[s], 1);
     mbar_init_fence();
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  for (int q = 0; q < STAGES && q < ntiles; ++q) issue(q);   // the weight stream starts before the activations are ready
+  for (int q = 0; q < STAGES && q < ntiles; ++q) issue(q);   // the weight stream starts before the activations are converted
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   for (int i = threadIdx.x; i < (nb_c + 16) * kTRows * kCols; i += blockDim.x) part[i] = 0.f;
 
   // ---- CTA prologue: every activation row of the group into pattern order --------------------------------------------------
   for (int m = 0; m < nrows; ++m) {
     size_t const xoff = size_t(arow + m) * k;
     float mx = 0.f;
-    for (int i = threadIdx.x * 8; i < k; i += blockDim.x * 8) {          // k % 256 == 0: whole warps in or out
-      uint4 const v = __ldg(reinterpret_cast<uint4 const*>(reinterpret_cast<uint16_t const*>(d.act) + xoff + i));
+    auto piece = [&](int i, uint4 v) {                     // k % 256 == 0: whole warps in or out
       *reinterpret_cast<uint4*>(xraw + i) = v;
       uint32_t const w4[4] = {v.x, v.y, v.z, v.w};
       float p = 0.f;
@@ -239,7 +253,14 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
 #pragma unroll
       for (int o = 1; o < GQ / 8; o <<= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
       if ((lane & (GQ / 8 - 1)) == 0) sxq[(i / GQ) * kCols + m] = p;
+    };
+    uint4 const* xg = reinterpret_cast<uint4 const*>(reinterpret_cast<uint16_t const*>(d.act) + xoff);
+#pragma unroll
+    for (int j = 0; j < kPre; ++j) {
+      int const i = (int(threadIdx.x) + j * 512) * 8;
+      if (i < k) piece(i, m == 0 ? pre[j] : __ldg(xg + i / 8));
     }
+    for (int i = (int(threadIdx.x) + kPre * 512) * 8; i < k; i += 512 * 8) piece(i, __ldg(xg + i / 8));
     mx = warp_max(mx);
     if (lane == 0) red[warp] = mx;
     __syncthreads();
@@ -432,7 +453,16 @@ int launch_rowmma(PlaneGemvDesc const& d, cudaStream_t stream) {
   a.ns = d.k / kTSlice; a.nblocks = (d.n + kTRows - 1) / kTRows;
   a.status = rt_device_status_ptr();
   if (!a.status) return kRuntimeError;
-  kern<<<dim3(p.gx, gy), 512, p.smem, stream>>>(m.lo, m.sc, m.zr, a);
+  // Programmatic dependent launch: this kernel may be scheduled while the previous kernel of the stream drains; it reads
+  // activations and offsets only after griddepcontrol.wait.  QUACTLIZE_B200_NO_PDL=1 launches it the plain way.
+  static bool const no_pdl = std::getenv("QUACTLIZE_B200_NO_PDL") != nullptr;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(p.gx, gy); cfg.blockDim = dim3(512); cfg.dynamicSmemBytes = p.smem; cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = no_pdl ? 0 : 1;
+  if (cudaLaunchKernelEx(&cfg, kern, m.lo, m.sc, m.zr, a) != cudaSuccess) { (void)cudaGetLastError(); return kRuntimeError; }
   return 0;
 }
 
