@@ -488,17 +488,22 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
       (void)xq;
 #pragma unroll
       for (int u = 0; u < NU; ++u) {
-        __half2 acc = __float2half2_rn(0.f);
+        // two independent fp16 chains per run (even and odd words) when the run has several words: half the dependent
+        // latency, half the products per fp16 accumulator
+        constexpr int WPR = U / CWL;                      // low-plane words per run
+        __half2 acc = __float2half2_rn(0.f), acc_b = __float2half2_rn(0.f);
 #pragma unroll
-        for (int wi = u * (U / CWL); wi < (u + 1) * (U / CWL); ++wi) {
+        for (int wi = u * WPR; wi < (u + 1) * WPR; ++wi) {
           __half2 xs[NPL];
 #pragma unroll
           for (int v = 0; v < NPL / 4; ++v) {
             uint4 const xv = lds128_a(xp + wi * (NPL * 4) + v * 16);
             xs[4 * v] = u32_as_h2(xv.x); xs[4 * v + 1] = u32_as_h2(xv.y); xs[4 * v + 2] = u32_as_h2(xv.z); xs[4 * v + 3] = u32_as_h2(xv.w);
           }
-          acc = rt_acc_word<LO>(wl[wi], xs, acc);
+          if (WPR > 1 && (wi & 1)) acc_b = rt_acc_word<LO>(wl[wi], xs, acc_b);
+          else acc = rt_acc_word<LO>(wl[wi], xs, acc);
         }
+        if constexpr (WPR > 1) acc = __hadd2(acc, acc_b);
         if constexpr (HI != 0 && !kCrossHi) {
 #pragma unroll
           for (int wi = u * (U / CWH); wi < (u + 1) * (U / CWH); ++wi) {
