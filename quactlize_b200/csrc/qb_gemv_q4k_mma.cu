@@ -178,31 +178,44 @@ __global__ void __launch_bounds__(512, 1) q4k_mma_kernel(const __grid_constant__
     }
     if (++is_s == bpr) { is_s = 0; is_row0 += row_step; }
   };
-  // The first activation row is requested BEFORE the weight stream: a load issued after it queues behind the ring's copies.
+  // Activation rows are requested BEFORE the weight stream: a load issued after it queues behind the ring's copies and
+  // costs a microsecond per row.  Row m + 1 is loaded into registers while row m is converted, and the stream starts as
+  // soon as the last row's loads are in flight.
   constexpr int kPre = 4;                                   // 16-byte pieces per thread held in registers (K <= 16384)
   uint4 pre[kPre];
-  {
-    uint16_t const* x0 = reinterpret_cast<uint16_t const*>(a.x) + size_t(arow) * k;
+  auto load_row = [&](int m) {
+    uint16_t const* x0 = reinterpret_cast<uint16_t const*>(a.x) + size_t(arow + m) * k;
 #pragma unroll
     for (int j = 0; j < kPre; ++j) {
       int const i = (int(threadIdx.x) + j * 512) * 8;
       pre[j] = i < k ? __ldg(reinterpret_cast<uint4 const*>(x0 + i)) : make_uint4(0u, 0u, 0u, 0u);
     }
-  }
+  };
+  load_row(0);
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) mbar_init(&mybars[s], 1);
     mbar_init_fence();
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  for (int q = 0; q < STAGES && q < ntiles; ++q) issue(q);   // the weight stream starts before the activations are converted
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  auto start_stream = [&]() {
+    for (int q = 0; q < STAGES && q < ntiles; ++q) issue(q);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  };
+  if (nrows == 1) start_stream();
   for (int i = threadIdx.x; i < (nb_c + 16) * kQRows * kQCols; i += blockDim.x) part[i] = 0.f;
 
   // ---- CTA prologue: activations into fragment order -------------------------------------------------------------------------
   for (int m = 0; m < nrows; ++m) {
     uint16_t const* xr = reinterpret_cast<uint16_t const*>(a.x) + size_t(arow + m) * k;
     float mx = 0.f;
+    uint4 cur[kPre];
+#pragma unroll
+    for (int j = 0; j < kPre; ++j) cur[j] = pre[j];
+    if (m + 1 < nrows) {                                                 // uniform for the CTA
+      load_row(m + 1);
+      if (m + 2 == nrows) start_stream();
+    }
     auto piece = [&](int i, uint4 v) {                                   // k % 256 == 0: whole warps in or out
       uint32_t const w4[4] = {v.x, v.y, v.z, v.w};
       float p = 0.f;
@@ -219,7 +232,7 @@ __global__ void __launch_bounds__(512, 1) q4k_mma_kernel(const __grid_constant__
 #pragma unroll
     for (int j = 0; j < kPre; ++j) {
       int const i = (int(threadIdx.x) + j * 512) * 8;
-      if (i < k) piece(i, m == 0 ? pre[j] : __ldg(reinterpret_cast<uint4 const*>(xr + i)));
+      if (i < k) piece(i, cur[j]);
     }
     for (int i = (int(threadIdx.x) + kPre * 512) * 8; i < k; i += 512 * 8) piece(i, __ldg(reinterpret_cast<uint4 const*>(xr + i)));
     mx = warp_max(mx);
@@ -231,8 +244,7 @@ __global__ void __launch_bounds__(512, 1) q4k_mma_kernel(const __grid_constant__
     int const ex = pow2_scale_exponent(mx, 15);
     if (threadIdx.x == 0) fmv[m] = ldexpf(1.f, 24 - ex);
     float const mul = __int_as_float((127 + ex) << 23);
-    for (int i = threadIdx.x * 8; i < k; i += blockDim.x * 8) {
-      uint4 const v = __ldg(reinterpret_cast<uint4 const*>(xr + i));
+    auto convert = [&](int i, uint4 v) {
       float2 const f0 = __half22float2(u32_as_h2(v.x)), f1 = __half22float2(u32_as_h2(v.y));
       float2 const f2 = __half22float2(u32_as_h2(v.z)), f3 = __half22float2(u32_as_h2(v.w));
       uint4 o;                                                           // [x0 x2 | x1 x3] [x4 x6 | x5 x7]
@@ -241,7 +253,13 @@ __global__ void __launch_bounds__(512, 1) q4k_mma_kernel(const __grid_constant__
       uint8_t* dst = xpat + size_t(m) * xrow + size_t(i) * 2;            // 16-byte aligned
       *reinterpret_cast<uint2*>(dst) = make_uint2(o.x, o.y);
       *reinterpret_cast<uint2*>(dst + 8) = make_uint2(o.z, o.w);
+    };
+#pragma unroll
+    for (int j = 0; j < kPre; ++j) {                                     // the pieces are still in registers
+      int const i = (int(threadIdx.x) + j * 512) * 8;
+      if (i < k) convert(i, cur[j]);
     }
+    for (int i = (int(threadIdx.x) + kPre * 512) * 8; i < k; i += 512 * 8) convert(i, __ldg(reinterpret_cast<uint4 const*>(xr + i)));
     __syncthreads();                                                     // red is reused by the next row
   }
 

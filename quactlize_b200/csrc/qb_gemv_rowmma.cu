@@ -214,31 +214,44 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
     }
     if (++is_s == ns) { is_s = 0; is_row0 += row_step; }
   };
-  // The first activation row is requested BEFORE the weight stream: a load issued after it queues behind the ring's copies.
+  // Activation rows are requested BEFORE the weight stream: a load issued after it queues behind the ring's copies and
+  // costs a microsecond per row.  Row m + 1 is loaded into registers while row m is converted, and the stream starts as
+  // soon as the last row's loads are in flight.
   constexpr int kPre = 4;                                   // 16-byte pieces per thread held in registers (K <= 16384)
   uint4 pre[kPre];
-  {
-    uint16_t const* x0 = reinterpret_cast<uint16_t const*>(d.act) + size_t(arow) * k;
+  auto load_row = [&](int m) {
+    uint16_t const* x0 = reinterpret_cast<uint16_t const*>(d.act) + size_t(arow + m) * k;
 #pragma unroll
     for (int j = 0; j < kPre; ++j) {
       int const i = (int(threadIdx.x) + j * 512) * 8;
       pre[j] = i < k ? __ldg(reinterpret_cast<uint4 const*>(x0 + i)) : make_uint4(0u, 0u, 0u, 0u);
     }
-  }
+  };
+  load_row(0);
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) mbar_init(&mybars[s], 1);
     mbar_init_fence();
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  for (int q = 0; q < STAGES && q < ntiles; ++q) issue(q);   // the weight stream starts before the activations are converted
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  auto start_stream = [&]() {
+    for (int q = 0; q < STAGES && q < ntiles; ++q) issue(q);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  };
+  if (nrows == 1) start_stream();
   for (int i = threadIdx.x; i < (nb_c + 16) * kTRows * kCols; i += blockDim.x) part[i] = 0.f;
 
   // ---- CTA prologue: every activation row of the group into pattern order --------------------------------------------------
   for (int m = 0; m < nrows; ++m) {
     size_t const xoff = size_t(arow + m) * k;
     float mx = 0.f;
+    uint4 cur[kPre];
+#pragma unroll
+    for (int j = 0; j < kPre; ++j) cur[j] = pre[j];
+    if (m + 1 < nrows) {                                   // uniform for the CTA
+      load_row(m + 1);
+      if (m + 2 == nrows) start_stream();
+    }
     auto piece = [&](int i, uint4 v) {                     // k % 256 == 0: whole warps in or out
       *reinterpret_cast<uint4*>(xraw + i) = v;
       uint32_t const w4[4] = {v.x, v.y, v.z, v.w};
@@ -258,7 +271,7 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
 #pragma unroll
     for (int j = 0; j < kPre; ++j) {
       int const i = (int(threadIdx.x) + j * 512) * 8;
-      if (i < k) piece(i, m == 0 ? pre[j] : __ldg(xg + i / 8));
+      if (i < k) piece(i, cur[j]);
     }
     for (int i = (int(threadIdx.x) + kPre * 512) * 8; i < k; i += 512 * 8) piece(i, __ldg(xg + i / 8));
     mx = warp_max(mx);
@@ -374,10 +387,9 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
 
 struct MmaPlan { int gx, rc; size_t smem; };
 
-template <int LO, int WL, int GQ>
-int launch_rowmma(PlaneGemvDesc const& d, cudaStream_t stream) {
+template <int LO, int WL, int GQ, int STAGES>
+int launch_rowmma_st(PlaneGemvDesc const& d, cudaStream_t stream) {
   constexpr int TILE = kTRows * 32 * LO;
-  constexpr int STAGES = LO == 1 ? 8 : 4;             // 64-128 KB in flight per SM (32 KB for the 1-bit plane)
   constexpr int XPAD = LO == 4 ? 24 : 8;
   constexpr int SC_TILE = 2 * std::max(128, (kTSlice / GQ) * kTRows * 2);
   auto kern = rowmma_gemv_kernel<LO, WL, GQ, STAGES>;
@@ -464,6 +476,18 @@ int launch_rowmma(PlaneGemvDesc const& d, cudaStream_t stream) {
   cfg.attrs = at; cfg.numAttrs = no_pdl ? 0 : 1;
   if (cudaLaunchKernelEx(&cfg, kern, m.lo, m.sc, m.zr, a) != cudaSuccess) { (void)cudaGetLastError(); return kRuntimeError; }
   return 0;
+}
+
+// Ring depth: 64-128 KB in flight per SM (32 KB for the 1-bit plane).  A 4-bit plane with a long K leaves no room for
+// eight rows of activations beside a 128 KB ring; it runs with half the depth rather than falling back to a kernel
+// that streams the weights once per four rows.
+template <int LO, int WL, int GQ>
+int launch_rowmma(PlaneGemvDesc const& d, cudaStream_t stream) {
+  int const rc = launch_rowmma_st<LO, WL, GQ, (LO == 1 ? 8 : 4)>(d, stream);
+  if constexpr (LO == 4) {
+    if (rc == 40) return launch_rowmma_st<LO, WL, GQ, 2>(d, stream);
+  }
+  return rc;
 }
 
 }  // namespace

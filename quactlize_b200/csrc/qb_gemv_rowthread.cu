@@ -294,26 +294,31 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
     }
     if (++is_s == ns) { is_s = 0; is_row0 += row_step; }
   };
-  // The first activation row is requested BEFORE the weight stream: a load issued after it queues behind the ring's
-  // copies (128 KB per SM) and delays the prologue by a microsecond.
+  // Activation rows are requested BEFORE the weight stream: a load issued after it queues behind the ring's copies
+  // (128 KB per SM) and costs a microsecond per row.  Row m + 1 is loaded into registers while row m is converted, and
+  // the stream starts as soon as the last row's loads are in flight.
   constexpr int kPre = 4;                                   // 16-byte pieces per thread held in registers: K <= 16384 is covered
   uint4 pre[kPre];
-  {
-    uint16_t const* x0 = reinterpret_cast<uint16_t const*>(d.act) + size_t(arow) * k;
+  auto load_row = [&](int m) {
+    uint16_t const* x0 = reinterpret_cast<uint16_t const*>(d.act) + size_t(arow + m) * k;
 #pragma unroll
     for (int j = 0; j < kPre; ++j) {
       int const i = (int(threadIdx.x) + j * 512) * 8;
       pre[j] = i < k ? __ldg(reinterpret_cast<uint4 const*>(x0 + i)) : make_uint4(0u, 0u, 0u, 0u);
     }
-  }
+  };
+  load_row(0);
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) mbar_init(&mybars[s], 1);
     mbar_init_fence();
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  for (int q = 0; q < STAGES && q < ntiles; ++q) issue(q);   // the weight stream starts before the activations are converted
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  auto start_stream = [&]() {
+    for (int q = 0; q < STAGES && q < ntiles; ++q) issue(q);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  };
+  if (nrows == 1) start_stream();
   for (int i = threadIdx.x; i < (nb_c + 16) * MR * kRows; i += blockDim.x) part[i] = 0.f;
 
   // ---- CTA prologue: activations into pattern order, one activation row at a time ---------------------------------------
@@ -326,6 +331,13 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
     // consecutive 8-element pieces, so a run is Q/8 neighbouring lanes)
     size_t const xoff = size_t(arow + m) * k;
     float mx = 0.f;
+    uint4 cur[kPre];
+#pragma unroll
+    for (int j = 0; j < kPre; ++j) cur[j] = pre[j];
+    if (m + 1 < nrows) {                                   // uniform for the CTA
+      load_row(m + 1);
+      if (m + 2 == nrows) start_stream();
+    }
     auto piece = [&](int i, uint4 v) {                     // k % 256 == 0: whole warps in or out
       *reinterpret_cast<uint4*>(xraw + i) = v;
       uint32_t const w4[4] = {v.x, v.y, v.z, v.w};
@@ -345,7 +357,7 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
 #pragma unroll
     for (int j = 0; j < kPre; ++j) {
       int const i = (int(threadIdx.x) + j * 512) * 8;
-      if (i < k) piece(i, m == 0 ? pre[j] : __ldg(xg + i / 8));
+      if (i < k) piece(i, cur[j]);
     }
     for (int i = (int(threadIdx.x) + kPre * 512) * 8; i < k; i += 512 * 8) piece(i, __ldg(xg + i / 8));
     mx = warp_max(mx);
