@@ -26,8 +26,10 @@
 #include <cstdlib>
 #include <map>
 #include <mutex>
+#include <type_traits>
 
 #include "qb_device.cuh"
+#include "qb_gemv_prologue.cuh"
 #include "qb_internal.hpp"
 #include "qb_runtime.hpp"
 #include "qb_tma.hpp"
@@ -242,59 +244,46 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
   for (int i = threadIdx.x; i < (nb_c + 16) * kTRows * kCols; i += blockDim.x) part[i] = 0.f;
 
   // ---- CTA prologue: every activation row of the group into pattern order --------------------------------------------------
-  for (int m = 0; m < nrows; ++m) {
-    size_t const xoff = size_t(arow + m) * k;
-    float mx = 0.f;
-    uint4 cur[kPre];
+  auto prologue = [&](auto bf16_tag) {
+    constexpr bool BF = decltype(bf16_tag)::value;
+    for (int m = 0; m < nrows; ++m) {
+      float mx = 0.f;
+      uint4 cur[kPre];
 #pragma unroll
-    for (int j = 0; j < kPre; ++j) cur[j] = pre[j];
-    if (m + 1 < nrows) {                                   // uniform for the CTA
-      load_row(m + 1);
-      if (m + 2 == nrows) start_stream();
-    }
-    auto piece = [&](int i, uint4 v) {                     // k % 256 == 0: whole warps in or out
-      *reinterpret_cast<uint4*>(xraw + i) = v;
-      uint32_t const w4[4] = {v.x, v.y, v.z, v.w};
-      float p = 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        uint32_t const h = (w4[j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
-        float const f = d.act_bf16 ? __uint_as_float(h << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(h)));
-        mx = fmaxf(mx, fabsf(f));
-        p += f;
+      for (int j = 0; j < kPre; ++j) cur[j] = pre[j];
+      if (m + 1 < nrows) {                                 // uniform for the CTA
+        load_row(m + 1);
+        if (m + 2 == nrows) start_stream();
       }
+      auto piece = [&](int i, uint4 v) {                   // k % 256 == 0: whole warps in or out
+        *reinterpret_cast<uint4*>(xraw + i) = v;
+        float p;
+        piece_stats<BF>(v, mx, p);
 #pragma unroll
-      for (int o = 1; o < GQ / 8; o <<= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
-      if ((lane & (GQ / 8 - 1)) == 0) sxq[(i / GQ) * kCols + m] = p;
-    };
-    uint4 const* xg = reinterpret_cast<uint4 const*>(reinterpret_cast<uint16_t const*>(d.act) + xoff);
+        for (int o = 1; o < GQ / 8; o <<= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
+        if ((lane & (GQ / 8 - 1)) == 0) sxq[(i / GQ) * kCols + m] = p;
+      };
+      uint4 const* xg = reinterpret_cast<uint4 const*>(reinterpret_cast<uint16_t const*>(d.act) + size_t(arow + m) * k);
 #pragma unroll
-    for (int j = 0; j < kPre; ++j) {
-      int const i = (int(threadIdx.x) + j * 512) * 8;
-      if (i < k) piece(i, cur[j]);
+      for (int j = 0; j < kPre; ++j) {
+        int const i = (int(threadIdx.x) + j * 512) * 8;
+        if (i < k) piece(i, cur[j]);
+      }
+      for (int i = (int(threadIdx.x) + kPre * 512) * 8; i < k; i += 512 * 8) piece(i, __ldg(xg + i / 8));
+      mx = warp_max(mx);
+      if (lane == 0) red[warp] = mx;
+      __syncthreads();
+      mx = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) mx = fmaxf(mx, red[i]);
+      int const ex = pow2_scale_exponent(mx, 15);
+      if (threadIdx.x == 0) fmv[m] = ldexpf(1.f, 24 - ex);
+      pattern_row<LO, BF>(xraw, xpat + size_t(m) * xrow, k, ex, kXPart, kXPartStride);   // one half2 operand per code pair
+      __syncthreads();                                     // xraw and red are reused by the next row
     }
-    for (int i = (int(threadIdx.x) + kPre * 512) * 8; i < k; i += 512 * 8) piece(i, __ldg(xg + i / 8));
-    mx = warp_max(mx);
-    if (lane == 0) red[warp] = mx;
-    __syncthreads();
-    mx = 0.f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) mx = fmaxf(mx, red[i]);
-    int const ex = pow2_scale_exponent(mx, 15);
-    if (threadIdx.x == 0) fmv[m] = ldexpf(1.f, 24 - ex);
-    for (int x = threadIdx.x; x < k / 2; x += blockDim.x) {              // one half2 operand per code pair
-      int const word = x / NP, p = x % NP, h = p / PER, o = p % PER;
-      int const c0 = word * CW + h * PER + o;
-      float const mul = __int_as_float((127 + ex - o * LO) << 23);
-      uint32_t const h0 = xraw[c0], h1 = xraw[c0 + 16 / LO];
-      float const f0 = d.act_bf16 ? __uint_as_float(h0 << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(h0)));
-      float const f1 = d.act_bf16 ? __uint_as_float(h1 << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(h1)));
-      int const pt = (word * CW) / kXPart;
-      *reinterpret_cast<__half2*>(xpat + size_t(m) * xrow + size_t(pt) * kXPartStride + size_t(x - pt * (kXPart / 2)) * 4) =
-          __floats2half2_rn(f0 * mul, f1 * mul);
-    }
-    __syncthreads();                                       // xraw and red are reused by the next row
-  }
+  };
+  if (d.act_bf16) prologue(std::true_type{});
+  else prologue(std::false_type{});
 
   // ---- per-lane constants of the fragment addressing ------------------------------------------------------------------------
   constexpr uint32_t M1 = ((1u << LO) - 1u) * 0x00010001u;

@@ -31,8 +31,10 @@
 #include <cstdlib>
 #include <map>
 #include <mutex>
+#include <type_traits>
 
 #include "qb_device.cuh"
+#include "qb_gemv_prologue.cuh"
 #include "qb_internal.hpp"
 #include "qb_kquant.cuh"
 #include "qb_runtime.hpp"
@@ -324,77 +326,53 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   // ---- CTA prologue: activations into pattern order, one activation row at a time ---------------------------------------
   float fm[MR];
 #pragma unroll
-  for (int m = 0; m < MR; ++m) {
-    fm[m] = 0.f;
-    if (m >= nrows) continue;                              // uniform for the CTA
-    // pass 1: raw 16-bit activations to shared memory, max |x|, and the sum of x over every Q-code run (lanes hold
-    // consecutive 8-element pieces, so a run is Q/8 neighbouring lanes)
-    size_t const xoff = size_t(arow + m) * k;
-    float mx = 0.f;
-    uint4 cur[kPre];
+  for (int m = 0; m < MR; ++m) fm[m] = 0.f;
+  auto prologue = [&](auto bf16_tag) {
+    constexpr bool BF = decltype(bf16_tag)::value;
 #pragma unroll
-    for (int j = 0; j < kPre; ++j) cur[j] = pre[j];
-    if (m + 1 < nrows) {                                   // uniform for the CTA
-      load_row(m + 1);
-      if (m + 2 == nrows) start_stream();
-    }
-    auto piece = [&](int i, uint4 v) {                     // k % 256 == 0: whole warps in or out
-      *reinterpret_cast<uint4*>(xraw + i) = v;
-      uint32_t const w4[4] = {v.x, v.y, v.z, v.w};
-      float p = 0.f;
+    for (int m = 0; m < MR; ++m) {
+      if (m >= nrows) continue;                            // uniform for the CTA
+      // pass 1: raw 16-bit activations to shared memory, max |x|, and the sum of x over every Q-code run (lanes hold
+      // consecutive 8-element pieces, so a run is Q/8 neighbouring lanes)
+      float mx = 0.f;
+      uint4 cur[kPre];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        uint32_t const h = (w4[j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
-        float const f = d.act_bf16 ? __uint_as_float(h << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(h)));
-        mx = fmaxf(mx, fabsf(f));
-        p += f;
+      for (int j = 0; j < kPre; ++j) cur[j] = pre[j];
+      if (m + 1 < nrows) {                                 // uniform for the CTA
+        load_row(m + 1);
+        if (m + 2 == nrows) start_stream();
       }
+      auto piece = [&](int i, uint4 v) {                   // k % 256 == 0: whole warps in or out
+        *reinterpret_cast<uint4*>(xraw + i) = v;
+        float p;
+        piece_stats<BF>(v, mx, p);
 #pragma unroll
-      for (int o = 1; o < Q / 8; o <<= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
-      if ((lane & (Q / 8 - 1)) == 0) sxq[m * (k / Q) + i / Q] = p;
-    };
-    uint4 const* xg = reinterpret_cast<uint4 const*>(reinterpret_cast<uint16_t const*>(d.act) + xoff);
+        for (int o = 1; o < Q / 8; o <<= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
+        if ((lane & (Q / 8 - 1)) == 0) sxq[m * (k / Q) + i / Q] = p;
+      };
+      uint4 const* xg = reinterpret_cast<uint4 const*>(reinterpret_cast<uint16_t const*>(d.act) + size_t(arow + m) * k);
 #pragma unroll
-    for (int j = 0; j < kPre; ++j) {
-      int const i = (int(threadIdx.x) + j * 512) * 8;
-      if (i < k) piece(i, cur[j]);
-    }
-    for (int i = (int(threadIdx.x) + kPre * 512) * 8; i < k; i += 512 * 8) piece(i, __ldg(xg + i / 8));
-    mx = warp_max(mx);
-    if (lane == 0) red[warp] = mx;
-    __syncthreads();
-    mx = 0.f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) if (i < int(blockDim.x >> 5)) mx = fmaxf(mx, red[i]);
-    int const ex = pow2_scale_exponent(mx, HI ? 15 - LO : 15);
-    fm[m] = ldexpf(1.f, 24 - ex);
-    auto xval = [&](int c) -> float {
-      uint32_t const h = xraw[c];
-      return d.act_bf16 ? __uint_as_float(h << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(h)));
-    };
-    // pass 2: one half2 operand per code pair, multiplier 2^(ex - shift) built from its exponent bits
-    for (int t = threadIdx.x; t < k / 2; t += blockDim.x) {
-      constexpr int PER = 8 / LO;
-      int const word = t / NPL, p = t % NPL, h = p / PER, o = p % PER;
-      int const c0 = word * CWL + h * PER + o;
-      float const mul = __int_as_float((127 + ex - o * LO) << 23);
-      __half2 const v = __floats2half2_rn(xval(c0) * mul, xval(c0 + 16 / LO) * mul);
-      int const pt = (word * CWL) / kPart;
-      *reinterpret_cast<__half2*>(xlo + size_t(m) * xrow + size_t(pt) * kPartStride + size_t(t - pt * (kPart / 2)) * 4) = v;
-    }
-    if constexpr (HI != 0) {
-      for (int t = threadIdx.x; t < k / 2; t += blockDim.x) {
-        constexpr int HB = HI ? HI : 1, PER = 8 / HB;
-        int const word = t / NPH, p = t % NPH, h = p / PER, o = p % PER;
-        int const c0 = word * CWH + h * PER + o;
-        float const mul = __int_as_float((127 + ex + LO - o * HB) << 23);
-        __half2 const v = __floats2half2_rn(xval(c0) * mul, xval(c0 + 16 / HB) * mul);
-        int const pt = (word * CWH) / kPart;
-        *reinterpret_cast<__half2*>(xhi + size_t(m) * xrow + size_t(pt) * kPartStride + size_t(t - pt * (kPart / 2)) * 4) = v;
+      for (int j = 0; j < kPre; ++j) {
+        int const i = (int(threadIdx.x) + j * 512) * 8;
+        if (i < k) piece(i, cur[j]);
       }
+      for (int i = (int(threadIdx.x) + kPre * 512) * 8; i < k; i += 512 * 8) piece(i, __ldg(xg + i / 8));
+      mx = warp_max(mx);
+      if (lane == 0) red[warp] = mx;
+      __syncthreads();
+      mx = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) mx = fmaxf(mx, red[i]);
+      int const ex = pow2_scale_exponent(mx, HI ? 15 - LO : 15);
+      fm[m] = ldexpf(1.f, 24 - ex);
+      // pass 2: one half2 operand per code pair and mask position, multiplier 2^(ex - shift)
+      pattern_row<LO, BF>(xraw, xlo + size_t(m) * xrow, k, ex, kPart, kPartStride);
+      if constexpr (HI != 0) pattern_row<(HI ? HI : 1), BF>(xraw, xhi + size_t(m) * xrow, k, ex + LO, kPart, kPartStride);
+      __syncthreads();                                     // xraw and red are reused by the next row
     }
-    __syncthreads();                                       // xraw and red are reused by the next row
-  }
+  };
+  if (d.act_bf16) prologue(std::true_type{});
+  else prologue(std::false_type{});
 
   // ---- where this lane finds its runs' scales inside the staged scale channel (fixed per lane) -----------------------------
   uint32_t sc_off[MODE == 0 ? NQ : 1];
