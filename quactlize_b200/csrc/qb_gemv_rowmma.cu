@@ -230,6 +230,11 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
     }
   };
   load_row(0);
+  if (!has_zero) {                                          // no copy ever lands in the zero halves: they read as zero
+    for (int i = lane; i < STAGES * (SC_HALF / 4); i += 32)
+      *reinterpret_cast<uint32_t*>(mysc + (i / (SC_HALF / 4)) * SC_TILE + SC_HALF + (i % (SC_HALF / 4)) * 4) = 0u;
+    __syncwarp();
+  }
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) mbar_init(&mybars[s], 1);
@@ -332,8 +337,8 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
       if (((j + 1) * S) % GQ == 0) {                         // a scale group is complete (compile-time condition)
         int const jg = (j * S) / GQ;
         uint32_t const sat = sc_a + st * SC_TILE + jg * (kTRows * 2);
-        uint32_t const raw_lo = lds_u16(sat) | (has_zero ? lds_u16(sat + SC_HALF) << 16 : 0u);
-        uint32_t const raw_hi = lds_u16(sat + 16) | (has_zero ? lds_u16(sat + SC_HALF + 16) << 16 : 0u);
+        uint32_t const raw_lo = lds_u16(sat) | (lds_u16(sat + SC_HALF) << 16);          // the zero half holds zeros when there is no zero plane
+        uint32_t const raw_hi = lds_u16(sat + 16) | (lds_u16(sat + SC_HALF + 16) << 16);
         dep ^= raw_lo ^ raw_hi;
         float2 const lo = __half22float2(u32_as_h2(raw_lo)), hi = __half22float2(u32_as_h2(raw_hi));   // (scale, zero)
         float2 const sx = lds_f32x2(sxq_a + uint32_t(s * NGT + jg) * (kCols * 4));                     // sums of x, columns 2t, 2t+1

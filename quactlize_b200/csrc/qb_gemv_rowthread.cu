@@ -310,6 +310,11 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
     }
   };
   load_row(0);
+  if (MODE == 0 && !has_zero) {                             // no copy ever lands in the zero halves: they read as zero
+    for (int i = lane; i < STAGES * (SC_HALF / 4); i += 32)
+      *reinterpret_cast<uint32_t*>(mysc + (i / (SC_HALF / 4)) * SC_TILE + SC_HALF + (i % (SC_HALF / 4)) * 4) = 0u;
+    __syncwarp();
+  }
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) mbar_init(&mybars[s], 1);
@@ -421,7 +426,7 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
 #pragma unroll
       for (int j = 0; j < NQ; ++j) {
         uint32_t const at = sc_a + st * SC_TILE + sc_off[j];
-        cur[j] = lds_u16(at) | (has_zero ? lds_u16(at + SC_HALF) << 16 : 0u);
+        cur[j] = lds_u16(at) | (lds_u16(at + SC_HALF) << 16);        // the zero half holds zeros when there is no zero plane
       }
     } else {
       uint32_t const at = sc_a + st * SC_TILE + sc_off[0] + uint32_t(s % UnitT::kSbPerUnit) * UnitT::kSbBytes;

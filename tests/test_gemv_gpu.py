@@ -286,3 +286,36 @@ def test_injected_host_failures_leave_output_untouched():
         assert bool((out == 7.0).all())
     out = qb.gguf_dequantize(b, 12)                       # the latch clears on the next call
     assert np.array_equal(_bits(out), g["dequant"].view(np.uint16))
+
+
+@pytest.mark.parametrize("rows", [1, 3], ids=["row_thread", "mma"])
+def test_dependent_launch_chain_reads_the_previous_output(rows):
+    """Two GEMVs back to back on one stream, the second reading the first one's fp16 output as its activations, replayed
+    from a CUDA graph.  The kernels are launched with programmatic stream serialisation, so the second may be scheduled
+    while the first drains: its result is right only if nothing of its input is read before the dependency wait."""
+    k1, n1, n2 = 512, 1024, 256
+    l1, s1, z1 = synth.group_planes(1, n1, k1, 4, 64, seed=11)
+    l2, s2, z2 = synth.group_planes(1, n2, n1, 4, 128, seed=12)
+    s1 = (s1.astype(np.float32) * 0.05).astype(np.float16)          # keeps the intermediate well inside fp16
+    z1 = (z1.astype(np.float32) * 0.05).astype(np.float16)
+    d1, d2 = [_cuda(t) for t in (l1, s1, z1)], [_cuda(t) for t in (l2, s2, z2)]
+    xs = [torch.from_numpy(synth.activations(rows, k1, seed=20 + i)).to(DEV) for i in range(4)]
+    x = torch.empty_like(xs[0])
+
+    def chain():
+        mid = qb.gemv_plane(x, d1[0], None, d1[1], d1[2], 4, 0, 64)
+        return mid, qb.gemv_plane(mid, d2[0], None, d2[1], d2[2], 4, 0, 128, out_dtype=torch.float32)
+
+    x.copy_(xs[0]); chain(); torch.cuda.synchronize()                 # plans and tensor maps exist before the capture
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        mid, out = chain()
+    for xi in xs:
+        x.copy_(xi)
+        g.replay(); g.replay()
+        torch.cuda.synchronize()
+        ref_mid = kq.planes_matmul(xi.float().cpu().numpy(), l1, None, s1, z1, 4, 0, 64).astype(np.float16)
+        assert kq.max_rel(mid.float().cpu().numpy(), ref_mid.astype(np.float32)) < TOL
+        ref = kq.planes_matmul(mid.float().cpu().numpy(), l2, None, s2, z2, 4, 0, 128)   # from the device's own intermediate
+        assert kq.max_rel(out.cpu().numpy(), ref) < TOL
+    _wait_ok()
