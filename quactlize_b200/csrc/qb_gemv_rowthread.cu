@@ -106,21 +106,22 @@ __device__ __forceinline__ __half2 rt_acc_word(uint32_t w, __half2 const* xs, __
 
 // this lane's 64 codes of plane row `r`, part `kp`, out of a swizzled tile whose rows are 32*B bytes
 // byte offset(s) of this lane's codes inside a tile: fixed per lane, computed once
-template <int B>
+// (RB = bytes of a tile row: 128, 64 or 32; a lane's quarter of it is 32, 16 or 8 bytes)
+template <int RB>
 __device__ __forceinline__ void part_offsets(int r, int kp, uint32_t* off) {
-  if constexpr (B == 4) { off[0] = r * 128 + (((2 * kp) ^ r) << 4); off[1] = r * 128 + (((2 * kp + 1) ^ r) << 4); }
-  else if constexpr (B == 2) { off[0] = r * 64 + ((kp ^ ((r >> 1) & 3)) << 4); off[1] = 0; }
+  if constexpr (RB == 128) { off[0] = r * 128 + (((2 * kp) ^ r) << 4); off[1] = r * 128 + (((2 * kp + 1) ^ r) << 4); }
+  else if constexpr (RB == 64) { off[0] = r * 64 + ((kp ^ ((r >> 1) & 3)) << 4); off[1] = 0; }
   else { off[0] = r * 32 + ((((kp >> 1) ^ ((r >> 2) & 1))) << 4) + (kp & 1) * 8; off[1] = 0; }
 }
-template <int B>
+template <int RB>
 __device__ __forceinline__ void load_part(uint32_t tile, uint32_t const* off, uint32_t* w) {
-  if constexpr (B == 4) {
+  if constexpr (RB == 128) {
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       uint4 const v = lds128_a(tile + off[j]);
       w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
     }
-  } else if constexpr (B == 2) {
+  } else if constexpr (RB == 64) {
     uint4 const v = lds128_a(tile + off[0]);
     w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
   } else {
@@ -142,18 +143,23 @@ __device__ __forceinline__ uint32_t bits_at(uint32_t const* u, int bit) {
 
 // LO/HI plane bits; MODE 0 fp16 scale(+zero) planes with NQ = 64/min(gs,64) runs per part, MODE 1 packed units of QT
 // MR activation rows share every weight tile (1, or up to 4 rows of one expert)
-template <int LO, int HI, int MODE, int QT, int NQ, int STAGES, int MR>
+// SL: 256-code slices per tile (1; 2 or 4 for a lone 2- or 1-bit plane, whose tile then is 1 KB like the 4-bit one and the
+// per-tile bookkeeping is paid per 512 / 1024 codes); NQ counts the runs of one lane's 64*SL codes
+template <int LO, int HI, int MODE, int QT, int NQ, int STAGES, int MR, int SL>
 __global__ void __launch_bounds__(512, 1)
 rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_constant__ CUtensorMap map_hi,
                       const __grid_constant__ CUtensorMap map_sc, const __grid_constant__ CUtensorMap map_zr, RtArgs a) {
-  constexpr int Q = kPart / NQ;                       // codes per run: one scale group (or 64 codes of a wider one)
-  constexpr int NWL = kPart * LO / 32;                // low-plane words per part: 8 / 4 / 2
-  constexpr int NWH = HI ? kPart * HI / 32 : 1;       // high-plane words per part: 4 / 2
+  static_assert(SL == 1 || (MODE == 0 && HI == 0 && LO * SL <= 4), "wide tiles are for a lone low plane");
+  constexpr int KS = kSlice * SL, KP = kPart * SL, KPS = KP * 2 + 16;   // codes per tile, per lane, bytes between pattern runs
+  constexpr int Q = KP / NQ;                          // codes per run: one scale group (or 64 codes of a wider one)
+  constexpr int NWL = KP * LO / 32;                   // low-plane words per part: 8 / 4 / 2
+  constexpr int NWH = HI ? KP * HI / 32 : 1;          // high-plane words per part: 4 / 2
   constexpr int CWL = 32 / LO, CWH = HI ? 32 / HI : 32;
   constexpr int NPL = 16 / LO, NPH = HI ? 16 / HI : 1;
   constexpr int U = Q < 32 ? Q : 32;                  // codes per fp16 accumulation run (then fp32)
-  constexpr int NU = kPart / U;
-  constexpr int LO_TILE = kRows * 32 * LO, HI_TILE = HI ? kRows * 32 * HI : 0;
+  constexpr int NU = KP / U;
+  constexpr int RBL = 32 * LO * SL, RBH = HI ? 32 * HI : 32;           // bytes of a tile row
+  constexpr int LO_TILE = kRows * RBL, HI_TILE = HI ? kRows * RBH : 0;
   constexpr int SC_TILE = sc_tile_bytes<MODE, QT, NQ>(), SC_HALF = SC_TILE / 2;   // scale channel of one tile, copied with it
   static_assert(CWL <= U, "a low-plane word must not straddle accumulation runs");
   constexpr bool kCrossHi = HI && CWH > U;            // a high word spans two runs (1-bit plane, 16-code groups)
@@ -225,10 +231,10 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
 
   // ---- shared memory carve-up -----------------------------------------------------------------------------------------
   constexpr int W = 16;
-  int const nparts = k / kPart;
+  int const nparts = k / KP;
   uint8_t* lo_ring = smem;                                              // [W][STAGES][LO_TILE]
   uint8_t* hi_ring = lo_ring + size_t(W) * STAGES * LO_TILE;             // [W][STAGES][HI_TILE]
-  uint32_t const xrow = uint32_t(nparts) * kPartStride;                  // bytes of one activation row in pattern order
+  uint32_t const xrow = uint32_t(nparts) * KPS;                  // bytes of one activation row in pattern order
   uint8_t* sc_ring = hi_ring + size_t(W) * STAGES * HI_TILE;             // [W][STAGES][SC_TILE]
   uint8_t* xlo = sc_ring + size_t(W) * STAGES * SC_TILE;                 // [MR][nparts][kPartStride]
   uint8_t* xhi = xlo + size_t(MR) * xrow;                                // same, if HI
@@ -268,13 +274,13 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   int const gshift = 31 - __clz(gs > 0 ? gs : 1);           // group size is a power of two
   bool const has_zero = MODE == 0 && d.zero != nullptr;
   using UnitT = kq::Unit<(MODE == 1 ? QT : 12)>;
-  int const sc_groups = MODE == 0 ? max(1, kSlice >> gshift) : 0;
+  int const sc_groups = MODE == 0 ? max(1, KS >> gshift) : 0;
   uint32_t const tx_bytes = LO_TILE + HI_TILE + (MODE == 0 ? uint32_t(sc_groups) * 16u * (has_zero ? 2u : 1u) : uint32_t(kRows * UnitT::kUnitTotal));
   uint8_t const* const un_e = MODE == 1 ? d.units + size_t(e) * ((k / 256) / UnitT::kSbPerUnit) * n * UnitT::kUnitTotal : nullptr;
   // called with q = 0, 1, 2, ... in order; every lane keeps the (uniform) bookkeeping, lane 0 issues the copies
   auto issue = [&](int q) {
     uint32_t const st = uint32_t(q) & (STAGES - 1), bar = bar_a + st * 8;
-    int const gy = MODE == 0 ? (is_s * kSlice) >> gshift : 0;
+    int const gy = MODE == 0 ? (is_s * KS) >> gshift : 0;
     if (lane == 0) {
       asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(tx_bytes) : "memory");
       if constexpr (MODE == 0) {
@@ -289,10 +295,10 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
                      ::"r"(ring_sc_a + st * SC_TILE), "l"(src), "n"(kRows * UnitT::kUnitTotal), "r"(bar) : "memory");
       }
       asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-                   ::"r"(ring_lo_a + st * LO_TILE), "l"(map_lo_p), "r"(bar), "r"(is_s * (kSlice * LO / 8)), "r"(is_row0), "r"(e) : "memory");
+                   ::"r"(ring_lo_a + st * LO_TILE), "l"(map_lo_p), "r"(bar), "r"(is_s * (KS * LO / 8)), "r"(is_row0), "r"(e) : "memory");
       if constexpr (HI != 0)
         asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-                     ::"r"(ring_hi_a + st * HI_TILE), "l"(map_hi_p), "r"(bar), "r"(is_s * (kSlice * HI / 8)), "r"(is_row0), "r"(e) : "memory");
+                     ::"r"(ring_hi_a + st * HI_TILE), "l"(map_hi_p), "r"(bar), "r"(is_s * (KS * HI / 8)), "r"(is_row0), "r"(e) : "memory");
     }
     if (++is_s == ns) { is_s = 0; is_row0 += row_step; }
   };
@@ -371,8 +377,8 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
       int const ex = pow2_scale_exponent(mx, HI ? 15 - LO : 15);
       fm[m] = ldexpf(1.f, 24 - ex);
       // pass 2: one half2 operand per code pair and mask position, multiplier 2^(ex - shift)
-      pattern_row<LO, BF>(xraw, xlo + size_t(m) * xrow, k, ex, kPart, kPartStride);
-      if constexpr (HI != 0) pattern_row<(HI ? HI : 1), BF>(xraw, xhi + size_t(m) * xrow, k, ex + LO, kPart, kPartStride);
+      pattern_row<LO, BF>(xraw, xlo + size_t(m) * xrow, k, ex, KP, KPS);
+      if constexpr (HI != 0) pattern_row<(HI ? HI : 1), BF>(xraw, xhi + size_t(m) * xrow, k, ex + LO, KP, KPS);
       __syncthreads();                                     // xraw and red are reused by the next row
     }
   };
@@ -383,7 +389,7 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   uint32_t sc_off[MODE == 0 ? NQ : 1];
   if constexpr (MODE == 0) {
 #pragma unroll
-    for (int j = 0; j < NQ; ++j) sc_off[j] = uint32_t(gs <= kSlice ? (kp * kPart + j * Q) >> gshift : 0) * 16u + uint32_t(r) * 2u;
+    for (int j = 0; j < NQ; ++j) sc_off[j] = uint32_t(gs <= KS ? (kp * KP + j * Q) >> gshift : 0) * 16u + uint32_t(r) * 2u;
   } else {
     sc_off[0] = uint32_t(r) * UnitT::kUnitTotal;
   }
@@ -397,8 +403,8 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
 #pragma unroll
   for (int m = 0; m < MR; ++m) tot[m] = 0.f;
   uint32_t offl[2], offh[2];
-  part_offsets<LO>(r, kp, offl);
-  part_offsets<(HI ? HI : 1)>(r, kp, offh);
+  part_offsets<RBL>(r, kp, offl);
+  part_offsets<RBH>(r, kp, offh);
   uint32_t const lo_a = smem_u32(mylo), hi_a = smem_u32(myhi), xlo_a = smem_u32(xlo), xhi_a = smem_u32(xhi), sxq_a = smem_u32(sxq);
   uint32_t const sx_row = uint32_t(k / Q) * 4;
   // a warp's sums for one block go to slot (block + warp): runs are contiguous and ordered, so slots never collide
@@ -417,10 +423,10 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
    for (int s = s_begin; s < s_end; ++s, ++q) {
     uint32_t const st = uint32_t(q) & (STAGES - 1);
     if (!mbar_wait_bounded(&mybars[st], unsigned(q / STAGES) & 1u, a.status, kWaitStageTimeout)) { dead = true; break; }
-    int const pt = s * (kSlice / kPart) + kp;
+    int const pt = s * (KS / KP) + kp;
     uint32_t wl[NWL], wh[NWH];
-    load_part<LO>(lo_a + st * LO_TILE, offl, wl);
-    if constexpr (HI != 0) load_part<(HI ? HI : 1)>(hi_a + st * HI_TILE, offh, wh);
+    load_part<RBL>(lo_a + st * LO_TILE, offl, wl);
+    if constexpr (HI != 0) load_part<RBH>(hi_a + st * HI_TILE, offh, wh);
     uint32_t cur[NSC];                                       // MODE 0: scale | zero << 16 per run; MODE 1: the superblock's scale bytes
     if constexpr (MODE == 0) {
 #pragma unroll
@@ -478,8 +484,8 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
     for (int m = 0; m < MR; ++m) {
       if (MR > 1 && m >= nrows) continue;                // uniform for the CTA
       float usum[NU];
-      uint32_t const xp = xlo_a + uint32_t(m) * xrow + uint32_t(pt) * kPartStride;
-      uint32_t const xq = xhi_a + uint32_t(m) * xrow + uint32_t(pt) * kPartStride;
+      uint32_t const xp = xlo_a + uint32_t(m) * xrow + uint32_t(pt) * KPS;
+      uint32_t const xq = xhi_a + uint32_t(m) * xrow + uint32_t(pt) * KPS;
       (void)xq;
 #pragma unroll
       for (int u = 0; u < NU; ++u) {
@@ -565,13 +571,14 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
 struct RtPlan { int gx, rc; size_t smem; };
 struct RtMaps { CUtensorMap lo, hi, sc, zr; };
 
-template <int LO, int HI, int MODE, int QT, int NQ, int MR>
+template <int LO, int HI, int MODE, int QT, int NQ, int MR, int SL>
 int launch_rowthread_mr(PlaneGemvDesc const& d, cudaStream_t stream) {
   constexpr int STAGES = (LO + HI >= 5) ? 4 : 8;     // a power of two; 64-96 KB in flight per SM for the wide tiles
-  constexpr int Q = kPart / NQ;
-  constexpr int LO_TILE = kRows * 32 * LO, HI_TILE = HI ? kRows * 32 * HI : 0;
+  constexpr int KS = kSlice * SL, KP = kPart * SL, KPS = KP * 2 + 16;
+  constexpr int Q = KP / NQ;
+  constexpr int LO_TILE = kRows * 32 * LO * SL, HI_TILE = HI ? kRows * 32 * HI : 0;
   constexpr int SC_TILE = sc_tile_bytes<MODE, QT, NQ>();
-  auto kern = rowthread_gemv_kernel<LO, HI, MODE, QT, NQ, STAGES, MR>;
+  auto kern = rowthread_gemv_kernel<LO, HI, MODE, QT, NQ, STAGES, MR, SL>;
   // grid rows: one per group of up to MR activation rows of one expert (ragged: an upper bound, surplus CTAs exit at once)
   int const gy = MR == 1 ? d.m_rows : (d.offsets ? std::min(d.m_rows, d.m_rows / MR + d.experts) : (d.m_rows + MR - 1) / MR);
   if (gy <= 0 || gy > 65535) return 40;
@@ -595,8 +602,8 @@ int launch_rowthread_mr(PlaneGemvDesc const& d, cudaStream_t stream) {
       p.gx = std::max(1, std::min(nblocks, share));
       int per = std::min(512, (nblocks + p.gx - 1) / p.gx);            // blocks per CTA, evened; bounded by the partial-sum table
       p.gx = (nblocks + per - 1) / per;
-      int const nparts = d.k / kPart;
-      p.smem = 1024 + size_t(16) * STAGES * (LO_TILE + HI_TILE + SC_TILE) + size_t(MR) * nparts * kPartStride * (HI ? 2 : 1) +
+      int const nparts = d.k / KP;
+      p.smem = 1024 + size_t(16) * STAGES * (LO_TILE + HI_TILE + SC_TILE) + size_t(MR) * nparts * KPS * (HI ? 2 : 1) +
                size_t(MR) * (d.k / Q) * 4 + size_t(d.k) * 2 + 16 * 4 + size_t(16) * STAGES * 8 + size_t(per + 16) * MR * kRows * 4;
       p.rc = p.smem > 227 * 1024 ? 40 : 0;
       // one ceiling for every shape of this instantiation: plans of other shapes are cached and never set it again
@@ -627,8 +634,8 @@ int launch_rowthread_mr(PlaneGemvDesc const& d, cudaStream_t stream) {
         cuuint64_t const rb = cuuint64_t(d.k) * LO / 8;
         cuuint64_t dims[3] = {rb, cuuint64_t(d.n), cuuint64_t(E)};
         cuuint64_t str[2] = {rb, rb * d.n};
-        cuuint32_t box[3] = {cuuint32_t(kSlice * LO / 8), cuuint32_t(kRows), 1};
-        if (!tma_make_map(&nm.lo, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.low, dims, str, box, tma_row_swizzle(kSlice * LO / 8))) return kRuntimeError;
+        cuuint32_t box[3] = {cuuint32_t(KS * LO / 8), cuuint32_t(kRows), 1};
+        if (!tma_make_map(&nm.lo, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.low, dims, str, box, tma_row_swizzle(KS * LO / 8))) return kRuntimeError;
       }
       if constexpr (HI != 0) {
         cuuint64_t const rb = cuuint64_t(d.k) * HI / 8;
@@ -644,7 +651,7 @@ int launch_rowthread_mr(PlaneGemvDesc const& d, cudaStream_t stream) {
         cuuint64_t const kg = cuuint64_t(d.k / d.group_size);
         cuuint64_t dims[3] = {cuuint64_t(d.n), kg, cuuint64_t(E)};
         cuuint64_t str[2] = {cuuint64_t(d.n) * 2, cuuint64_t(d.n) * 2 * kg};
-        cuuint32_t box[3] = {cuuint32_t(kRows), cuuint32_t(std::max(1, kSlice / d.group_size)), 1};
+        cuuint32_t box[3] = {cuuint32_t(kRows), cuuint32_t(std::max(1, KS / d.group_size)), 1};
         if (!tma_make_map(&nm.sc, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, d.scale, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
         if (d.zero && !tma_make_map(&nm.zr, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, d.zero, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
       }
@@ -654,7 +661,7 @@ int launch_rowthread_mr(PlaneGemvDesc const& d, cudaStream_t stream) {
   }
   RtArgs a{};
   a.d = d;
-  a.ns = d.k / kSlice; a.nblocks = (d.n + kRows - 1) / kRows;
+  a.ns = d.k / KS; a.nblocks = (d.n + kRows - 1) / kRows;
   a.status = rt_device_status_ptr();
   if (!a.status) return kRuntimeError;
   // Programmatic dependent launch: this kernel may be scheduled while the previous kernel of the stream drains; it reads
@@ -672,14 +679,14 @@ int launch_rowthread_mr(PlaneGemvDesc const& d, cudaStream_t stream) {
 
 // Rows per weight pass: several rows of one expert (or of a dense batch) share every tile when there are enough of them;
 // a long K may leave no room for four rows of activations, then every row streams the weights itself.
-template <int LO, int HI, int MODE, int QT, int NQ>
+template <int LO, int HI, int MODE, int QT, int NQ, int SL = 1>
 int launch_rowthread(PlaneGemvDesc const& d, cudaStream_t stream) {
   bool const many = d.offsets ? d.m_rows >= 2 * std::max(1, d.experts) : d.m_rows >= 2;
   if (many) {
-    int const rc = launch_rowthread_mr<LO, HI, MODE, QT, NQ, 4>(d, stream);
+    int const rc = launch_rowthread_mr<LO, HI, MODE, QT, NQ, 4, SL>(d, stream);
     if (rc != 40) return rc;
   }
-  return launch_rowthread_mr<LO, HI, MODE, QT, NQ, 1>(d, stream);
+  return launch_rowthread_mr<LO, HI, MODE, QT, NQ, 1, SL>(d, stream);
 }
 
 }  // namespace
@@ -706,6 +713,15 @@ int enqueue_rowthread_gemv(PlaneGemvDesc const& d, cudaStream_t s) {
   int const gs = d.group_size;
   if (gs < 16 || (gs & (gs - 1)) || d.k % gs) return 40;
   int const nq = gs >= 64 ? 1 : 64 / gs;
+  // a lone 2- or 1-bit plane takes 512- or 1024-code tiles (1 KB, as the 4-bit plane's) when K is a multiple of them
+  if (d.hi_bits == 0 && d.lo_bits == 2 && d.k % 512 == 0 && gs >= 32) {
+    int const rc = gs >= 64 ? launch_rowthread<2, 0, 0, 0, 2, 2>(d, s) : launch_rowthread<2, 0, 0, 0, 4, 2>(d, s);
+    if (rc != 40) return rc;
+  }
+  if (d.hi_bits == 0 && d.lo_bits == 1 && d.k % 1024 == 0 && gs >= 64) {
+    int const rc = launch_rowthread<1, 0, 0, 0, 4, 4>(d, s);
+    if (rc != 40) return rc;
+  }
   int const key = d.lo_bits * 100 + d.hi_bits * 10 + nq;
   switch (key) {
     case 401: return launch_rowthread<4, 0, 0, 0, 1>(d, s);
