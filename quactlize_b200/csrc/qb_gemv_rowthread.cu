@@ -79,10 +79,10 @@ __device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
 }
 // bytes one ring stage keeps for a tile's scale channel: fp16 scale and zero of 8 rows x up to 4 * NQ groups (two halves),
 // or the packed units of 8 rows
-template <int MODE, int QT, int NQ>
+template <int MODE, int QT, int NQ, int WR>
 constexpr int sc_tile_bytes() {
-  if constexpr (MODE == 0) return NQ <= 2 ? 256 : NQ * 128;      // each half starts 128-byte aligned, as a tiled copy's destination must
-  else return kRows * kq::Unit<QT>::kUnitTotal;                  // an untiled bulk copy needs 16-byte alignment only
+  if constexpr (MODE == 0) return NQ * WR <= 2 ? 256 : NQ * WR * 128;   // each half starts 128-byte aligned, as a tiled copy's destination must
+  else return kRows * WR * kq::Unit<QT>::kUnitTotal;             // an untiled bulk copy needs 16-byte alignment only
 }
 __device__ __forceinline__ float lds_f32(uint32_t addr) {
   float v;
@@ -145,7 +145,9 @@ __device__ __forceinline__ uint32_t bits_at(uint32_t const* u, int bit) {
 // MR activation rows share every weight tile (1, or up to 4 rows of one expert)
 // SL: 256-code slices per tile (1; 2 or 4 for a lone 2- or 1-bit plane, whose tile then is 1 KB like the 4-bit one and the
 // per-tile bookkeeping is paid per 512 / 1024 codes); NQ counts the runs of one lane's 64*SL codes
-template <int LO, int HI, int MODE, int QT, int NQ, int STAGES, int MR, int SL>
+// WR: weight rows per lane (1, or 2: tile rows r and r + 8 of a 16-row tile share the lane's activation operands and every
+// per-tile step -- wait, copy issue, scale addressing -- is paid once per two rows)
+template <int LO, int HI, int MODE, int QT, int NQ, int STAGES, int MR, int SL, int WR>
 __global__ void __launch_bounds__(512, 1)
 rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_constant__ CUtensorMap map_hi,
                       const __grid_constant__ CUtensorMap map_sc, const __grid_constant__ CUtensorMap map_zr, RtArgs a) {
@@ -159,8 +161,9 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   constexpr int U = Q < 32 ? Q : 32;                  // codes per fp16 accumulation run (then fp32)
   constexpr int NU = KP / U;
   constexpr int RBL = 32 * LO * SL, RBH = HI ? 32 * HI : 32;           // bytes of a tile row
-  constexpr int LO_TILE = kRows * RBL, HI_TILE = HI ? kRows * RBH : 0;
-  constexpr int SC_TILE = sc_tile_bytes<MODE, QT, NQ>(), SC_HALF = SC_TILE / 2;   // scale channel of one tile, copied with it
+  constexpr int TR = kRows * WR;                                       // rows of a tile
+  constexpr int LO_TILE = TR * RBL, HI_TILE = HI ? TR * RBH : 0;
+  constexpr int SC_TILE = sc_tile_bytes<MODE, QT, NQ, WR>(), SC_HALF = SC_TILE / 2;   // scale channel of one tile, copied with it
   static_assert(CWL <= U, "a low-plane word must not straddle accumulation runs");
   constexpr bool kCrossHi = HI && CWH > U;            // a high word spans two runs (1-bit plane, 16-code groups)
   static_assert(!kCrossHi || CWH == 2 * U, "a high-plane word may span at most two runs");
@@ -242,7 +245,7 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   uint16_t* xraw = reinterpret_cast<uint16_t*>(sxq + MR * (k / Q));      // [k] raw activations (prologue only, one row at a time)
   float* red = reinterpret_cast<float*>(xraw + k);                       // [16]
   uint64_t* bars = reinterpret_cast<uint64_t*>(red + 16);                // [W][STAGES]
-  float* part = reinterpret_cast<float*>(bars + W * STAGES);             // [blocks of this CTA + 16][MR][kRows]
+  float* part = reinterpret_cast<float*>(bars + W * STAGES);             // [blocks of this CTA + 16][MR][TR]
   (void)xhi;
 
   // ---- this warp's share of the work ------------------------------------------------------------------------------------
@@ -262,8 +265,8 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   int const b_first = ntiles > 0 ? t0 / ns : 0, s_first = ntiles > 0 ? t0 % ns : 0;
   // next tile to request (lane 0 only): everything the copy needs is kept in registers and advanced by additions
   int is_s = s_first;
-  int is_row0 = (blockIdx.x + b_first * gridDim.x) * kRows;
-  int const row_step = gridDim.x * kRows;
+  int is_row0 = (blockIdx.x + b_first * gridDim.x) * TR;
+  int const row_step = gridDim.x * TR;
   uint32_t const bar_a = smem_u32(mybars), ring_lo_a = smem_u32(mylo), ring_hi_a = smem_u32(myhi), ring_sc_a = smem_u32(mysc);
   uint64_t const map_lo_p = reinterpret_cast<uint64_t>(&map_lo), map_hi_p = reinterpret_cast<uint64_t>(&map_hi);
   uint64_t const map_sc_p = reinterpret_cast<uint64_t>(&map_sc), map_zr_p = reinterpret_cast<uint64_t>(&map_zr);
@@ -275,7 +278,7 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   bool const has_zero = MODE == 0 && d.zero != nullptr;
   using UnitT = kq::Unit<(MODE == 1 ? QT : 12)>;
   int const sc_groups = MODE == 0 ? max(1, KS >> gshift) : 0;
-  uint32_t const tx_bytes = LO_TILE + HI_TILE + (MODE == 0 ? uint32_t(sc_groups) * 16u * (has_zero ? 2u : 1u) : uint32_t(kRows * UnitT::kUnitTotal));
+  uint32_t const tx_bytes = LO_TILE + HI_TILE + (MODE == 0 ? uint32_t(sc_groups) * uint32_t(TR * 2) * (has_zero ? 2u : 1u) : uint32_t(TR * UnitT::kUnitTotal));
   uint8_t const* const un_e = MODE == 1 ? d.units + size_t(e) * ((k / 256) / UnitT::kSbPerUnit) * n * UnitT::kUnitTotal : nullptr;
   // called with q = 0, 1, 2, ... in order; every lane keeps the (uniform) bookkeeping, lane 0 issues the copies
   auto issue = [&](int q) {
@@ -292,7 +295,7 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
       } else {
         uint8_t const* src = un_e + (size_t(is_s / UnitT::kSbPerUnit) * n + is_row0) * UnitT::kUnitTotal;
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                     ::"r"(ring_sc_a + st * SC_TILE), "l"(src), "n"(kRows * UnitT::kUnitTotal), "r"(bar) : "memory");
+                     ::"r"(ring_sc_a + st * SC_TILE), "l"(src), "n"(TR * UnitT::kUnitTotal), "r"(bar) : "memory");
       }
       asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
                    ::"r"(ring_lo_a + st * LO_TILE), "l"(map_lo_p), "r"(bar), "r"(is_s * (KS * LO / 8)), "r"(is_row0), "r"(e) : "memory");
@@ -332,7 +335,7 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   };
   if (nrows == 1) start_stream();
-  for (int i = threadIdx.x; i < (nb_c + 16) * MR * kRows; i += blockDim.x) part[i] = 0.f;
+  for (int i = threadIdx.x; i < (nb_c + 16) * MR * TR; i += blockDim.x) part[i] = 0.f;
 
   // ---- CTA prologue: activations into pattern order, one activation row at a time ---------------------------------------
   float fm[MR];
@@ -386,22 +389,26 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   else prologue(std::false_type{});
 
   // ---- where this lane finds its runs' scales inside the staged scale channel (fixed per lane) -----------------------------
+  // (weight row w of the lane is tile row r + 8*w: 16 bytes further in a scale row, 8 units further in the packed units)
   uint32_t sc_off[MODE == 0 ? NQ : 1];
   if constexpr (MODE == 0) {
 #pragma unroll
-    for (int j = 0; j < NQ; ++j) sc_off[j] = uint32_t(gs <= KS ? (kp * KP + j * Q) >> gshift : 0) * 16u + uint32_t(r) * 2u;
+    for (int j = 0; j < NQ; ++j) sc_off[j] = uint32_t(gs <= KS ? (kp * KP + j * Q) >> gshift : 0) * uint32_t(TR * 2) + uint32_t(r) * 2u;
   } else {
     sc_off[0] = uint32_t(r) * UnitT::kUnitTotal;
   }
   constexpr int NSC = MODE == 0 ? NQ : 5;
+  constexpr uint32_t SC_ROW8 = MODE == 0 ? 16u : 8u * UnitT::kUnitTotal;   // from tile row r to tile row r + 8
   uint32_t const sc_a = smem_u32(mysc);
 
   float const coff = float(d.code_offset);
   bool dead = false;
   int q = 0;
-  float tot[MR];
+  float tot[MR][WR];
 #pragma unroll
-  for (int m = 0; m < MR; ++m) tot[m] = 0.f;
+  for (int m = 0; m < MR; ++m)
+#pragma unroll
+    for (int w = 0; w < WR; ++w) tot[m][w] = 0.f;
   uint32_t offl[2], offh[2];
   part_offsets<RBL>(r, kp, offl);
   part_offsets<RBH>(r, kp, offh);
@@ -410,13 +417,15 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   // a warp's sums for one block go to slot (block + warp): runs are contiguous and ordered, so slots never collide
   auto flush = [&](int bi) {
 #pragma unroll
-    for (int m = 0; m < MR; ++m) {
-      float v = tot[m];
-      v += __shfl_xor_sync(0xffffffffu, v, 8);
-      v += __shfl_xor_sync(0xffffffffu, v, 16);
-      if (lane < kRows) part[((bi + warp) * MR + m) * kRows + lane] = v;
-      tot[m] = 0.f;
-    }
+    for (int m = 0; m < MR; ++m)
+#pragma unroll
+      for (int w = 0; w < WR; ++w) {
+        float v = tot[m][w];
+        v += __shfl_xor_sync(0xffffffffu, v, 8);
+        v += __shfl_xor_sync(0xffffffffu, v, 16);
+        if (lane < kRows) part[((bi + warp) * MR + m) * TR + 8 * w + lane] = v;
+        tot[m][w] = 0.f;
+      }
   };
   for (int bi = b_first, s_begin = s_first; q < ntiles; ++bi, s_begin = 0) {
    int const s_end = min(ns, s_begin + (ntiles - q));
@@ -424,75 +433,86 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
     uint32_t const st = uint32_t(q) & (STAGES - 1);
     if (!mbar_wait_bounded(&mybars[st], unsigned(q / STAGES) & 1u, a.status, kWaitStageTimeout)) { dead = true; break; }
     int const pt = s * (KS / KP) + kp;
-    uint32_t wl[NWL], wh[NWH];
-    load_part<RBL>(lo_a + st * LO_TILE, offl, wl);
-    if constexpr (HI != 0) load_part<RBH>(hi_a + st * HI_TILE, offh, wh);
-    uint32_t cur[NSC];                                       // MODE 0: scale | zero << 16 per run; MODE 1: the superblock's scale bytes
-    if constexpr (MODE == 0) {
+    uint32_t wl[WR][NWL], wh[WR][NWH];
+    uint32_t cur[WR][NSC];                                   // MODE 0: scale | zero << 16 per run; MODE 1: the superblock's scale bytes
 #pragma unroll
-      for (int j = 0; j < NQ; ++j) {
-        uint32_t const at = sc_a + st * SC_TILE + sc_off[j];
-        cur[j] = lds_u16(at) | (lds_u16(at + SC_HALF) << 16);        // the zero half holds zeros when there is no zero plane
-      }
-    } else {
-      uint32_t const at = sc_a + st * SC_TILE + sc_off[0] + uint32_t(s % UnitT::kSbPerUnit) * UnitT::kSbBytes;
+    for (int w = 0; w < WR; ++w) {
+      load_part<RBL>(lo_a + st * LO_TILE + w * (8 * RBL), offl, wl[w]);      // the swizzle pattern repeats every 8 rows
+      if constexpr (HI != 0) load_part<RBH>(hi_a + st * HI_TILE + w * (8 * RBH), offh, wh[w]);
+      if constexpr (MODE == 0) {
 #pragma unroll
-      for (int i = 0; i < NSC; ++i) cur[i] = 0u;
+        for (int j = 0; j < NQ; ++j) {
+          uint32_t const at = sc_a + st * SC_TILE + sc_off[j] + w * SC_ROW8;
+          cur[w][j] = lds_u16(at) | (lds_u16(at + SC_HALF) << 16);   // the zero half holds zeros when there is no zero plane
+        }
+      } else {
+        uint32_t const at = sc_a + st * SC_TILE + sc_off[0] + w * SC_ROW8 + uint32_t(s % UnitT::kSbPerUnit) * UnitT::kSbBytes;
 #pragma unroll
-      for (int i = 0; i < (UnitT::kSbBytes + 3) / 4; ++i) {
-        uint32_t const lo16 = lds_u16(at + 4 * i);
-        uint32_t const hi16 = (4 * i + 2 < UnitT::kSbBytes) ? lds_u16(at + 4 * i + 2) : 0u;
-        cur[i] = lo16 | (hi16 << 16);
+        for (int i = 0; i < NSC; ++i) cur[w][i] = 0u;
+#pragma unroll
+        for (int i = 0; i < (UnitT::kSbBytes + 3) / 4; ++i) {
+          uint32_t const lo16 = lds_u16(at + 4 * i);
+          uint32_t const hi16 = (4 * i + 2 < UnitT::kSbBytes) ? lds_u16(at + 4 * i + 2) : 0u;
+          cur[w][i] = lo16 | (hi16 << 16);
+        }
       }
     }
     // Once the loads above have returned, the slot can be refilled while the rows are multiplied.  The mov reads one word of
     // every load instruction, so it cannot issue before they have completed for the whole warp; the copy is issued after it.
     {
-      uint32_t dep = wl[0] ^ wl[NWL - 1] ^ (HI ? wh[0] : 0u), sink;
+      uint32_t dep = 0u, sink;
 #pragma unroll
-      for (int i = 0; i < (MODE == 0 ? NQ : (UnitT::kSbBytes + 3) / 4); ++i) dep ^= cur[i];
+      for (int w = 0; w < WR; ++w) {
+        dep ^= wl[w][0] ^ wl[w][NWL - 1] ^ (HI ? wh[w][0] : 0u);
+#pragma unroll
+        for (int i = 0; i < (MODE == 0 ? NQ : (UnitT::kSbBytes + 3) / 4); ++i) dep ^= cur[w][i];
+      }
       asm volatile("mov.u32 %0, %1;" : "=r"(sink) : "r"(dep) : "memory");
       __syncwarp();
       if (q + STAGES < ntiles) issue(q + STAGES);
     }
-    // scale channel of this lane's NQ runs, decoded once for all rows: weight = sv * (code + off) + zv
-    float sv[NQ], zv[NQ], ov[NQ];
+    // scale channel of this lane's NQ runs, decoded once for all activation rows: weight = sv * (code + off) + zv
+    float sv[WR][NQ], oz[WR][NQ];                            // scale, and (code offset * scale + zero)
 #pragma unroll
-    for (int j = 0; j < NQ; ++j) {
-      if constexpr (MODE == 0) {
-        float2 const sz = __half22float2(u32_as_h2(cur[j]));
-        sv[j] = sz.x; zv[j] = sz.y; ov[j] = coff * sz.x;
-      } else {
-        using F = kq::Fmt<QT>;
-        using UU = kq::Unit<QT>;
-        int const grp = kp * NQ + j;                     // group inside the superblock
-        float2 const dd = __half22float2(u32_as_h2(cur[0]));         // (d, dmin); dmin lane meaningless without a min
-        uint32_t const sraw = bits_at<5>(cur, UU::bit_of(grp, 0)) & ((1u << F::kScaleBits) - 1u);
-        int sc = int(sraw);
-        if constexpr (F::kSignedScale) sc = int(int8_t(sraw));
-        sc -= F::kScaleBias;
-        sv[j] = dd.x * float(sc);
-        ov[j] = -float(F::kCodeBias) * sv[j];
-        zv[j] = 0.f;
-        if constexpr (F::kHasMin) {
-          uint32_t const mraw = bits_at<5>(cur, UU::bit_of(grp, 1)) & ((1u << F::kMinBits) - 1u);
-          zv[j] = -dd.y * float(mraw);
+    for (int w = 0; w < WR; ++w)
+#pragma unroll
+      for (int j = 0; j < NQ; ++j) {
+        if constexpr (MODE == 0) {
+          float2 const sz = __half22float2(u32_as_h2(cur[w][j]));
+          sv[w][j] = sz.x; oz[w][j] = fmaf(coff, sz.x, sz.y);
+        } else {
+          using F = kq::Fmt<QT>;
+          using UU = kq::Unit<QT>;
+          int const grp = kp * NQ + j;                     // group inside the superblock
+          float2 const dd = __half22float2(u32_as_h2(cur[w][0]));    // (d, dmin); dmin lane meaningless without a min
+          uint32_t const sraw = bits_at<5>(cur[w], UU::bit_of(grp, 0)) & ((1u << F::kScaleBits) - 1u);
+          int sc = int(sraw);
+          if constexpr (F::kSignedScale) sc = int(int8_t(sraw));
+          sc -= F::kScaleBias;
+          sv[w][j] = dd.x * float(sc);
+          float zz = 0.f;
+          if constexpr (F::kHasMin) {
+            uint32_t const mraw = bits_at<5>(cur[w], UU::bit_of(grp, 1)) & ((1u << F::kMinBits) - 1u);
+            zz = -dd.y * float(mraw);
+          }
+          oz[w][j] = -float(F::kCodeBias) * sv[w][j] + zz;
         }
       }
-    }
 #pragma unroll
     for (int m = 0; m < MR; ++m) {
       if (MR > 1 && m >= nrows) continue;                // uniform for the CTA
-      float usum[NU];
+      float usum[WR][NU];
       uint32_t const xp = xlo_a + uint32_t(m) * xrow + uint32_t(pt) * KPS;
       uint32_t const xq = xhi_a + uint32_t(m) * xrow + uint32_t(pt) * KPS;
       (void)xq;
 #pragma unroll
       for (int u = 0; u < NU; ++u) {
-        // two independent fp16 chains per run (even and odd words) when the run has several words: half the dependent
-        // latency, half the products per fp16 accumulator
+        // two independent fp16 chains per run and weight row (even and odd words) when the run has several words: half the
+        // dependent latency, half the products per fp16 accumulator.  The operands of a word are loaded once for both rows.
         constexpr int WPR = U / CWL;                      // low-plane words per run
-        __half2 acc = __float2half2_rn(0.f), acc_b = __float2half2_rn(0.f);
+        __half2 acc[WR], acc_b[WR];
+#pragma unroll
+        for (int w = 0; w < WR; ++w) { acc[w] = __float2half2_rn(0.f); acc_b[w] = __float2half2_rn(0.f); }
 #pragma unroll
         for (int wi = u * WPR; wi < (u + 1) * WPR; ++wi) {
           __half2 xs[NPL];
@@ -501,10 +521,16 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
             uint4 const xv = lds128_a(xp + wi * (NPL * 4) + v * 16);
             xs[4 * v] = u32_as_h2(xv.x); xs[4 * v + 1] = u32_as_h2(xv.y); xs[4 * v + 2] = u32_as_h2(xv.z); xs[4 * v + 3] = u32_as_h2(xv.w);
           }
-          if (WPR > 1 && (wi & 1)) acc_b = rt_acc_word<LO>(wl[wi], xs, acc_b);
-          else acc = rt_acc_word<LO>(wl[wi], xs, acc);
+#pragma unroll
+          for (int w = 0; w < WR; ++w) {
+            if (WPR > 1 && (wi & 1)) acc_b[w] = rt_acc_word<LO>(wl[w][wi], xs, acc_b[w]);
+            else acc[w] = rt_acc_word<LO>(wl[w][wi], xs, acc[w]);
+          }
         }
-        if constexpr (WPR > 1) acc = __hadd2(acc, acc_b);
+        if constexpr (WPR > 1) {
+#pragma unroll
+          for (int w = 0; w < WR; ++w) acc[w] = __hadd2(acc[w], acc_b[w]);
+        }
         if constexpr (HI != 0 && !kCrossHi) {
 #pragma unroll
           for (int wi = u * (U / CWH); wi < (u + 1) * (U / CWH); ++wi) {
@@ -514,10 +540,12 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
               uint4 const xv = lds128_a(xq + wi * (NPH * 4) + v * 16);
               xs[4 * v] = u32_as_h2(xv.x); xs[4 * v + 1] = u32_as_h2(xv.y); xs[4 * v + 2] = u32_as_h2(xv.z); xs[4 * v + 3] = u32_as_h2(xv.w);
             }
-            acc = rt_acc_word<(HI ? HI : 1)>(wh[wi], xs, acc);
+#pragma unroll
+            for (int w = 0; w < WR; ++w) acc[w] = rt_acc_word<(HI ? HI : 1)>(wh[w][wi], xs, acc[w]);
           }
         }
-        usum[u] = h2_sum(acc);
+#pragma unroll
+        for (int w = 0; w < WR; ++w) usum[w][u] = h2_sum(acc[w]);
       }
       if constexpr (kCrossHi) {                         // the low half-lane of a high word is run 2w, the high one run 2w+1
 #pragma unroll
@@ -528,19 +556,25 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
             uint4 const xv = lds128_a(xq + wi * (NPH * 4) + v * 16);
             xs[4 * v] = u32_as_h2(xv.x); xs[4 * v + 1] = u32_as_h2(xv.y); xs[4 * v + 2] = u32_as_h2(xv.z); xs[4 * v + 3] = u32_as_h2(xv.w);
           }
-          float2 const f = __half22float2(rt_acc_word<(HI ? HI : 1)>(wh[wi], xs, __float2half2_rn(0.f)));
-          usum[2 * wi] += f.x; usum[2 * wi + 1] += f.y;
+#pragma unroll
+          for (int w = 0; w < WR; ++w) {
+            float2 const f = __half22float2(rt_acc_word<(HI ? HI : 1)>(wh[w][wi], xs, __float2half2_rn(0.f)));
+            usum[w][2 * wi] += f.x; usum[w][2 * wi + 1] += f.y;
+          }
         }
       }
       // runs -> scale groups
 #pragma unroll
       for (int j = 0; j < NQ; ++j) {
-        float gsum = 0.f;
-#pragma unroll
-        for (int u = j * (NU / NQ); u < (j + 1) * (NU / NQ); ++u) gsum += usum[u];
         float const sx = lds_f32(sxq_a + uint32_t(m) * sx_row + uint32_t(pt * NQ + j) * 4);
-        tot[m] = fmaf(sv[j] * fm[m], gsum, tot[m]);
-        tot[m] = fmaf(ov[j] + zv[j], sx, tot[m]);
+#pragma unroll
+        for (int w = 0; w < WR; ++w) {
+          float gsum = 0.f;
+#pragma unroll
+          for (int u = j * (NU / NQ); u < (j + 1) * (NU / NQ); ++u) gsum += usum[w][u];
+          tot[m][w] = fmaf(sv[w][j] * fm[m], gsum, tot[m][w]);
+          tot[m][w] = fmaf(oz[w][j], sx, tot[m][w]);
+        }
       }
     }
    }
@@ -552,14 +586,14 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
       (void)mbar_wait_bounded(&mybars[i % STAGES], unsigned(i / STAGES) & 1u, nullptr, 0, 250000000ull);
   __syncthreads();
   // ---- every block's contributions, added in warp order (fixed: results do not depend on timing) ------------------------------
-  for (int o = threadIdx.x; o < nb_c * MR * kRows; o += blockDim.x) {
-    int const bi = o / (MR * kRows), m = (o / kRows) % MR, rr = o % kRows;
-    int const row = (blockIdx.x + bi * gridDim.x) * kRows + rr;
+  for (int o = threadIdx.x; o < nb_c * MR * TR; o += blockDim.x) {
+    int const bi = o / (MR * TR), m = (o / TR) % MR, rr = o % TR;
+    int const row = (blockIdx.x + bi * gridDim.x) * TR + rr;
     if (row >= n || m >= nrows) continue;
     float sum = 0.f;
     for (int w2 = 0; w2 < 16; ++w2) {
       int const u0 = int((long long)w2 * T / 16), u1 = int((long long)(w2 + 1) * T / 16);
-      if (u1 > u0 && u0 < (bi + 1) * ns && u1 > bi * ns) sum += part[((bi + w2) * MR + m) * kRows + rr];
+      if (u1 > u0 && u0 < (bi + 1) * ns && u1 > bi * ns) sum += part[((bi + w2) * MR + m) * TR + rr];
     }
     size_t const oi = size_t(arow + m) * n + row;
     if (d.out_kind == 1) reinterpret_cast<float*>(d.out)[oi] = sum;
@@ -571,14 +605,15 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
 struct RtPlan { int gx, rc; size_t smem; };
 struct RtMaps { CUtensorMap lo, hi, sc, zr; };
 
-template <int LO, int HI, int MODE, int QT, int NQ, int MR, int SL>
+template <int LO, int HI, int MODE, int QT, int NQ, int MR, int SL, int WR>
 int launch_rowthread_mr(PlaneGemvDesc const& d, cudaStream_t stream) {
-  constexpr int STAGES = (LO + HI >= 5) ? 4 : 8;     // a power of two; 64-96 KB in flight per SM for the wide tiles
+  constexpr int STAGES = ((LO + HI >= 5) ? 4 : 8) / WR;   // a power of two; 64-96 KB in flight per SM for the wide tiles
   constexpr int KS = kSlice * SL, KP = kPart * SL, KPS = KP * 2 + 16;
   constexpr int Q = KP / NQ;
-  constexpr int LO_TILE = kRows * 32 * LO * SL, HI_TILE = HI ? kRows * 32 * HI : 0;
-  constexpr int SC_TILE = sc_tile_bytes<MODE, QT, NQ>();
-  auto kern = rowthread_gemv_kernel<LO, HI, MODE, QT, NQ, STAGES, MR, SL>;
+  constexpr int TR = kRows * WR;
+  constexpr int LO_TILE = TR * 32 * LO * SL, HI_TILE = HI ? TR * 32 * HI : 0;
+  constexpr int SC_TILE = sc_tile_bytes<MODE, QT, NQ, WR>();
+  auto kern = rowthread_gemv_kernel<LO, HI, MODE, QT, NQ, STAGES, MR, SL, WR>;
   // grid rows: one per group of up to MR activation rows of one expert (ragged: an upper bound, surplus CTAs exit at once)
   int const gy = MR == 1 ? d.m_rows : (d.offsets ? std::min(d.m_rows, d.m_rows / MR + d.experts) : (d.m_rows + MR - 1) / MR);
   if (gy <= 0 || gy > 65535) return 40;
@@ -596,7 +631,7 @@ int launch_rowthread_mr(PlaneGemvDesc const& d, cudaStream_t stream) {
     Key const key{d.n, d.k, gy, dev};
     auto it = plans.find(key);
     if (it == plans.end()) {
-      int const nblocks = (d.n + kRows - 1) / kRows, sms = rt_sm_count();
+      int const nblocks = (d.n + TR - 1) / TR, sms = rt_sm_count();
       int const act_rows = MR == 1 ? gy : std::max(1, (d.m_rows + MR - 1) / MR);    // groups that do work
       int const share = std::max(1, sms / std::max(1, std::min(act_rows, sms)));   // CTAs per activation row: one wave in all
       p.gx = std::max(1, std::min(nblocks, share));
@@ -604,7 +639,7 @@ int launch_rowthread_mr(PlaneGemvDesc const& d, cudaStream_t stream) {
       p.gx = (nblocks + per - 1) / per;
       int const nparts = d.k / KP;
       p.smem = 1024 + size_t(16) * STAGES * (LO_TILE + HI_TILE + SC_TILE) + size_t(MR) * nparts * KPS * (HI ? 2 : 1) +
-               size_t(MR) * (d.k / Q) * 4 + size_t(d.k) * 2 + 16 * 4 + size_t(16) * STAGES * 8 + size_t(per + 16) * MR * kRows * 4;
+               size_t(MR) * (d.k / Q) * 4 + size_t(d.k) * 2 + 16 * 4 + size_t(16) * STAGES * 8 + size_t(per + 16) * MR * TR * 4;
       p.rc = p.smem > 227 * 1024 ? 40 : 0;
       // one ceiling for every shape of this instantiation: plans of other shapes are cached and never set it again
       if (!p.rc && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) { (void)cudaGetLastError(); p.rc = 40; }
@@ -634,14 +669,14 @@ int launch_rowthread_mr(PlaneGemvDesc const& d, cudaStream_t stream) {
         cuuint64_t const rb = cuuint64_t(d.k) * LO / 8;
         cuuint64_t dims[3] = {rb, cuuint64_t(d.n), cuuint64_t(E)};
         cuuint64_t str[2] = {rb, rb * d.n};
-        cuuint32_t box[3] = {cuuint32_t(KS * LO / 8), cuuint32_t(kRows), 1};
+        cuuint32_t box[3] = {cuuint32_t(KS * LO / 8), cuuint32_t(TR), 1};
         if (!tma_make_map(&nm.lo, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.low, dims, str, box, tma_row_swizzle(KS * LO / 8))) return kRuntimeError;
       }
       if constexpr (HI != 0) {
         cuuint64_t const rb = cuuint64_t(d.k) * HI / 8;
         cuuint64_t dims[3] = {rb, cuuint64_t(d.n), cuuint64_t(E)};
         cuuint64_t str[2] = {rb, rb * d.n};
-        cuuint32_t box[3] = {cuuint32_t(kSlice * HI / 8), cuuint32_t(kRows), 1};
+        cuuint32_t box[3] = {cuuint32_t(kSlice * HI / 8), cuuint32_t(TR), 1};
         if (!tma_make_map(&nm.hi, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.high, dims, str, box, tma_row_swizzle(kSlice * HI / 8))) return kRuntimeError;
       } else {
         nm.hi = nm.lo;
@@ -651,7 +686,7 @@ int launch_rowthread_mr(PlaneGemvDesc const& d, cudaStream_t stream) {
         cuuint64_t const kg = cuuint64_t(d.k / d.group_size);
         cuuint64_t dims[3] = {cuuint64_t(d.n), kg, cuuint64_t(E)};
         cuuint64_t str[2] = {cuuint64_t(d.n) * 2, cuuint64_t(d.n) * 2 * kg};
-        cuuint32_t box[3] = {cuuint32_t(kRows), cuuint32_t(std::max(1, KS / d.group_size)), 1};
+        cuuint32_t box[3] = {cuuint32_t(TR), cuuint32_t(std::max(1, KS / d.group_size)), 1};
         if (!tma_make_map(&nm.sc, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, d.scale, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
         if (d.zero && !tma_make_map(&nm.zr, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, d.zero, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
       }
@@ -661,7 +696,7 @@ int launch_rowthread_mr(PlaneGemvDesc const& d, cudaStream_t stream) {
   }
   RtArgs a{};
   a.d = d;
-  a.ns = d.k / KS; a.nblocks = (d.n + kRows - 1) / kRows;
+  a.ns = d.k / KS; a.nblocks = (d.n + TR - 1) / TR;
   a.status = rt_device_status_ptr();
   if (!a.status) return kRuntimeError;
   // Programmatic dependent launch: this kernel may be scheduled while the previous kernel of the stream drains; it reads
@@ -683,10 +718,14 @@ template <int LO, int HI, int MODE, int QT, int NQ, int SL = 1>
 int launch_rowthread(PlaneGemvDesc const& d, cudaStream_t stream) {
   bool const many = d.offsets ? d.m_rows >= 2 * std::max(1, d.experts) : d.m_rows >= 2;
   if (many) {
-    int const rc = launch_rowthread_mr<LO, HI, MODE, QT, NQ, 4, SL>(d, stream);
+    int const rc = launch_rowthread_mr<LO, HI, MODE, QT, NQ, 4, SL, 1>(d, stream);
     if (rc != 40) return rc;
   }
-  return launch_rowthread_mr<LO, HI, MODE, QT, NQ, 1, SL>(d, stream);
+  if (d.n % 16 == 0) {                                 // 16-row tiles, two weight rows per lane
+    int const rc = launch_rowthread_mr<LO, HI, MODE, QT, NQ, 1, SL, 2>(d, stream);
+    if (rc != 40) return rc;
+  }
+  return launch_rowthread_mr<LO, HI, MODE, QT, NQ, 1, SL, 1>(d, stream);
 }
 
 }  // namespace
