@@ -721,6 +721,15 @@ int launch_rowthread(PlaneGemvDesc const& d, cudaStream_t stream) {
     int const rc = launch_rowthread_mr<LO, HI, MODE, QT, NQ, 4, SL, 1>(d, stream);
     if (rc != 40) return rc;
   }
+  if constexpr (HI == 0 && MODE == 0) {
+    // 32-row tiles, four weight rows per lane, where every warp of a CTA still gets two tiles or more
+    int const nb32 = d.n / 32, sms = rt_sm_count();
+    int const ctas = std::max(1, std::min(nb32, std::max(1, sms / std::max(1, std::min(d.m_rows, sms)))));
+    if (d.n % 32 == 0 && (long long)nb32 * (d.k / (kSlice * SL)) / ctas >= 32) {
+      int const rc = launch_rowthread_mr<LO, HI, MODE, QT, NQ, 1, SL, 4>(d, stream);
+      if (rc != 40) return rc;
+    }
+  }
   if (d.n % 16 == 0) {                                 // 16-row tiles, two weight rows per lane
     int const rc = launch_rowthread_mr<LO, HI, MODE, QT, NQ, 1, SL, 2>(d, stream);
     if (rc != 40) return rc;
