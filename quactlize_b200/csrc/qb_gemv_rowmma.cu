@@ -89,7 +89,9 @@ __device__ __forceinline__ uint32_t word_offset(int rr, int w) {
 }
 
 // LO plane bits; WL distinct words per step across a quad (4, 2 or 1); GQ = min(group size, 256) codes
-template <int LO, int WL, int GQ, int STAGES>
+// RB: 16-row blocks per tile (1 or 2).  With two, the activation fragments of an MMA and every per-tile step are shared by
+// 32 weight rows.
+template <int LO, int WL, int GQ, int STAGES, int RB>
 __global__ void __launch_bounds__(512, 1)
 rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_constant__ CUtensorMap map_sc,
                    const __grid_constant__ CUtensorMap map_zr, MmaArgs a) {
@@ -102,9 +104,10 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
   constexpr int MSTEP = WL * NP / 8;                  // MMAs per step
   constexpr int NGT = kTSlice / GQ;                   // scale groups per tile (1, 2, 4 or 8)
   constexpr int NGR = NGT > 4 ? NGT / 4 : 1;          // scale registers per row and lane
-  constexpr int TILE = kTRows * 32 * LO;
+  constexpr int TR = kTRows * RB;                     // weight rows of a tile
+  constexpr int TILE = TR * 32 * LO;
   // fp16 scale, then zero: [group][16 rows], copied with the tile; each half 128-byte aligned (destination of a tiled copy)
-  constexpr int SC_HALF = NGT * kTRows * 2 < 128 ? 128 : NGT * kTRows * 2, SC_TILE = 2 * SC_HALF;
+  constexpr int SC_HALF = NGT * TR * 2 < 128 ? 128 : NGT * TR * 2, SC_TILE = 2 * SC_HALF;
   constexpr int XPAD = LO == 4 ? 24 : 8;              // skew between activation rows: B-fragment loads spread over the banks
   static_assert(S <= GQ && GQ % S == 0, "the codes of one MMA must lie inside one scale group");
   static_assert((STAGES & (STAGES - 1)) == 0, "ring depth is a power of two");
@@ -188,8 +191,8 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
   int const b_first = ntiles > 0 ? t0 / ns : 0, s_first = ntiles > 0 ? t0 % ns : 0;
   // next tile to request (lane 0 only): addresses and coordinates live in registers and advance by additions
   int is_s = s_first;
-  int is_row0 = (blockIdx.x + b_first * gridDim.x) * kTRows;
-  int const row_step = gridDim.x * kTRows;
+  int is_row0 = (blockIdx.x + b_first * gridDim.x) * TR;
+  int const row_step = gridDim.x * TR;
   uint32_t const bar_a = smem_u32(mybars), ring_issue_a = smem_u32(myring);
   uint64_t const map_p = reinterpret_cast<uint64_t>(&map_lo);
   uint64_t const map_sc_p = reinterpret_cast<uint64_t>(&map_sc), map_zr_p = reinterpret_cast<uint64_t>(&map_zr);
@@ -199,7 +202,7 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
   int const gs = d.group_size;
   int const gshift = 31 - __clz(gs);
   bool const has_zero = d.zero != nullptr;
-  uint32_t const tx_bytes = TILE + uint32_t(NGT * kTRows * 2) * (has_zero ? 2u : 1u);   // the boxes' bytes, not the padded halves
+  uint32_t const tx_bytes = TILE + uint32_t(NGT * TR * 2) * (has_zero ? 2u : 1u);   // the boxes' bytes, not the padded halves
   // called with q = 0, 1, 2, ... in order; every lane keeps the (uniform) bookkeeping, lane 0 issues the copies
   auto issue = [&](int q) {
     uint32_t const st = uint32_t(q) & (STAGES - 1), bar = bar_a + st * 8;
@@ -246,7 +249,7 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   };
   if (nrows == 1) start_stream();
-  for (int i = threadIdx.x; i < (nb_c + 16) * kTRows * kCols; i += blockDim.x) part[i] = 0.f;
+  for (int i = threadIdx.x; i < (nb_c + 16) * TR * kCols; i += blockDim.x) part[i] = 0.f;
 
   // ---- CTA prologue: every activation row of the group into pattern order --------------------------------------------------
   auto prologue = [&](auto bf16_tag) {
@@ -296,17 +299,24 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
   uint32_t const sc_a = smem_u32(mysc) + uint32_t(g) * 2;    // this lane's rows g (and g + 8) of the staged scales
   uint32_t const ring_a = smem_u32(myring), xpat_a = smem_u32(xpat) + uint32_t(g) * xrow, sxq_a = smem_u32(sxq) + uint32_t(t) * 8;
   float const coff = float(d.code_offset);
-  float totA[4] = {0.f, 0.f, 0.f, 0.f}, totB[4] = {0.f, 0.f, 0.f, 0.f};
+  float totA[RB][4], totB[RB][4];
+#pragma unroll
+  for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { totA[rb][i] = 0.f; totB[rb][i] = 0.f; }
   bool dead = false;
   int q = 0, cur_b = b_first, c_b = b_first, c_s = s_first;
   float const fm0 = fmv[2 * t], fm1 = fmv[2 * t + 1];
   // a warp's sums for one block go to slot (block + warp): runs are contiguous and ordered, so slots never collide
   auto flush = [&](int bi) {
-    float* p0 = part + (size_t(bi + warp) * kTRows + g) * kCols + 2 * t;
-    *reinterpret_cast<float2*>(p0) = make_float2(fmaf(totA[0], fm0, totB[0]), fmaf(totA[1], fm1, totB[1]));
-    *reinterpret_cast<float2*>(p0 + 8 * kCols) = make_float2(fmaf(totA[2], fm0, totB[2]), fmaf(totA[3], fm1, totB[3]));
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { totA[i] = 0.f; totB[i] = 0.f; }
+    for (int rb = 0; rb < RB; ++rb) {
+      float* p0 = part + (size_t(bi + warp) * TR + 16 * rb + g) * kCols + 2 * t;
+      *reinterpret_cast<float2*>(p0) = make_float2(fmaf(totA[rb][0], fm0, totB[rb][0]), fmaf(totA[rb][1], fm1, totB[rb][1]));
+      *reinterpret_cast<float2*>(p0 + 8 * kCols) = make_float2(fmaf(totA[rb][2], fm0, totB[rb][2]), fmaf(totA[rb][3], fm1, totB[rb][3]));
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { totA[rb][i] = 0.f; totB[rb][i] = 0.f; }
+    }
   };
   for (; q < ntiles; ++q) {
     int const st = q & (STAGES - 1);
@@ -315,13 +325,19 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
     if (bi != cur_b) { flush(cur_b); cur_b = bi; }
     if (!mbar_wait_bounded(&mybars[st], unsigned(q / STAGES) & 1u, a.status, kWaitStageTimeout)) { dead = true; break; }
     uint32_t const tile_a = ring_a + st * TILE;
-    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    float c[RB][4];
+#pragma unroll
+    for (int rb = 0; rb < RB; ++rb) c[rb][0] = c[rb][1] = c[rb][2] = c[rb][3] = 0.f;
     uint32_t dep = 0u;
 #pragma unroll
     for (int j = 0; j < NSTEP; ++j) {
       int const w = j * WL + wsel;                           // word of the row's 256 codes this lane reads in this step
-      uint32_t const w_lo = lds32(tile_a + word_offset<LO>(g, w));
-      uint32_t const w_hi = lds32(tile_a + word_offset<LO>(g + 8, w));
+      uint32_t w_lo[RB], w_hi[RB];
+#pragma unroll
+      for (int rb = 0; rb < RB; ++rb) {                      // the swizzle pattern repeats every 8 rows
+        w_lo[rb] = lds32(tile_a + rb * (16 * 32 * LO) + word_offset<LO>(g, w));
+        w_hi[rb] = lds32(tile_a + rb * (16 * 32 * LO) + word_offset<LO>(g + 8, w));
+      }
       // pattern-order activations of that word: run (s*4 + code/64), word inside the run, then this lane's patterns
       int const code0 = j * S + wsel * CW;
       uint32_t const xw = xpat_a + uint32_t(s * (kTSlice / kXPart) + code0 / kXPart) * kXPartStride + uint32_t((code0 % kXPart) / CW) * (NP * 4);
@@ -329,25 +345,31 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
       for (int i = 0; i < MSTEP; ++i) {
         int const p = i * 2 * L + 2 * lsel;                  // this lane's two patterns of MMA i (compile-time when L == 1)
         int const h = p / PER, o = p % PER;
-        uint32_t const src_lo = w_lo >> (8 * h), src_hi = w_hi >> (8 * h);
         uint32_t const mA = M1 << (o * LO), mB = M1 << ((o + 1) * LO);
-        uint2 const b = lds64(xw + uint32_t(p) * 4);
-        mma16816(c, src_lo & mA, src_hi & mA, src_lo & mB, src_hi & mB, b.x, b.y);
+        uint2 const b = lds64(xw + uint32_t(p) * 4);         // one activation fragment for every row block
+#pragma unroll
+        for (int rb = 0; rb < RB; ++rb) {
+          uint32_t const src_lo = w_lo[rb] >> (8 * h), src_hi = w_hi[rb] >> (8 * h);
+          mma16816(c[rb], src_lo & mA, src_hi & mA, src_lo & mB, src_hi & mB, b.x, b.y);
+        }
       }
       if (((j + 1) * S) % GQ == 0) {                         // a scale group is complete (compile-time condition)
         int const jg = (j * S) / GQ;
-        uint32_t const sat = sc_a + st * SC_TILE + jg * (kTRows * 2);
-        uint32_t const raw_lo = lds_u16(sat) | (lds_u16(sat + SC_HALF) << 16);          // the zero half holds zeros when there is no zero plane
-        uint32_t const raw_hi = lds_u16(sat + 16) | (lds_u16(sat + SC_HALF + 16) << 16);
-        dep ^= raw_lo ^ raw_hi;
-        float2 const lo = __half22float2(u32_as_h2(raw_lo)), hi = __half22float2(u32_as_h2(raw_hi));   // (scale, zero)
         float2 const sx = lds_f32x2(sxq_a + uint32_t(s * NGT + jg) * (kCols * 4));                     // sums of x, columns 2t, 2t+1
-        totA[0] = fmaf(lo.x, c[0], totA[0]); totA[1] = fmaf(lo.x, c[1], totA[1]);
-        totA[2] = fmaf(hi.x, c[2], totA[2]); totA[3] = fmaf(hi.x, c[3], totA[3]);
-        float const oz_lo = fmaf(coff, lo.x, lo.y), oz_hi = fmaf(coff, hi.x, hi.y);
-        totB[0] = fmaf(oz_lo, sx.x, totB[0]); totB[1] = fmaf(oz_lo, sx.y, totB[1]);
-        totB[2] = fmaf(oz_hi, sx.x, totB[2]); totB[3] = fmaf(oz_hi, sx.y, totB[3]);
-        c[0] = c[1] = c[2] = c[3] = 0.f;
+#pragma unroll
+        for (int rb = 0; rb < RB; ++rb) {
+          uint32_t const sat = sc_a + st * SC_TILE + jg * (TR * 2) + rb * 32;
+          uint32_t const raw_lo = lds_u16(sat) | (lds_u16(sat + SC_HALF) << 16);        // the zero half holds zeros when there is no zero plane
+          uint32_t const raw_hi = lds_u16(sat + 16) | (lds_u16(sat + SC_HALF + 16) << 16);
+          dep ^= raw_lo ^ raw_hi;
+          float2 const lo = __half22float2(u32_as_h2(raw_lo)), hi = __half22float2(u32_as_h2(raw_hi));   // (scale, zero)
+          totA[rb][0] = fmaf(lo.x, c[rb][0], totA[rb][0]); totA[rb][1] = fmaf(lo.x, c[rb][1], totA[rb][1]);
+          totA[rb][2] = fmaf(hi.x, c[rb][2], totA[rb][2]); totA[rb][3] = fmaf(hi.x, c[rb][3], totA[rb][3]);
+          float const oz_lo = fmaf(coff, lo.x, lo.y), oz_hi = fmaf(coff, hi.x, hi.y);
+          totB[rb][0] = fmaf(oz_lo, sx.x, totB[rb][0]); totB[rb][1] = fmaf(oz_lo, sx.y, totB[rb][1]);
+          totB[rb][2] = fmaf(oz_hi, sx.x, totB[rb][2]); totB[rb][3] = fmaf(oz_hi, sx.y, totB[rb][3]);
+          c[rb][0] = c[rb][1] = c[rb][2] = c[rb][3] = 0.f;
+        }
       }
     }
     {                                                        // the scale loads have returned before the slot is refilled
@@ -363,14 +385,14 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
       (void)mbar_wait_bounded(&mybars[i % STAGES], unsigned(i / STAGES) & 1u, nullptr, 0, 250000000ull);
   __syncthreads();
   // ---- every block's contributions, added in warp order (fixed: results do not depend on timing) ------------------------------
-  for (int o = threadIdx.x; o < nb_c * kTRows * kCols; o += blockDim.x) {
-    int const bi = o / (kTRows * kCols), col = (o / kTRows) % kCols, rr = o % kTRows;     // consecutive threads: consecutive rows
-    int const row = (blockIdx.x + bi * gridDim.x) * kTRows + rr;
+  for (int o = threadIdx.x; o < nb_c * TR * kCols; o += blockDim.x) {
+    int const bi = o / (TR * kCols), col = (o / TR) % kCols, rr = o % TR;                 // consecutive threads: consecutive rows
+    int const row = (blockIdx.x + bi * gridDim.x) * TR + rr;
     if (row >= n || col >= nrows) continue;
     float sum = 0.f;
     for (int w2 = 0; w2 < 16; ++w2) {
       int const u0 = int((long long)w2 * T / 16), u1 = int((long long)(w2 + 1) * T / 16);
-      if (u1 > u0 && u0 < (bi + 1) * ns && u1 > bi * ns) sum += part[(size_t(bi + w2) * kTRows + rr) * kCols + col];
+      if (u1 > u0 && u0 < (bi + 1) * ns && u1 > bi * ns) sum += part[(size_t(bi + w2) * TR + rr) * kCols + col];
     }
     size_t const oi = size_t(arow + col) * n + row;
     if (d.out_kind == 1) reinterpret_cast<float*>(d.out)[oi] = sum;
@@ -381,12 +403,13 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
 
 struct MmaPlan { int gx, rc; size_t smem; };
 
-template <int LO, int WL, int GQ, int STAGES>
+template <int LO, int WL, int GQ, int STAGES, int RB>
 int launch_rowmma_st(PlaneGemvDesc const& d, cudaStream_t stream) {
-  constexpr int TILE = kTRows * 32 * LO;
+  constexpr int TR = kTRows * RB;
+  constexpr int TILE = TR * 32 * LO;
   constexpr int XPAD = LO == 4 ? 24 : 8;
-  constexpr int SC_TILE = 2 * std::max(128, (kTSlice / GQ) * kTRows * 2);
-  auto kern = rowmma_gemv_kernel<LO, WL, GQ, STAGES>;
+  constexpr int SC_TILE = 2 * std::max(128, (kTSlice / GQ) * TR * 2);
+  auto kern = rowmma_gemv_kernel<LO, WL, GQ, STAGES, RB>;
   // grid rows: one per group of up to 8 activation rows of one expert (ragged: an upper bound, surplus CTAs exit at once)
   int const gy = d.offsets ? std::min(d.m_rows, d.m_rows / kCols + d.experts) : (d.m_rows + kCols - 1) / kCols;
   if (gy <= 0 || gy > 65535) return 40;
@@ -403,7 +426,7 @@ int launch_rowmma_st(PlaneGemvDesc const& d, cudaStream_t stream) {
     Key const key{d.n, d.k, gy, d.m_rows, dev};
     auto it = plans.find(key);
     if (it == plans.end()) {
-      int const nblocks = (d.n + kTRows - 1) / kTRows, sms = rt_sm_count();
+      int const nblocks = (d.n + TR - 1) / TR, sms = rt_sm_count();
       // groups that do work: between rows/8 and one per expert with rows; a ragged launch cannot know, assume the mean
       int const groups = d.offsets ? std::max(1, std::min(d.m_rows, (d.m_rows / kCols + std::min(d.experts, d.m_rows) + 1) / 2))
                                    : (d.m_rows + kCols - 1) / kCols;
@@ -414,7 +437,7 @@ int launch_rowmma_st(PlaneGemvDesc const& d, cudaStream_t stream) {
       int const nparts = d.k / kXPart;
       p.smem = 1024 + size_t(16) * STAGES * (TILE + SC_TILE) + size_t(kCols) * (size_t(nparts) * kXPartStride + XPAD) +
                size_t(d.k / GQ) * kCols * 4 + kCols * 4 + size_t(d.k) * 2 + 16 * 4 + size_t(16) * STAGES * 8 +
-               size_t(per + 16) * kTRows * kCols * 4;
+               size_t(per + 16) * TR * kCols * 4;
       p.rc = p.smem > 227 * 1024 ? 40 : 0;
       if (!p.rc && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) { (void)cudaGetLastError(); p.rc = 40; }
       it = plans.emplace(key, p).first;
@@ -439,13 +462,13 @@ int launch_rowmma_st(PlaneGemvDesc const& d, cudaStream_t stream) {
       cuuint64_t const rb = cuuint64_t(d.k) * LO / 8;
       cuuint64_t dims[3] = {rb, cuuint64_t(d.n), cuuint64_t(E)};
       cuuint64_t str[2] = {rb, rb * d.n};
-      cuuint32_t box[3] = {cuuint32_t(kTSlice * LO / 8), cuuint32_t(kTRows), 1};
+      cuuint32_t box[3] = {cuuint32_t(kTSlice * LO / 8), cuuint32_t(TR), 1};
       if (!tma_make_map(&nm.lo, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.low, dims, str, box, tma_row_swizzle(kTSlice * LO / 8))) return kRuntimeError;
       {                                                     // fp16 [E][k/gs][n]: a box is 16 rows x the groups of one slice
         cuuint64_t const kg = cuuint64_t(d.k / d.group_size);
         cuuint64_t sdims[3] = {cuuint64_t(d.n), kg, cuuint64_t(E)};
         cuuint64_t sstr[2] = {cuuint64_t(d.n) * 2, cuuint64_t(d.n) * 2 * kg};
-        cuuint32_t sbox[3] = {cuuint32_t(kTRows), cuuint32_t(kTSlice / GQ), 1};
+        cuuint32_t sbox[3] = {cuuint32_t(TR), cuuint32_t(kTSlice / GQ), 1};
         if (!tma_make_map(&nm.sc, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, d.scale, sdims, sstr, sbox, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
         nm.zr = nm.sc;
         if (d.zero && !tma_make_map(&nm.zr, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, d.zero, sdims, sstr, sbox, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
@@ -456,7 +479,7 @@ int launch_rowmma_st(PlaneGemvDesc const& d, cudaStream_t stream) {
   }
   MmaArgs a{};
   a.d = d;
-  a.ns = d.k / kTSlice; a.nblocks = (d.n + kTRows - 1) / kTRows;
+  a.ns = d.k / kTSlice; a.nblocks = (d.n + TR - 1) / TR;
   a.status = rt_device_status_ptr();
   if (!a.status) return kRuntimeError;
   // Programmatic dependent launch: this kernel may be scheduled while the previous kernel of the stream drains; it reads
@@ -477,9 +500,14 @@ int launch_rowmma_st(PlaneGemvDesc const& d, cudaStream_t stream) {
 // that streams the weights once per four rows.
 template <int LO, int WL, int GQ>
 int launch_rowmma(PlaneGemvDesc const& d, cudaStream_t stream) {
-  int const rc = launch_rowmma_st<LO, WL, GQ, (LO == 1 ? 8 : 4)>(d, stream);
+  constexpr int ST = LO == 1 ? 8 : 4;
+  if (d.n % 32 == 0) {                                 // 32-row tiles: the same bytes per ring with half the stages
+    int const rc = launch_rowmma_st<LO, WL, GQ, ST / 2, 2>(d, stream);
+    if (rc != 40) return rc;
+  }
+  int const rc = launch_rowmma_st<LO, WL, GQ, ST, 1>(d, stream);
   if constexpr (LO == 4) {
-    if (rc == 40) return launch_rowmma_st<LO, WL, GQ, 2>(d, stream);
+    if (rc == 40) return launch_rowmma_st<LO, WL, GQ, 2, 1>(d, stream);
   }
   return rc;
 }
