@@ -215,10 +215,12 @@ def test_generic_plane_gemv_dense(bits, gs, n, k, dtype):
 
 
 @pytest.mark.parametrize("bits,gs,n,k", [(4, 128, 4096, 4096), (4, 128, 2048, 4096), (4, 128, 64, 3072), (4, 128, 64, 8192),
-                                         (2, 16, 64, 14336), (2, 64, 256, 14336), (1, 64, 1536, 2048), (4, 32, 72, 1024)])
+                                         (2, 16, 64, 14336), (2, 64, 256, 14336), (1, 64, 1536, 2048), (4, 32, 72, 1024),
+                                         (4, 128, 16384, 4096), (2, 64, 16384, 4096), (4, 64, 40, 512)])
 def test_generic_plane_gemv_single_row_shapes(bits, gs, n, k):
     # one activation row through the row-thread kernel: several row blocks per CTA, K split over few / all warps, ragged
-    # last stage of a ring (K not a multiple of 1024), n not a multiple of 8
+    # last stage of a ring (K not a multiple of 1024), n a multiple of 8 only (8-row tiles), of 16 (two weight rows per lane),
+    # and large enough for the 32-row tiles (four weight rows per lane)
     low, scale, zero = synth.group_planes(1, n, k, bits, gs, seed=bits + n)
     x = synth.activations(1, k, seed=4)
     out = qb.gemv_plane(_cuda(x), _cuda(low), None, _cuda(scale), _cuda(zero), bits, 0, gs, out_dtype=torch.float32)
