@@ -184,6 +184,20 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   // Under programmatic dependent launch the activations (and a router's offsets) may be the preceding kernel's output:
   // nothing of them is read before this wait.  Without the launch attribute it returns at once.
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  // The first activation row is requested at once where its index does not depend on the expert look-up (always, except
+  // for ragged groups of several rows): the look-up's own global loads then overlap it.
+  constexpr int kPre = 4;                                   // 16-byte pieces per thread held in registers: K <= 16384 is covered
+  uint4 pre[kPre];
+  bool const early_x = MR == 1 || d.offsets == nullptr;
+  if (early_x) {
+    uint16_t const* x0 = reinterpret_cast<uint16_t const*>(d.act) + size_t(blockIdx.y) * MR * d.k;
+    bool const have = d.offsets != nullptr || int(blockIdx.y) * MR < d.m_rows;
+#pragma unroll
+    for (int j = 0; j < kPre; ++j) {
+      int const i = (int(threadIdx.x) + j * 512) * 8;
+      pre[j] = (have && i < d.k) ? __ldg(reinterpret_cast<uint4 const*>(x0 + i)) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
   if (d.offsets) {
     volatile int* sh = reinterpret_cast<volatile int*>(smem);            // ring space, not yet in use
     if (threadIdx.x < 4) sh[threadIdx.x] = -1;
@@ -308,8 +322,6 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
   // Activation rows are requested BEFORE the weight stream: a load issued after it queues behind the ring's copies
   // (128 KB per SM) and costs a microsecond per row.  Row m + 1 is loaded into registers while row m is converted, and
   // the stream starts as soon as the last row's loads are in flight.
-  constexpr int kPre = 4;                                   // 16-byte pieces per thread held in registers: K <= 16384 is covered
-  uint4 pre[kPre];
   auto load_row = [&](int m) {
     uint16_t const* x0 = reinterpret_cast<uint16_t const*>(d.act) + size_t(arow + m) * k;
 #pragma unroll
@@ -318,7 +330,7 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
       pre[j] = i < k ? __ldg(reinterpret_cast<uint4 const*>(x0 + i)) : make_uint4(0u, 0u, 0u, 0u);
     }
   };
-  load_row(0);
+  if (!early_x) load_row(0);
   if (MODE == 0 && !has_zero) {                             // no copy ever lands in the zero halves: they read as zero
     for (int i = lane; i < STAGES * (SC_HALF / 4); i += 32)
       *reinterpret_cast<uint32_t*>(mysc + (i / (SC_HALF / 4)) * SC_TILE + SC_HALF + (i % (SC_HALF / 4)) * 4) = 0u;
