@@ -187,6 +187,7 @@ __global__ void __launch_bounds__(512, 1) q4k_mma_kernel(const __grid_constant__
     uint16_t const* x0 = reinterpret_cast<uint16_t const*>(a.x) + size_t(arow + m) * k;
 #pragma unroll
     for (int j = 0; j < kPre; ++j) {
+      if (j * 4096 >= k) break;                            // uniform: no thread has a piece j
       int const i = (int(threadIdx.x) + j * 512) * 8;
       pre[j] = i < k ? __ldg(reinterpret_cast<uint4 const*>(x0 + i)) : make_uint4(0u, 0u, 0u, 0u);
     }
@@ -231,6 +232,7 @@ __global__ void __launch_bounds__(512, 1) q4k_mma_kernel(const __grid_constant__
     };
 #pragma unroll
     for (int j = 0; j < kPre; ++j) {
+      if (j * 4096 >= k) break;                            // uniform
       int const i = (int(threadIdx.x) + j * 512) * 8;
       if (i < k) piece(i, cur[j]);
     }
@@ -240,7 +242,10 @@ __global__ void __launch_bounds__(512, 1) q4k_mma_kernel(const __grid_constant__
     __syncthreads();
     mx = 0.f;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) mx = fmaxf(mx, red[i]);
+    for (int i = 0; i < 4; ++i) {                            // red is 16-byte aligned
+      float4 const v = reinterpret_cast<float4 const*>(red)[i];
+      mx = fmaxf(fmaxf(mx, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
+    }
     int const ex = pow2_scale_exponent(mx, 15);
     if (threadIdx.x == 0) fmv[m] = ldexpf(1.f, 24 - ex);
     float const mul = __int_as_float((127 + ex) << 23);
@@ -256,6 +261,7 @@ __global__ void __launch_bounds__(512, 1) q4k_mma_kernel(const __grid_constant__
     };
 #pragma unroll
     for (int j = 0; j < kPre; ++j) {                                     // the pieces are still in registers
+      if (j * 4096 >= k) break;                                          // uniform
       int const i = (int(threadIdx.x) + j * 512) * 8;
       if (i < k) convert(i, cur[j]);
     }

@@ -228,6 +228,7 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
     uint16_t const* x0 = reinterpret_cast<uint16_t const*>(d.act) + size_t(arow + m) * k;
 #pragma unroll
     for (int j = 0; j < kPre; ++j) {
+      if (j * 4096 >= k) break;                            // uniform: no thread has a piece j
       int const i = (int(threadIdx.x) + j * 512) * 8;
       pre[j] = i < k ? __ldg(reinterpret_cast<uint4 const*>(x0 + i)) : make_uint4(0u, 0u, 0u, 0u);
     }
@@ -274,6 +275,7 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
       uint4 const* xg = reinterpret_cast<uint4 const*>(reinterpret_cast<uint16_t const*>(d.act) + size_t(arow + m) * k);
 #pragma unroll
       for (int j = 0; j < kPre; ++j) {
+        if (j * 4096 >= k) break;                          // uniform
         int const i = (int(threadIdx.x) + j * 512) * 8;
         if (i < k) piece(i, cur[j]);
       }
@@ -283,7 +285,10 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
       __syncthreads();
       mx = 0.f;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) mx = fmaxf(mx, red[i]);
+      for (int i = 0; i < 4; ++i) {                            // red is 16-byte aligned
+        float4 const v = reinterpret_cast<float4 const*>(red)[i];
+        mx = fmaxf(fmaxf(mx, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
+      }
       int const ex = pow2_scale_exponent(mx, 15);
       if (threadIdx.x == 0) fmv[m] = ldexpf(1.f, 24 - ex);
       pattern_row<LO, BF>(xraw, xpat + size_t(m) * xrow, k, ex, kXPart, kXPartStride);   // one half2 operand per code pair

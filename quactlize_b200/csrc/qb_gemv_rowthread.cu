@@ -326,6 +326,7 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
     uint16_t const* x0 = reinterpret_cast<uint16_t const*>(d.act) + size_t(arow + m) * k;
 #pragma unroll
     for (int j = 0; j < kPre; ++j) {
+      if (j * 4096 >= k) break;                            // uniform: no thread has a piece j
       int const i = (int(threadIdx.x) + j * 512) * 8;
       pre[j] = i < k ? __ldg(reinterpret_cast<uint4 const*>(x0 + i)) : make_uint4(0u, 0u, 0u, 0u);
     }
@@ -379,6 +380,7 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
       uint4 const* xg = reinterpret_cast<uint4 const*>(reinterpret_cast<uint16_t const*>(d.act) + size_t(arow + m) * k);
 #pragma unroll
       for (int j = 0; j < kPre; ++j) {
+        if (j * 4096 >= k) break;                          // uniform
         int const i = (int(threadIdx.x) + j * 512) * 8;
         if (i < k) piece(i, cur[j]);
       }
@@ -388,7 +390,10 @@ rowthread_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_c
       __syncthreads();
       mx = 0.f;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) mx = fmaxf(mx, red[i]);
+      for (int i = 0; i < 4; ++i) {                            // red is 16-byte aligned
+        float4 const v = reinterpret_cast<float4 const*>(red)[i];
+        mx = fmaxf(fmaxf(mx, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
+      }
       int const ex = pow2_scale_exponent(mx, HI ? 15 - LO : 15);
       fm[m] = ldexpf(1.f, 24 - ex);
       // pass 2: one half2 operand per code pair and mask position, multiplier 2^(ex - shift)
