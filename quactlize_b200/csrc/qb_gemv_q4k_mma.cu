@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(512, 1) q4k_mma_kernel(const __grid_constant__
   // ---- this warp's contiguous run of tiles ----------------------------------------------------------------------------------
   int const nb_c = blockIdx.x < a.nblocks ? (a.nblocks - 1 - blockIdx.x) / gridDim.x + 1 : 0;
   int const T = nb_c * bpr;
-  int const t0 = int((long long)warp * T / 16), t1 = int((long long)(warp + 1) * T / 16);
+  int const t0 = ((warp * T) >> 4), t1 = (((warp + 1) * T) >> 4);
   int const ntiles = t1 - t0;
   uint64_t* mybars = bars + warp * STAGES;
   uint8_t* myring = ring + size_t(warp) * STAGES * kQTile;
@@ -338,7 +338,7 @@ __global__ void __launch_bounds__(512, 1) q4k_mma_kernel(const __grid_constant__
     if (row >= n || col >= nrows) continue;
     float sum = 0.f;
     for (int w2 = 0; w2 < 16; ++w2) {
-      int const u0 = int((long long)w2 * T / 16), u1 = int((long long)(w2 + 1) * T / 16);
+      int const u0 = ((w2 * T) >> 4), u1 = (((w2 + 1) * T) >> 4);
       if (u1 > u0 && u0 < (bi + 1) * bpr && u1 > bi * bpr) sum += part[(size_t(bi + w2) * kQRows + rr) * kQCols + col];
     }
     a.out[size_t(arow + col) * n + row] = sum;

@@ -183,7 +183,7 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
   int const ns = a.ns;
   int const nb_c = blockIdx.x < a.nblocks ? (a.nblocks - 1 - blockIdx.x) / gridDim.x + 1 : 0;
   int const T = nb_c * ns;
-  int const t0 = int((long long)warp * T / 16), t1 = int((long long)(warp + 1) * T / 16);
+  int const t0 = ((warp * T) >> 4), t1 = (((warp + 1) * T) >> 4);
   int const ntiles = t1 - t0;
   uint64_t* mybars = bars + warp * STAGES;
   uint8_t* myring = ring + size_t(warp) * STAGES * TILE;
@@ -396,7 +396,7 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
     if (row >= n || col >= nrows) continue;
     float sum = 0.f;
     for (int w2 = 0; w2 < 16; ++w2) {
-      int const u0 = int((long long)w2 * T / 16), u1 = int((long long)(w2 + 1) * T / 16);
+      int const u0 = ((w2 * T) >> 4), u1 = (((w2 + 1) * T) >> 4);
       if (u1 > u0 && u0 < (bi + 1) * ns && u1 > bi * ns) sum += part[(size_t(bi + w2) * TR + rr) * kCols + col];
     }
     size_t const oi = size_t(arow + col) * n + row;
