@@ -337,7 +337,11 @@ __global__ void __launch_bounds__(512, 1) q4k_mma_kernel(const __grid_constant__
     int const row = (blockIdx.x + bi * gridDim.x) * kQRows + rr;
     if (row >= n || col >= nrows) continue;
     float sum = 0.f;
-    for (int w2 = 0; w2 < 16; ++w2) {
+    // with many blocks per CTA only the warps whose run can touch block bi are visited (a conservative range; the test
+    // below is exact); with one or two blocks the two divisions would cost more than the full loop
+    int w_lo = 0, w_hi = 15;
+    if (nb_c > 2) { w_lo = max(0, (bi * bpr * 16) / T - 1); w_hi = min(15, ((bi + 1) * bpr * 16) / T + 1); }
+    for (int w2 = w_lo; w2 <= w_hi; ++w2) {
       int const u0 = ((w2 * T) >> 4), u1 = (((w2 + 1) * T) >> 4);
       if (u1 > u0 && u0 < (bi + 1) * bpr && u1 > bi * bpr) sum += part[(size_t(bi + w2) * kQRows + rr) * kQCols + col];
     }

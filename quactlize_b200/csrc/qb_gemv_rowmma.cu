@@ -395,7 +395,11 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
     int const row = (blockIdx.x + bi * gridDim.x) * TR + rr;
     if (row >= n || col >= nrows) continue;
     float sum = 0.f;
-    for (int w2 = 0; w2 < 16; ++w2) {
+    // with many blocks per CTA only the warps whose run can touch block bi are visited (a conservative range; the test
+    // below is exact); with one or two blocks the two divisions would cost more than the full loop
+    int w_lo = 0, w_hi = 15;
+    if (nb_c > 2) { w_lo = max(0, (bi * ns * 16) / T - 1); w_hi = min(15, ((bi + 1) * ns * 16) / T + 1); }
+    for (int w2 = w_lo; w2 <= w_hi; ++w2) {
       int const u0 = ((w2 * T) >> 4), u1 = (((w2 + 1) * T) >> 4);
       if (u1 > u0 && u0 < (bi + 1) * ns && u1 > bi * ns) sum += part[(size_t(bi + w2) * TR + rr) * kCols + col];
     }
