@@ -47,6 +47,7 @@ constexpr int kXPartStride = 144;    // bytes between runs (128 + 16: neighbouri
 struct MmaArgs {
   PlaneGemvDesc d;
   int ns, nblocks;                   // K slices per block, 16-row blocks
+  int xrows;                         // activation rows kept in shared memory (1..8): the most any group has
   unsigned int* status;
 };
 
@@ -153,13 +154,13 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
     if (e >= 0) {
       int const r0 = d.offsets[e], r1 = d.offsets[e + 1];
       arow = r0 + sh[1] * kCols;
-      nrows = min(kCols, r1 - arow);
+      nrows = min(min(kCols, a.xrows), r1 - arow);     // (a bound smaller than an expert's rows drops the surplus, as the grid bound does elsewhere)
     }
     __syncthreads();                                  // the scratch has been read before the first copy may land there
     if (e < 0) return;                                // uniform for the CTA
   } else {
     arow = blockIdx.y * kCols;
-    nrows = min(kCols, d.m_rows - arow);
+    nrows = min(min(kCols, a.xrows), d.m_rows - arow);
     if (nrows <= 0) return;
   }
   e = __shfl_sync(0xffffffffu, e, 0);                 // uniform for the compiler too (it was read from shared memory)
@@ -172,7 +173,8 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
   uint8_t* ring = smem;                                                  // [W][STAGES][TILE]
   uint8_t* sc_ring = ring + size_t(W) * STAGES * TILE;                   // [W][STAGES][SC_TILE]
   uint8_t* xpat = sc_ring + size_t(W) * STAGES * SC_TILE;                // [8][xrow]
-  float* sxq = reinterpret_cast<float*>(xpat + size_t(kCols) * xrow);    // [k/GQ][8]
+  // [k/GQ][8]; the rows are skewed by 8 or 24 bytes, so their total is rounded up: the raw row behind is stored 16 bytes at a time
+  float* sxq = reinterpret_cast<float*>(xpat + ((size_t(a.xrows) * xrow + 15) & ~size_t(15)));
   float* fmv = sxq + (k / GQ) * kCols;                                   // [8] 2^(24-ex) per activation row
   uint16_t* xraw = reinterpret_cast<uint16_t*>(fmv + kCols);             // [k] (prologue only)
   float* red = reinterpret_cast<float*>(xraw + k);                       // [16]
@@ -302,7 +304,8 @@ rowmma_gemv_kernel(const __grid_constant__ CUtensorMap map_lo, const __grid_cons
   constexpr uint32_t M1 = ((1u << LO) - 1u) * 0x00010001u;
   int const wsel = t / L, lsel = t % L;                      // which word of the step, which share of its patterns
   uint32_t const sc_a = smem_u32(mysc) + uint32_t(g) * 2;    // this lane's rows g (and g + 8) of the staged scales
-  uint32_t const ring_a = smem_u32(myring), xpat_a = smem_u32(xpat) + uint32_t(g) * xrow, sxq_a = smem_u32(sxq) + uint32_t(t) * 8;
+  uint32_t const ring_a = smem_u32(myring), xpat_a = smem_u32(xpat) + uint32_t(min(g, a.xrows - 1)) * xrow,   // columns beyond the group's rows re-read a held row; their results are dropped
+       sxq_a = smem_u32(sxq) + uint32_t(t) * 8;
   float const coff = float(d.code_offset);
   float totA[RB][4], totB[RB][4];
 #pragma unroll
@@ -425,14 +428,16 @@ int launch_rowmma_st(PlaneGemvDesc const& d, cudaStream_t stream) {
   int const E = d.experts > 0 ? d.experts : 1;
   int dev = 0;
   cudaGetDevice(&dev);
-  struct Key { int n, k, gy, rows, dev; bool operator<(Key const& o) const {
-    return n != o.n ? n < o.n : k != o.k ? k < o.k : gy != o.gy ? gy < o.gy : rows != o.rows ? rows < o.rows : dev < o.dev; } };
+  // activation rows to hold: a dense batch's own count, or the caller's bound on any expert's rows
+  int const xrows = std::max(1, std::min(kCols, d.offsets ? (d.max_rows > 0 ? d.max_rows : kCols) : d.m_rows));
+  struct Key { int n, k, gy, rows, xrows, dev; bool operator<(Key const& o) const {
+    return n != o.n ? n < o.n : k != o.k ? k < o.k : gy != o.gy ? gy < o.gy : rows != o.rows ? rows < o.rows : xrows != o.xrows ? xrows < o.xrows : dev < o.dev; } };
   static std::map<Key, MmaPlan> plans;
   static std::mutex mu;
   MmaPlan p{};
   {
     std::lock_guard<std::mutex> lk(mu);
-    Key const key{d.n, d.k, gy, d.m_rows, dev};
+    Key const key{d.n, d.k, gy, d.m_rows, xrows, dev};
     auto it = plans.find(key);
     if (it == plans.end()) {
       int const nblocks = (d.n + TR - 1) / TR, sms = rt_sm_count();
@@ -444,7 +449,7 @@ int launch_rowmma_st(PlaneGemvDesc const& d, cudaStream_t stream) {
       int const per = std::min(256, (nblocks + p.gx - 1) / p.gx);
       p.gx = (nblocks + per - 1) / per;
       int const nparts = d.k / kXPart;
-      p.smem = 1024 + size_t(16) * STAGES * (TILE + SC_TILE) + size_t(kCols) * (size_t(nparts) * kXPartStride + XPAD) +
+      p.smem = 1024 + size_t(16) * STAGES * (TILE + SC_TILE) + ((size_t(xrows) * (size_t(nparts) * kXPartStride + XPAD) + 15) & ~size_t(15)) +
                size_t(d.k / GQ) * kCols * 4 + kCols * 4 + size_t(d.k) * 2 + 16 * 4 + size_t(16) * STAGES * 8 +
                size_t(per + 16) * TR * kCols * 4;
       p.rc = p.smem > 227 * 1024 ? 40 : 0;
@@ -488,7 +493,7 @@ int launch_rowmma_st(PlaneGemvDesc const& d, cudaStream_t stream) {
   }
   MmaArgs a{};
   a.d = d;
-  a.ns = d.k / kTSlice; a.nblocks = (d.n + TR - 1) / TR;
+  a.ns = d.k / kTSlice; a.nblocks = (d.n + TR - 1) / TR; a.xrows = xrows;
   a.status = rt_device_status_ptr();
   if (!a.status) return kRuntimeError;
   // Programmatic dependent launch: this kernel may be scheduled while the previous kernel of the stream drains; it reads
