@@ -321,3 +321,15 @@ def test_dependent_launch_chain_reads_the_previous_output(rows):
         ref = kq.planes_matmul(mid.float().cpu().numpy(), l2, None, s2, z2, 4, 0, 128)   # from the device's own intermediate
         assert kq.max_rel(out.cpu().numpy(), ref) < TOL
     _wait_ok()
+
+
+@pytest.mark.parametrize("rows", [3, 5, 7, 8, 11])
+@pytest.mark.parametrize("bits,gs,n,k", [(4, 128, 512, 1024), (2, 64, 288, 2048), (1, 64, 256, 1024)])
+def test_generic_plane_gemv_dense_batches(bits, gs, n, k, rows):
+    # small dense batches through the tensor-core kernel: every count of held activation rows (their skewed rows must leave
+    # the regions behind them aligned), more rows than one group holds, n a multiple of 32 and of 16 only
+    low, scale, zero = synth.group_planes(1, n, k, bits, gs, seed=bits * 7 + rows)
+    x = synth.activations(rows, k, seed=9)
+    out = qb.gemv_plane(_cuda(x), _cuda(low), None, _cuda(scale), _cuda(zero), bits, 0, gs, out_dtype=torch.float32)
+    assert kq.max_rel(out.cpu().numpy(), kq.planes_matmul(x, low, None, scale, zero, bits, 0, gs)) < TOL
+    _wait_ok()
