@@ -505,8 +505,20 @@ int launch_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
   auto kern = mixed_gemm_kernel<LO, HI, BF16, MT, NT>;
   size_t const smem = sizeof(GemmSmem<LO, HI, MT, NT>) + 1024;
   static_assert(sizeof(GemmSmem<LO, HI, MT, NT>) + 1024 <= 232448, "shared memory of one CTA");
-  static bool attr_set = false;
-  if (!attr_set) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); attr_set = true; }
+  {  // the opt-in to large dynamic shared memory is a per-device attribute of the function
+    static std::mutex mu;
+    static bool attr_set[kMaxDevices] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { (void)cudaGetLastError(); return kRuntimeError; }
+    std::lock_guard<std::mutex> lock(mu);
+    if (!attr_set[dev]) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return kRuntimeError;
+      }
+      attr_set[dev] = true;
+    }
+  }
   int const mtiles = (d.total_rows + kTM * MT - 1) / (kTM * MT) + (d.experts > 0 ? d.experts : 0);
   if (mtiles > 65535) return 30;
   kern<<<dim3((d.n + kTN * NT - 1) / (kTN * NT), mtiles), 128 + 128 * MT, smem, stream>>>(ma, ml, mh, ms, mz, g);

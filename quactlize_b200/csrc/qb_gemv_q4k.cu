@@ -143,6 +143,9 @@ __global__ void __launch_bounds__(kQ4Warps * 32, 1) q4k_gemv1_kernel(Q4Args a) {
   int const T = blockDim.x, W = T >> 5, warp = __shfl_sync(0xffffffffu, int(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   int const seg = warp % a.S, rslot = warp / a.S;
   int e = 0, arow;
+  // Under programmatic dependent launch the offsets and the activation may be the preceding kernel's output: nothing
+  // of them is read before this wait (it also precedes the early return of surplus CTAs).
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (a.offsets) {
     e = blockIdx.y / a.max_rows;
     int const r = blockIdx.y % a.max_rows, r0 = a.offsets[e], r1 = a.offsets[e + 1];
@@ -152,7 +155,6 @@ __global__ void __launch_bounds__(kQ4Warps * 32, 1) q4k_gemv1_kernel(Q4Args a) {
     arow = blockIdx.y;
   }
 #if defined(QB_ABL_EMPTY)
-  asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x == 0 && blockIdx.x == 0) a.out[0] = 1.f;
   return;
@@ -170,9 +172,7 @@ __global__ void __launch_bounds__(kQ4Warps * 32, 1) q4k_gemv1_kernel(Q4Args a) {
   float* red = reinterpret_cast<float*>(smem + (red32 - s0));
   float* part = reinterpret_cast<float*>(smem + (part32 - s0));
 
-  // ---- 1. activation pieces -> registers, issued BEFORE the weight copies so they do not queue behind them.  Under
-  // programmatic dependent launch the activation may be the preceding kernel's output: wait for it first.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // ---- 1. activation pieces -> registers, issued BEFORE the weight copies so they do not queue behind them.
   int const npieces = k >> 3;
   uint4 const* xg = reinterpret_cast<uint4 const*>(a.x + size_t(arow) * k);
   uint4 pc[kQ4MaxPieces];

@@ -10,7 +10,6 @@ namespace qb {
 static __device__ unsigned int g_wait_status[4];
 
 namespace {
-constexpr int kMaxDevices = 64;
 unsigned int* g_status_ptr[kMaxDevices];
 int g_sm_count[kMaxDevices];
 std::mutex g_mu;

@@ -20,6 +20,7 @@
 namespace qb {
 
 constexpr int kRuntimeError = 41;
+constexpr int kMaxDevices = 64;          // device ordinals that per-device caches are sized for
 
 enum class RtStatus : int { Ok = 0, Allocation = 1, HostToDevice = 2, DeviceToHost = 3, Synchronize = 4,
                             HostAllocation = 5, Launch = 6, DeviceWait = 7 };
