@@ -135,7 +135,8 @@ int quactlize_b200_gemv_plane_dev_v1(void const* act, uint8_t const* low, uint8_
 /* ================================ tensor-core mixed-input GEMM (dense fpA_intB, MoE grouped) ===================== */
 
 /* Config inventory.  quactlize/include/quactlize_ppu_config.h:42-71, quactlize/csrc/device/ppu_dense_backend.cu:603-664.
- * One tensor-core tactic is listed ("256x256x64:tcgen05"; small problems run its 128x128 form); an unknown name logs a decline and runs it. */
+ * Two tensor-core tactics are listed ("256x256x64:tcgen05" and "128x128x64:tcgen05"); a null or empty name lets the
+ * library choose by problem size, an unknown name logs a decline and runs that default. */
 int32_t quactlize_ppu_list_configs(quactlize_ppu_config_v1 const** configs);
 int32_t quactlize_ppu_list_grouped_configs(quactlize_ppu_config_v1 const** configs);
 int32_t quactlize_ppu_list_valid_dense_lowbit_configs_v2(quactlize_ppu_config_v2* configs, int32_t capacity, int m, int n,
@@ -218,7 +219,8 @@ int quactlize_b200_gemm_plane_dev_v1(void const* act, uint8_t const* low, uint8_
 /* No counterpart in the reference.  The fully-quantized dense GEMM of quactlize_ppu_dense_fully_quantized_dev_v1 for
  * callers that cannot allocate device memory and have no workspace to hand over: the fp16 scale/zero planes derived
  * from the packed units go to a fixed array inside the library's device image, QUACTLIZE_B200_STATIC_SCRATCH_BYTES
- * per device.  Enqueues on `stream` and returns; allocates nothing.  37 = the planes (4 * k/group_size * n bytes) exceed
+ * per device (held by every process that loads the library, on every device it uses, until exit, called or not).
+ * Enqueues on `stream` and returns; allocates nothing.  37 = the planes (4 * k/group_size * n bytes) exceed
  * the array; 30 / 33 / 41 as for the regular entry.  The first call on a device looks the array's address up: make it
  * outside stream capture.  All calls on a device share the array (each rewrites what it reads, nothing needs
  * clearing); calls that may overlap in time on one device race on it. */
@@ -226,6 +228,17 @@ int quactlize_b200_gemm_plane_dev_v1(void const* act, uint8_t const* low, uint8_
 int quactlize_b200_dense_fully_quantized_static_v1(uint16_t const* act, uint8_t const* low, uint8_t const* high,
                                                    uint8_t const* units, uint16_t* out, int m, int n, int k, int qtype,
                                                    void* stream);
+
+/* additive: the reference's host ops gguf_unpack and gguf_*_artifact_dequantize (quactlize/csrc/preprocess/thop/
+ * gguf_prepass_ops.cpp:767-799, 1118-1205) as device kernels, bit-exact with their host definitions.
+ * unpack: raw blocks -> codes int8 [count][256] (signed for Q3_K/Q6_K), scale/zero fp16 [count][groups], W = code*scale+zero.
+ * planes_dequantize: Native planes + fp16 planes [E][k/gs][n] -> fp16 [E][n][k] = half(float(u+code_shift)*scale + zero);
+ * zero may be null; k % 8 == 0.  Both enqueue on `stream`, allocate nothing, return 0 = enqueued. */
+int quactlize_b200_unpack_dev_v1(uint8_t const* blocks, int64_t block_bytes, int8_t* codes, uint16_t* scale, uint16_t* zero,
+                                 int count, int qtype, void* stream);
+int quactlize_b200_planes_dequantize_dev_v1(uint8_t const* low, uint8_t const* high, uint16_t const* scale,
+                                            uint16_t const* zero, uint16_t* out, int experts, int n, int k, int bits_lo,
+                                            int bits_hi, int group_size, int code_shift, void* stream);
 
 /* ================================ host-only artifact producers ================================================== */
 
@@ -254,6 +267,15 @@ int quactlize_b200_prepare_gemv(uint8_t const* blocks, uint8_t* low, uint8_t* hi
 /* additive: packed-unit producer without the n % 256 restriction of the GEMM-facing entries. */
 int quactlize_b200_pack_units(uint8_t const* blocks, uint8_t* units, int n, int k, int experts, int qtype);
 
+/* additive: planes placed by the reference's device library (its "xplane" order: 64-column x TileK tiles, a bit
+ * permutation inside each tile, quactlize/include/gguf_bc_vecdot.hpp:34-95) to and from the Native order this library's
+ * kernels read.  One expert per call; n % 64 == 0, k % 256 == 0.  `slot` is the placed code index of logical (n, k). */
+int quactlize_b200_xplane_to_native(uint8_t const* low_placed, uint8_t const* high_placed, uint8_t* low_native,
+                                    uint8_t* high_native, int n, int k, int qtype);
+int quactlize_b200_native_to_xplane(uint8_t const* low_native, uint8_t const* high_native, uint8_t* low_placed,
+                                    uint8_t* high_placed, int n, int k, int qtype);
+long long quactlize_b200_xplane_slot(int qtype, int high, int n, int k, int num_cols);
+
 /* ================================ runtime ======================================================================= */
 
 /* additive: make the NEXT runtime call of the given kind fail on the host (1 alloc, 2 H2D, 3 D2H, 4 sync, 6 launch);
@@ -264,6 +286,10 @@ void quactlize_b200_rt_fail_next(int kind);
 void quactlize_b200_rt_trim(void);
 int quactlize_b200_rt_last_status(void);
 int quactlize_b200_device_wait_status(void);
+/* additive, for tests of the failure path: enqueue a one-CTA kernel that waits on an mbarrier nothing arms and gives
+ * up after limit_ns (1 .. 100 000 000).  The kernel returns normally; the next quactlize_b200_device_wait_status()
+ * reports 41 once, then 0.  No counterpart in the reference (its waits are unbounded). */
+int quactlize_b200_debug_wait_probe(long long limit_ns, void* stream);
 
 #ifdef __cplusplus
 }

@@ -4,8 +4,8 @@ TEST INFRASTRUCTURE ONLY.  Nothing in the product path imports this file or anyt
 tests, the smoke check and the CPU-baseline leg of the benchmark load the resulting library, and only as the
 checker / the timed CPU reference.
 
-The sources are compiled where they lie in the read-only reference checkout (``QUACTLIZE_REFERENCE_ROOT``, else the
-default location coded in ``ref_root()``); nothing is copied.  The reference extension is host C++ that needs
+The sources are compiled where they lie in the read-only reference checkout (``QUACTLIZE_REFERENCE_ROOT`` or ``--ref``,
+else a directory named ``reference`` beside this repository); nothing is copied.  The reference extension is host C++ that needs
 CUTLASS/CuTe *headers* only; the stock CUTLASS tree vendored with flashinfer serves.  Sources compiled
 (paths inside the reference project):
 
@@ -26,7 +26,8 @@ NAME = "quactlize_ref_C"
 
 
 def ref_root() -> str:
-    return os.environ.get("QUACTLIZE_REFERENCE_ROOT", "/root/reference")
+    """The reference checkout: QUACTLIZE_REFERENCE_ROOT, else a directory named `reference` beside this repository."""
+    return os.environ.get("QUACTLIZE_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def built_library():
@@ -60,5 +61,7 @@ def build(verbose: bool = False):
 
 
 if __name__ == "__main__":
+    if "--ref" in sys.argv:
+        os.environ["QUACTLIZE_REFERENCE_ROOT"] = sys.argv[sys.argv.index("--ref") + 1]
     lib = build(verbose="-v" in sys.argv)
     print(lib or "reference checkout not present; nothing built")

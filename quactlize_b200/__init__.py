@@ -25,6 +25,9 @@ __all__ = [
     "gguf_packed_scale_prepass", "gguf_prepare_gemv", "gguf_prepare_fully_quantized_dense",
     "gguf_prepare_fully_quantized_grouped", "gguf_recover_fully_quantized", "gguf_gemv_scale_first",
     "gguf_gemv_scale_first_moe", "gguf_gemv_bc", "gguf_gemv_bc_moe", "gemv_plane", "gguf_backend", "gguf_pack_unit",
+    "gguf_pack_units", "gguf_unit_decode", "gguf_scale_block_shape", "gguf_unpack", "planes_dequantize",
+    "gguf_gemv_artifact_dequantize", "gguf_gemv_artifact_dequantize_scale", "gguf_dense_artifact_dequantize",
+    "gguf_dense_artifact_dequantize_scale", "gguf_grouped_artifact_dequantize",
 ]
 
 
@@ -320,14 +323,169 @@ def gguf_recover_fully_quantized(low, high, units, n: int, k: int, qtype: int):
     return out.to(low.device)
 
 
-def gguf_pack_unit(blocks, n: int, k: int, qtype: int, experts: int = 1):
-    """Raw blocks -> packed scale units [E,U,n,bytes] only (any n)."""
+def gguf_pack_units(blocks, n: int, k: int, qtype: int, experts: int = 1):
+    """Raw blocks -> packed scale units [E,U,n,bytes] only (any n).  Additive: the producer the fully-quantized artifact
+    uses, reachable without building the code planes."""
     g = _geom(qtype)
     b, e = _blocks_cpu(blocks, n, k, g, experts)
     _check((k // 256) % g.sb_per_unit == 0, f"this format needs {g.sb_per_unit} superblocks per copyable unit")
     units = torch.empty((e, k // 256 // g.sb_per_unit, n, g.unit_total), dtype=torch.uint8)
-    _rc(_lib.lib().quactlize_b200_pack_units(_p(b), _p(units), n, k, e, int(qtype)), "gguf_pack_unit")
+    _rc(_lib.lib().quactlize_b200_pack_units(_p(b), _p(units), n, k, e, int(qtype)), "gguf_pack_units")
     return units.to(blocks.device)
+
+
+_HDR_OFF = {10: (80, 82, 0), 11: (108, -1, 96), 12: (0, 2, 4), 13: (0, 2, 4), 14: (208, -1, 192)}   # d, dmin, scale block
+
+
+def gguf_pack_unit(scale_blocks, d, dmin, qtype: int):
+    """GGUF scale block (+ fp16 headers) -> the reordered, byte-neutral packed unit (the reference op of the same name,
+    gguf_prepass_ops.cpp:1253-1311).
+
+    2-D scale_blocks [rows,scale_bytes] with d (and dmin) [rows] -> the row-wise form [rows/P,unit_bytes] (P consecutive
+    rows share a unit for Q3_K/Q6_K); 3-D [N,superblocks,scale_bytes] with headers [N,superblocks] -> the stored
+    artifact [superblocks/P,N,unit_bytes]."""
+    g = _geom(qtype)
+    _u8(scale_blocks, "scale_blocks")
+    _check(scale_blocks.dim() in (2, 3), "scale_blocks must be uint8 [rows,bytes] or [N,superblocks,bytes]")
+    _check(scale_blocks.shape[-1] == g.scale_bytes, "scale_blocks last dim must be the SCALE block")
+    _check(d.dtype == torch.float16, "d must be float16")
+    artifact = scale_blocks.dim() == 3
+    rows = scale_blocks.numel() // g.scale_bytes
+    _check(d.numel() == rows and tuple(d.shape) == tuple(scale_blocks.shape[:-1]), "d must match scale_blocks' leading dimensions")
+    has = dmin is not None and dmin.numel() > 0
+    _check(not g.has_min or has, "this format has a min channel, so dmin is required")
+    _check(not has or (dmin.dtype == torch.float16 and dmin.shape == d.shape), "dmin must be float16 with the same shape as d")
+    ncols, nsb = (scale_blocks.shape[0], scale_blocks.shape[1]) if artifact else (1, rows)
+    _check(nsb % g.sb_per_unit == 0, f"this format packs {g.sb_per_unit} superblocks per unit, so the superblock count "
+                                     f"must be a multiple of that; got {nsb}")
+    # the block-form producer reads the scale block and the headers at their raw offsets: build blocks holding only those
+    d_off, m_off, s_off = _HDR_OFF[int(qtype)]
+    raw = torch.zeros((rows, g.block_bytes), dtype=torch.uint8)
+    raw[:, s_off:s_off + g.scale_bytes] = scale_blocks.reshape(rows, g.scale_bytes).cpu()
+    raw[:, d_off:d_off + 2] = d.reshape(rows).cpu().contiguous().view(torch.uint8).reshape(rows, 2)
+    if g.has_min:
+        raw[:, m_off:m_off + 2] = dmin.reshape(rows).cpu().contiguous().view(torch.uint8).reshape(rows, 2)
+    units = torch.empty((1, nsb // g.sb_per_unit, ncols, g.unit_total), dtype=torch.uint8)
+    _rc(_lib.lib().quactlize_b200_pack_units(_p(raw), _p(units), ncols, nsb * 256, 1, int(qtype)), "gguf_pack_unit")
+    out = units[0] if artifact else units[0, :, 0, :]
+    return out.contiguous().to(scale_blocks.device)
+
+
+def gguf_unit_decode(units, qtype: int, zmul: int):
+    """Packed units -> (scale, zero) fp16, one row per SUPERBLOCK: [superblocks,groups] for the row-wise form
+    [rows,unit_bytes], [N,superblocks,groups] for the artifact form [U,N,unit_bytes] (gguf_prepass_ops.cpp:1314-1359)."""
+    g = _geom(qtype)
+    _u8(units, "units")
+    _check(units.dim() in (2, 3), "units must be uint8 [rows,unit] or artifact [unit_sb,N,unit]")
+    _check(zmul in (-32, -24, -4, 0, 8), "zmul must be one of -32, -24, -4, 0, 8; it is the consumer's complete code correction")
+    _check(units.shape[-1] == g.unit_total, f"this format's unit is {g.unit_total} bytes, got {units.shape[-1]}")
+    u3 = units if units.dim() == 3 else units.unsqueeze(1)            # [U, N, bytes]
+    scale, zero = gguf_packed_scale_prepass(u3, qtype, zmul)          # [1, U*P*groups, N]
+    nu, n = u3.shape[0], u3.shape[1]
+    shape = (nu * g.sb_per_unit, g.groups, n)
+    s = scale.reshape(shape).permute(2, 0, 1).contiguous()
+    z = zero.reshape(shape).permute(2, 0, 1).contiguous()
+    return (s, z) if units.dim() == 3 else (s[0], z[0])
+
+
+def gguf_scale_block_shape(qtype: int):
+    """(scale block bytes, groups, group size, has_min, scale bias, signed) of a k-quant's SCALE block."""
+    g = _geom(qtype)
+    return [g.scale_bytes, g.groups, g.group_size, int(g.has_min), 32 if int(qtype) == 11 else 0, int(int(qtype) == 14)]
+
+
+def _to_cuda(t):
+    return t if t is None or t.is_cuda else t.cuda()
+
+
+def gguf_unpack(blocks, qtype: int):
+    """Raw blocks [rows,type_size] -> (codes int8 [rows,256], scale fp16 [rows,groups], zero fp16 [rows,groups]) with
+    W = code*scale + zero; codes are signed for Q3_K (-4..3) and Q6_K (-32..31).  Runs on the device; CPU tensors are
+    staged through it and the results come back on the CPU."""
+    g = _geom(qtype)
+    _u8(blocks, "blocks", 2)
+    _check(blocks.shape[1] == g.block_bytes, f"this format's raw GGUF block is {g.block_bytes} bytes, got {blocks.shape[1]}")
+    b = _to_cuda(blocks)
+    rows = b.shape[0]
+    codes = torch.empty((rows, 256), dtype=torch.int8, device=b.device)
+    scale = torch.empty((rows, g.groups), dtype=torch.float16, device=b.device)
+    zero = torch.empty_like(scale)
+    if rows:
+        with torch.cuda.device(b.device):
+            _rc(_lib.lib().quactlize_b200_unpack_dev_v1(_p(b), g.block_bytes, _p(codes), _p(scale), _p(zero), rows, int(qtype),
+                                                        _stream(b)), "gguf_unpack")
+    return tuple(t.to(blocks.device) for t in (codes, scale, zero))
+
+
+def planes_dequantize(low, high, scale, zero, bits_lo: int, bits_hi: int, group_size: int, code_shift: int = 0):
+    """Additive: any plane artifact -> fp16 [E,n,k] = half(float(lo + 2^bits_lo*hi + code_shift)*scale + zero), the
+    materialisation of the dequantise-then-dense route.  Device kernel; CPU tensors are staged through the device."""
+    _u8(low, "low", 3)
+    e, n = low.shape[0], low.shape[1]
+    k = low.shape[2] * 8 // bits_lo
+    if bits_hi:
+        _u8(high, "high", 3)
+        _check(tuple(high.shape) == (e, n, k * bits_hi // 8), "artifact high plane does not match its scale shape and qtype")
+    _check(scale.dtype == torch.float16 and tuple(scale.shape) == (e, k // group_size, n), "scale must be fp16 [E,k/group_size,n]")
+    _check(zero is None or (zero.dtype == torch.float16 and zero.shape == scale.shape), "zero must match scale")
+    lo, hi, sc, ze = _to_cuda(low), _to_cuda(high) if bits_hi else None, _to_cuda(scale).contiguous(), _to_cuda(zero)
+    out = torch.empty((e, n, k), dtype=torch.float16, device=lo.device)
+    with torch.cuda.device(lo.device):
+        _rc(_lib.lib().quactlize_b200_planes_dequantize_dev_v1(_p(lo), _p(hi) if bits_hi else None, _p(sc),
+                                                               _p(ze.contiguous()) if ze is not None else None, _p(out), e, n, k,
+                                                               bits_lo, bits_hi, group_size, int(code_shift), _stream(lo)),
+            "plane dequantize")
+    return out.to(low.device)
+
+
+def _artifact_dequantize(low, high, scale, zero, qtype, placed):
+    g = _geom(qtype)
+    _check(low.dtype == torch.uint8 and high.dtype == torch.uint8, "artifact code planes must be uint8")
+    _check(low.dim() == 3, "artifact low plane must be [experts,n,packed_k]")
+    _check(scale.dtype == torch.float16 and zero.dtype == torch.float16, "artifact scale and zero must be fp16")
+    _check(scale.dim() == 3 and scale.shape == zero.shape, "artifact scale and zero must have equal [experts,k/group_size,n] shapes")
+    e, sk, n = scale.shape
+    k = sk * g.group_size
+    _check(tuple(low.shape) == (e, n, k * g.lo_bits // 8), "artifact low plane does not match its scale shape and qtype")
+    if g.hi_bits == 0:
+        _check(high.numel() == 0, "single-plane artifact must have an empty high plane")
+    if placed:
+        _check(n % 256 == 0 and k % 256 == 0, "placed artifact inverse needs n/k multiples of 256")
+    return planes_dequantize(low, high if g.hi_bits else None, scale, zero, g.lo_bits, g.hi_bits, g.group_size,
+                             code_shift=-8 if placed and g.lo_bits == 4 else 0)
+
+
+def _artifact_dequantize_scale(scale, zero, qtype):
+    _geom(qtype)
+    _check(scale.dtype == torch.float16 and zero.dtype == torch.float16, "artifact scale and zero must be fp16")
+    _check(scale.dim() == 3 and scale.shape == zero.shape, "artifact scale and zero must have equal [experts,k/group_size,n] shapes")
+    _check(scale.numel() > 0, "artifact scale planes must be nonempty")
+    return scale.transpose(1, 2).contiguous(), zero.transpose(1, 2).contiguous()
+
+
+def gguf_gemv_artifact_dequantize(low, high, scale, zero, qtype: int):
+    """Inverse of `gguf_prepare_gemv`: resident artifact -> fp16 [experts,n,k] (gguf_prepass_ops.cpp:1215-1218)."""
+    return _artifact_dequantize(low, high, scale, zero, qtype, False)
+
+
+def gguf_gemv_artifact_dequantize_scale(scale, zero, qtype: int):
+    """The GEMV artifact's affine channels as stored, transposed to [experts,n,k/group_size] (gguf_prepass_ops.cpp:1207-1210)."""
+    return _artifact_dequantize_scale(scale, zero, qtype)
+
+
+def gguf_dense_artifact_dequantize(low, high, scale, zero, qtype: int):
+    """Inverse of `gguf_prepare_dense`: int4-low codes decode as (code - 8) against the stored zero plane -> fp16 [1,n,k]."""
+    return _artifact_dequantize(low, high, scale, zero, qtype, True)
+
+
+def gguf_dense_artifact_dequantize_scale(scale, zero, qtype: int):
+    """The dense artifact's affine channels as stored, [1,n,k/group_size]."""
+    return _artifact_dequantize_scale(scale, zero, qtype)
+
+
+def gguf_grouped_artifact_dequantize(low, high, scale, zero, qtype: int):
+    """The per-expert form of `gguf_dense_artifact_dequantize` -> fp16 [experts,n,k]."""
+    return _artifact_dequantize(low, high, scale, zero, qtype, True)
 
 
 # ---------------------------------------------------------------------------------------------------------------------

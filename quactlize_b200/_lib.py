@@ -82,10 +82,16 @@ SIGNATURES = {
     "quactlize_ppu_recover_dense_for_tile": (I, [P, P, P, P, I, I, I, I]),
     "quactlize_b200_prepare_gemv": (I, [P, P, P, P, P, I, I, I, I]),
     "quactlize_b200_pack_units": (I, [P, P, I, I, I, I]),
+    "quactlize_b200_xplane_to_native": (I, [P, P, P, P, I, I, I]),
+    "quactlize_b200_native_to_xplane": (I, [P, P, P, P, I, I, I]),
+    "quactlize_b200_xplane_slot": (C.c_longlong, [I, I, I, I, I]),
     "quactlize_b200_rt_fail_next": (None, [I]),
     "quactlize_b200_rt_trim": (None, []),
     "quactlize_b200_rt_last_status": (I, []),
     "quactlize_b200_device_wait_status": (I, []),
+    "quactlize_b200_debug_wait_probe": (I, [C.c_longlong, P]),
+    "quactlize_b200_unpack_dev_v1": (I, [P, I64, P, P, P, I, I, P]),
+    "quactlize_b200_planes_dequantize_dev_v1": (I, [P, P, P, P, P, I, I, I, I, I, I, I, P]),
 }
 
 

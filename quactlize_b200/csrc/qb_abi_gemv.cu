@@ -146,6 +146,34 @@ extern "C" int quactlize_b200_dequantize_dev_v1(uint8_t const* b, int64_t block_
   return rt_check_launch("GGUF dequantize enqueue") ? 0 : kRuntimeError;
 }
 
+// Additive: the gguf_unpack op on the device.  codes int8 [count][256], scale/zero fp16 [count][groups].
+extern "C" int quactlize_b200_unpack_dev_v1(uint8_t const* b, int64_t block_bytes, int8_t* codes, uint16_t* scale,
+                                            uint16_t* zero, int count, int qtype, void* stream) {
+  if (kq::raw_bytes(qtype) == 0) return 3;
+  if (block_bytes != kq::raw_bytes(qtype) || count <= 0 || !b || !codes || !scale || !zero) return 12;
+  rt_clear_error();
+  enqueue_unpack(b, codes, reinterpret_cast<__half*>(scale), reinterpret_cast<__half*>(zero), count, qtype,
+                 static_cast<cudaStream_t>(stream));
+  return rt_check_launch("GGUF unpack enqueue") ? 0 : kRuntimeError;
+}
+
+// Additive: dequantise a plane artifact (Native planes + fp16 scale/zero planes [E][k/gs][n]) to fp16 [E][n][k] -- the
+// materialisation the dequant-then-dense route pays for.  code_shift is added to the unsigned code (the reference's
+// dense contract stores int4-low codes against a zero plane that carries +8*scale: shift -8).
+extern "C" int quactlize_b200_planes_dequantize_dev_v1(uint8_t const* low, uint8_t const* high, uint16_t const* scale,
+                                                       uint16_t const* zero, uint16_t* out, int experts, int n, int k,
+                                                       int bits_lo, int bits_hi, int group_size, int code_shift, void* stream) {
+  if (!low || !scale || !out || experts <= 0 || n <= 0 || k <= 0) return 20;
+  if (!(bits_lo == 1 || bits_lo == 2 || bits_lo == 4) || bits_hi < 0 || bits_hi > 2 || (bits_hi && !high)) return 21;
+  if (group_size <= 0 || k % group_size || k % 8) return 24;
+  rt_clear_error();
+  if (!enqueue_planes_dequantize(low, high, reinterpret_cast<__half const*>(scale), reinterpret_cast<__half const*>(zero),
+                                 reinterpret_cast<__half*>(out), experts, n, k, bits_lo, bits_hi, group_size, code_shift,
+                                 static_cast<cudaStream_t>(stream)))
+    return 30;
+  return rt_check_launch("plane dequantize enqueue") ? 0 : kRuntimeError;
+}
+
 extern "C" int quactlize_ppu_prepass(uint8_t const* b, int64_t block_bytes, uint16_t const* d, uint16_t const* dm,
                                      int count, uint16_t* scale, uint16_t* zero, int groups, int qtype, int zmul) {
   (void)block_bytes; (void)groups;

@@ -8,7 +8,9 @@
 //
 // What follows from that:
 //   * the array has one size, QUACTLIZE_B200_STATIC_SCRATCH_BYTES (16 MiB) per device; a weight whose planes
-//     (2 planes x k/group_size x n fp16) do not fit is refused with code 37 and a message, nothing is launched;
+//     (2 planes x k/group_size x n fp16) do not fit is refused with code 37 and a message, nothing is launched.
+//     The array is part of the library's device image: every process that loads the library pays these 16 MiB on
+//     every device it creates a context on, whether or not it ever calls this entry, until the process exits;
 //   * the first call on each device looks the array's device address up (a runtime query, made with that device
 //     current, result kept per device).  Make that first call outside any stream capture;
 //   * every call on a device uses the same array.  The planes of a call are rewritten completely by that call's own
@@ -33,7 +35,6 @@ using namespace qb;
 namespace {
 
 constexpr int64_t kStaticScratchBytes = QUACTLIZE_B200_STATIC_SCRATCH_BYTES;
-constexpr int kMaxDevices = 64;
 
 // The scratch itself.  Host code never uses this name as an address: it asks the runtime for the device address.
 static __device__ __align__(256) unsigned char g_static_planes[kStaticScratchBytes];

@@ -14,27 +14,110 @@
 
 namespace qb {
 
-// one warp per block, lane -> 8 consecutive elements, one 16-byte store per lane
+// Raw blocks -> fp16 weights.  A CTA takes kDqBlocks consecutive blocks: their bytes are one contiguous run, staged in
+// shared memory by 16-byte loads (coalesced whatever the block size; the ragged ends by byte loads), then a warp owns a
+// block, lane -> 8 consecutive elements, one 16-byte store per lane (a warp writes 512 contiguous bytes).  DRAM traffic
+// is the algorithmic 144..210 B in + 512 B out per block; the reference's warp-per-256 kernel has the same shape
+// (quactlize/include/gguf_vecdot.hpp:782-854, 78 % of peak published at :762-770).
+constexpr int kDqBlocks = 32;
 template <int QT>
 __global__ void __launch_bounds__(256) dequant_kernel(uint8_t const* __restrict__ blocks, __half* __restrict__ out, int count) {
+  using F = kq::Fmt<QT>;
+  constexpr int GS = 256 / F::kGroups;
+  __shared__ __align__(16) uint8_t stage[kDqBlocks * F::kBytes + 16];
+  int const b0 = blockIdx.x * kDqBlocks;
+  int const nb = min(kDqBlocks, count - b0);
+  if (nb <= 0) return;
+  uint8_t const* src = blocks + size_t(b0) * F::kBytes;
+  int const bytes = nb * F::kBytes;
+  // align the staged copy to the source's 16-byte grid: stage[lead + i] = src[i]
+  int const lead = int(reinterpret_cast<uintptr_t>(src) & 15u);
+  int const head = lead ? min(16 - lead, bytes) : 0;
+  for (int i = threadIdx.x; i < head; i += blockDim.x) stage[lead + i] = src[i];
+  int const body = (bytes - head) >> 4;
+  for (int i = threadIdx.x; i < body; i += blockDim.x)
+    *reinterpret_cast<uint4*>(stage + lead + head + 16 * i) = __ldg(reinterpret_cast<uint4 const*>(src + head) + i);
+  for (int i = head + 16 * body + threadIdx.x; i < bytes; i += blockDim.x) stage[lead + i] = src[i];
+  __syncthreads();
+  int const lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int lb = warp; lb < nb; lb += (blockDim.x >> 5)) {
+    uint8_t const* blk = stage + lead + lb * F::kBytes;
+    float const d = __half2float(__ushort_as_half(kq::load_u16(blk + F::kD)));
+    float dmin = 0.f;
+    if constexpr (F::kHasMin) dmin = __half2float(__ushort_as_half(kq::load_u16(blk + F::kDmin)));
+    int const i0 = lane * 8, g = i0 / GS, j0 = i0 % GS;
+    int sc, mn;
+    kq::scale_min<QT>(blk + F::kScaleOff, g, sc, mn);
+    float const dl = __fmul_rn(d, float(sc)), ml = __fmul_rn(dmin, float(mn));
+    __align__(16) __half w[8];
+#pragma unroll
+    for (int t = 0; t < 8; ++t)
+      w[t] = __float2half_rn(__fsub_rn(__fmul_rn(dl, float(kq::code<QT>(blk, g, j0 + t))), ml));
+    *reinterpret_cast<uint4*>(out + size_t(b0 + lb) * 256 + i0) = *reinterpret_cast<uint4 const*>(w);
+  }
+}
+
+// Raw blocks -> (codes int8 [rows][256], scale fp16 [rows][G], zero fp16 [rows][G]) with W = code*scale + zero:
+// scale = half(float(d)*sc), zero = half(-(float(dmin)*mn)) (quactlize/include/gguf_vecdot.hpp:336-343, the
+// gguf_unpack op).  One warp per block, a lane writes eight codes.
+template <int QT>
+__global__ void __launch_bounds__(256) unpack_kernel(uint8_t const* __restrict__ blocks, int8_t* __restrict__ codes,
+                                                     __half* __restrict__ scale, __half* __restrict__ zero, int count) {
   using F = kq::Fmt<QT>;
   constexpr int GS = 256 / F::kGroups;
   int const lane = threadIdx.x & 31;
   int const b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (b >= count) return;
   uint8_t const* blk = blocks + size_t(b) * F::kBytes;
-  float const d = __half2float(__ushort_as_half(kq::load_u16(blk + F::kD)));
-  float dmin = 0.f;
-  if constexpr (F::kHasMin) dmin = __half2float(__ushort_as_half(kq::load_u16(blk + F::kDmin)));
   int const i0 = lane * 8, g = i0 / GS, j0 = i0 % GS;
-  int sc, mn;
-  kq::scale_min<QT>(blk + F::kScaleOff, g, sc, mn);
-  float const dl = __fmul_rn(d, float(sc)), ml = __fmul_rn(dmin, float(mn));
+  __align__(8) int8_t c[8];
+#pragma unroll
+  for (int t = 0; t < 8; ++t) c[t] = int8_t(kq::code<QT>(blk, g, j0 + t));
+  *reinterpret_cast<uint2*>(codes + size_t(b) * 256 + i0) = *reinterpret_cast<uint2 const*>(c);
+  if (lane < F::kGroups) {
+    float const d = __half2float(__ushort_as_half(kq::load_u16(blk + F::kD)));
+    float dmin = 0.f;
+    if constexpr (F::kHasMin) dmin = __half2float(__ushort_as_half(kq::load_u16(blk + F::kDmin)));
+    int sc, mn;
+    kq::scale_min<QT>(blk + F::kScaleOff, lane, sc, mn);
+    scale[size_t(b) * F::kGroups + lane] = __float2half_rn(__fmul_rn(d, float(sc)));
+    zero[size_t(b) * F::kGroups + lane] = __float2half_rn(-__fmul_rn(dmin, float(mn)));
+  }
+}
+
+// Plane artifact -> fp16 [E][n][k]:  half( float(lo + 2^LO*hi + shift) * float(scale) + float(zero) ), product and sum
+// rounded separately as the host definition does (quactlize/csrc/preprocess/thop/gguf_prepass_ops.cpp:1194-1202).
+// A thread converts eight consecutive k of one row (one 16-byte store); planes are K-contiguous per row, the fp16
+// planes are [E][k/gs][n].
+__global__ void __launch_bounds__(256) planes_dequant_kernel(uint8_t const* __restrict__ low, uint8_t const* __restrict__ high,
+                                                             __half const* __restrict__ scale, __half const* __restrict__ zero,
+                                                             __half* __restrict__ out, int64_t rows, int n, int k, int lo, int hi,
+                                                             int gs, int shift) {
+  int64_t const idx = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  int const per_row = k >> 3;
+  if (idx >= rows * per_row) return;
+  int64_t const row = idx / per_row;                    // e*n + col
+  int const k0 = int(idx % per_row) * 8;
+  int64_t const e = row / n;
+  int const col = int(row % n);
+  uint8_t const* lp = low + (row * k * lo >> 3) + (int64_t(k0) * lo >> 3);
+  uint32_t lw = 0;
+  for (int i = 0; i < lo; ++i) lw |= uint32_t(lp[i]) << (8 * i);      // eight codes of `lo` bits = lo bytes
+  uint32_t hw = 0;
+  if (hi) {
+    uint8_t const* hp = high + (row * k * hi >> 3) + (int64_t(k0) * hi >> 3);
+    for (int i = 0; i < hi; ++i) hw |= uint32_t(hp[i]) << (8 * i);
+  }
   __align__(16) __half w[8];
 #pragma unroll
-  for (int t = 0; t < 8; ++t)
-    w[t] = __float2half_rn(__fsub_rn(__fmul_rn(dl, float(kq::code<QT>(blk, g, j0 + t))), ml));
-  *reinterpret_cast<uint4*>(out + size_t(b) * 256 + i0) = *reinterpret_cast<uint4 const*>(w);
+  for (int t = 0; t < 8; ++t) {
+    int q = int((lw >> (t * lo)) & ((1u << lo) - 1u));
+    if (hi) q |= int((hw >> (t * hi)) & ((1u << hi) - 1u)) << lo;
+    int64_t const a = (e * (k / gs) + (k0 + t) / gs) * n + col;
+    float const z = zero ? __half2float(zero[a]) : 0.f;
+    w[t] = __float2half_rn(__fadd_rn(__fmul_rn(float(q + shift), __half2float(scale[a])), z));
+  }
+  *reinterpret_cast<uint4*>(out + row * k + k0) = *reinterpret_cast<uint4 const*>(w);
 }
 
 __device__ __forceinline__ void scale_zero_from_codes(float d, float dmin, int sc, int mn, bool has_min, int zmul,
@@ -92,9 +175,24 @@ __global__ void __launch_bounds__(256) prepass_unit_kernel(uint8_t const* __rest
                    case 13: CALL(13); break; case 14: CALL(14); break; default: return false; }
 
 bool enqueue_dequantize(uint8_t const* blocks, __half* out, int count, int qtype, cudaStream_t s) {
-#define CALL(Q) dequant_kernel<Q><<<(count + 7) / 8, 256, 0, s>>>(blocks, out, count)
+#define CALL(Q) dequant_kernel<Q><<<(count + kDqBlocks - 1) / kDqBlocks, 256, 0, s>>>(blocks, out, count)
   QB_QT_SWITCH(qtype, CALL)
 #undef CALL
+  return true;
+}
+
+bool enqueue_unpack(uint8_t const* blocks, int8_t* codes, __half* scale, __half* zero, int count, int qtype, cudaStream_t s) {
+#define CALL(Q) unpack_kernel<Q><<<(count + 7) / 8, 256, 0, s>>>(blocks, codes, scale, zero, count)
+  QB_QT_SWITCH(qtype, CALL)
+#undef CALL
+  return true;
+}
+
+bool enqueue_planes_dequantize(uint8_t const* low, uint8_t const* high, __half const* scale, __half const* zero, __half* out,
+                               int experts, int n, int k, int lo, int hi, int gs, int shift, cudaStream_t s) {
+  int64_t const rows = int64_t(experts) * n, total = rows * (k >> 3);
+  if (total <= 0 || total > int64_t(0x7fffffff) * 256) return false;
+  planes_dequant_kernel<<<unsigned((total + 255) / 256), 256, 0, s>>>(low, high, scale, zero, out, rows, n, k, lo, hi, gs, shift);
   return true;
 }
 

@@ -242,3 +242,93 @@ extern "C" int quactlize_ppu_recover_dense_for_tile(uint8_t const* a, uint8_t co
   if (tile_k <= 0 || tile_k > 256 || (tile_k & (tile_k - 1))) return 23;
   return copy_planes(a, b, c, d, n, k, qtype);
 }
+
+// ---- planes placed by the reference's device library ("xplane" order) <-> Native planes -----------------------------
+//
+// The reference places code planes for its tensor-core converter in tiles of 64 columns x TileK codes (TileK 256; 128 for
+// Q6_K).  Inside a tile the logical index  n_in_tile*TileK + k_in_tile  is mapped to a physical code slot by a pure
+// BIT PERMUTATION, stated per (format, plane) as one stride per input bit, least significant first
+// (quactlize/include/gguf_bc_vecdot.hpp:34-72); tiles are laid out k-tile-major, then 64-column tile, 256 code rows of
+// 64 columns each, and TileK = 128 interleaves two k-tiles into one 256-row band (:81-95).  The same maps run both ways
+// here, so an artifact placed for that library can be read (to Native, which every kernel of this library consumes)
+// and written back byte for byte.
+namespace qb {
+namespace {
+
+struct XplaneMap { int bits; int tile_k; uint16_t stride[14]; };
+
+// input bit i of (n_in_tile*TileK + k_in_tile) -> stride[i]
+constexpr XplaneMap kXLow2  = {14, 256, {0x8, 0x10, 0x20, 0x1, 0x2, 0x4, 0x40, 0x80, 0x100, 0x200, 0x400, 0x800, 0x1000, 0x2000}};
+constexpr XplaneMap kXQ3Hi  = {14, 256, {0x10, 0x20, 0x40, 0x1, 0x2, 0x4, 0x8, 0x80, 0x100, 0x200, 0x400, 0x800, 0x1000, 0x2000}};
+constexpr XplaneMap kXLow4  = {14, 256, {0x4, 0x8, 0x10, 0x1, 0x2, 0x20, 0x40, 0x80, 0x100, 0x200, 0x400, 0x800, 0x1000, 0x2000}};
+constexpr XplaneMap kXQ5Hi  = {14, 256, {0x10, 0x20, 0x40, 0x1, 0x2, 0x4, 0x80, 0x800, 0x100, 0x200, 0x400, 0x8, 0x1000, 0x2000}};
+constexpr XplaneMap kXQ6Lo  = {13, 128, {0x4, 0x8, 0x10, 0x1, 0x2, 0x20, 0x40, 0x80, 0x100, 0x200, 0x400, 0x800, 0x1000, 0}};
+constexpr XplaneMap kXQ6Hi  = {13, 128, {0x8, 0x10, 0x20, 0x1, 0x2, 0x4, 0x40, 0x80, 0x100, 0x200, 0x400, 0x800, 0x1000, 0}};
+
+XplaneMap const* xplane_map(int qtype, bool high) {
+  switch (qtype) {
+    case 10: return high ? nullptr : &kXLow2;
+    case 11: return high ? &kXQ3Hi : &kXLow2;
+    case 12: return high ? nullptr : &kXLow4;
+    case 13: return high ? &kXQ5Hi : &kXLow4;
+    case 14: return high ? &kXQ6Hi : &kXQ6Lo;
+    default: return nullptr;
+  }
+}
+
+inline int64_t xplane_slot(XplaneMap const& m, int n, int k, int num_cols) {
+  int const kt = k / m.tile_k, kr = k % m.tile_k, nt = n / 64, nr = n % 64;
+  int const logical = nr * m.tile_k + kr;
+  int rel = 0;
+  for (int i = 0; i < m.bits; ++i) if ((logical >> i) & 1) rel += m.stride[i];
+  if (m.tile_k == 128) {
+    int const rows = (rel & 127) | ((rel & ~127) << 1) | ((kt & 1) << 7);
+    return int64_t(kt / 2) * num_cols * 256 + int64_t(nt) * 64 * 256 + rows;
+  }
+  return int64_t(kt) * num_cols * 256 + int64_t(nt) * 64 * 256 + rel;
+}
+
+template <int Bits>
+void xplane_move(XplaneMap const& m, uint8_t const* src, uint8_t* dst, int n, int k, bool to_native) {
+  std::memset(dst, 0, size_t(n) * k * Bits / 8);
+  for (int col = 0; col < n; ++col)
+    for (int kk = 0; kk < k; ++kk) {
+      int64_t const native = int64_t(col) * k + kk, placed = xplane_slot(m, col, kk, n);
+      if (to_native) plane_put<Bits>(dst, native, plane_get<Bits>(src, placed));
+      else plane_put<Bits>(dst, placed, plane_get<Bits>(src, native));
+    }
+}
+
+int xplane_convert(uint8_t const* lo_in, uint8_t const* hi_in, uint8_t* lo_out, uint8_t* hi_out, int n, int k, int qtype,
+                   bool to_native) {
+  if (!lo_in || !lo_out || n <= 0 || k <= 0 || n % 64 || k % 256 || kq::raw_bytes(qtype) == 0) return 20;
+  int const hb = kq::hi_bits(qtype);
+  if (hb && (!hi_in || !hi_out)) return 21;
+  XplaneMap const* ml = xplane_map(qtype, false);
+  if (kq::lo_bits(qtype) == 2) xplane_move<2>(*ml, lo_in, lo_out, n, k, to_native);
+  else xplane_move<4>(*ml, lo_in, lo_out, n, k, to_native);
+  if (hb) {
+    XplaneMap const* mh = xplane_map(qtype, true);
+    if (hb == 1) xplane_move<1>(*mh, hi_in, hi_out, n, k, to_native);
+    else xplane_move<2>(*mh, hi_in, hi_out, n, k, to_native);
+  }
+  return 0;
+}
+
+}  // namespace
+}  // namespace qb
+
+extern "C" int quactlize_b200_xplane_to_native(uint8_t const* low_placed, uint8_t const* high_placed, uint8_t* low_native,
+                                                uint8_t* high_native, int n, int k, int qtype) {
+  return qb::xplane_convert(low_placed, high_placed, low_native, high_native, n, k, qtype, true);
+}
+extern "C" int quactlize_b200_native_to_xplane(uint8_t const* low_native, uint8_t const* high_native, uint8_t* low_placed,
+                                                uint8_t* high_placed, int n, int k, int qtype) {
+  return qb::xplane_convert(low_native, high_native, low_placed, high_placed, n, k, qtype, false);
+}
+// The physical code slot of logical (n, k) in a placed plane of `num_cols` columns; -1 for a plane the format lacks.
+extern "C" long long quactlize_b200_xplane_slot(int qtype, int high, int n, int k, int num_cols) {
+  qb::XplaneMap const* m = qb::xplane_map(qtype, high != 0);
+  if (!m || n < 0 || k < 0 || num_cols <= 0 || n >= num_cols) return -1;
+  return qb::xplane_slot(*m, n, k, num_cols);
+}

@@ -16,6 +16,10 @@ bool enqueue_q4k_gemv1(uint8_t const* blocks, __half const* x, float* out, int c
 bool enqueue_q4k_mma(uint8_t const* blocks, __half const* x, float* out, int const* offsets, int n, int bpr, int experts,
                      int rows, unsigned int* status, cudaStream_t stream);   // tensor-core small-batch form
 bool enqueue_dequantize(uint8_t const* blocks, __half* out, int count, int qtype, cudaStream_t s);
+bool enqueue_unpack(uint8_t const* blocks, int8_t* codes, __half* scale, __half* zero, int count, int qtype, cudaStream_t s);
+// planes (Native order) + fp16 scale/zero planes -> fp16 [E][n][k]; `shift` is added to the unsigned code
+bool enqueue_planes_dequantize(uint8_t const* low, uint8_t const* high, __half const* scale, __half const* zero, __half* out,
+                               int experts, int n, int k, int lo, int hi, int gs, int shift, cudaStream_t s);
 bool enqueue_prepass(uint8_t const* sblocks, uint16_t const* d, uint16_t const* dmin, int count, int qtype, int zmul,
                      __half* scale, __half* zero, cudaStream_t s);
 bool enqueue_prepass_unit(uint8_t const* units, __half* scale, __half* zero, int experts, int n, int nsb, int qtype,

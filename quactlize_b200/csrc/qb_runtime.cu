@@ -1,6 +1,8 @@
 // Runtime shim: staged host copies, the device wait-status word, device properties.
 #include "qb_runtime.hpp"
 
+#include "qb_device.cuh"
+
 #include <mutex>
 #include <vector>
 
@@ -109,7 +111,30 @@ int rt_sm_count() {
   return g_sm_count[dev];
 }
 
+// A one-CTA kernel that waits on an mbarrier nothing ever arms, with a caller-chosen limit.  The wait gives up, records
+// its code in the device status word and the kernel returns normally: the path every bounded wait of the library takes
+// when a copy never lands, exercised without a fault, a trap or a hang.
+namespace {
+__global__ void wait_probe_kernel(unsigned int* status, unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_init_fence();
+    (void)mbar_wait_bounded(&bar, 0u, status, kWaitStageTimeout, limit_ns);
+  }
+}
+}  // namespace
+
 }  // namespace qb
+
+extern "C" int quactlize_b200_debug_wait_probe(long long limit_ns, void* stream) {
+  if (limit_ns <= 0 || limit_ns > 100000000ll) return 20;          // at most 100 ms: this is a test hook, not a sleep
+  qb::rt_clear_error();
+  unsigned int* st = qb::rt_device_status_ptr();
+  if (!st) return qb::kRuntimeError;
+  qb::wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(st, static_cast<unsigned long long>(limit_ns));
+  return qb::rt_check_launch("wait probe enqueue") ? 0 : qb::kRuntimeError;
+}
 
 // ---- additive C entries: fault injection for tests, status query ---------------------------------------------------
 extern "C" void quactlize_b200_rt_fail_next(int kind) { qb::rt_tls().inject = static_cast<qb::RtStatus>(kind); }

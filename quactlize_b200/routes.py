@@ -12,10 +12,14 @@ from typing import Optional
 
 import torch
 
+import quactlize_b200 as _pkg
 from . import (gguf_dequantize, gguf_vecdot_dense, gguf_vecdot_moe, gguf_prepare_gemv, gguf_gemv_scale_first,
                gguf_gemv_scale_first_moe, gguf_packed_scale_prepass, gguf_gemv_bc, gguf_gemv_bc_moe,
-               gguf_prepare_fully_quantized_dense, gguf_prepare_fully_quantized_grouped, gguf_vecdot_rows)
-from .formats import QuantType, kquant_geometry
+               gguf_prepare_fully_quantized_dense, gguf_prepare_fully_quantized_grouped, gguf_vecdot_rows,
+               gguf_prepare_dense, gguf_dense_scale_first, gguf_dense_fully_quantized, gguf_grouped_fully_quantized,
+               gguf_gemv_artifact_dequantize, gguf_gemv_artifact_dequantize_scale, gguf_dense_artifact_dequantize,
+               gguf_dense_artifact_dequantize_scale, gguf_grouped_artifact_dequantize)
+from .formats import QuantType, placed_code_zmul, select_path
 
 
 def _check_shape(blocks: torch.Tensor, n: int, k: int, qtype: int) -> None:
@@ -130,15 +134,63 @@ def _unpack_fq(artifact, where: str):
     return xs[0], xs[1], xs[2]
 
 
+def has_op(name: str) -> bool:
+    """Whether an op of the reference's registry exists in this build (quactlize/routes.py:228-243).  Here every op is
+    a function of the package, so the package namespace is the registry."""
+    return callable(getattr(_pkg, name, None))
+
+
 def dequantize_scale_from_units(units, qtype: int, zmul: Optional[int] = None):
     """Packed scale units -> fp16 (scale, zero) planes [E, k/group_size, n] (quactlize/routes.py:262-288).
 
-    zmul is the consumer's code correction.  The kernels of this library read offset-binary plane codes directly, so
-    their correction is minus the format's code bias (0, -4, 0, 0, -32); pass the reference's placed-code value
-    (formats.placed_code_zmul) to build planes for ITS dense contract instead."""
+    zmul is the consumer's complete code correction and is DERIVED from the format when not given: the placed dense
+    contract's table (Q2_K 0, Q3_K -4, Q4_K 8, Q5_K 8, Q6_K -24: int4-low codes convert as low-8, signed formats are
+    stored offset-binary).  A consumer that reads the offset-binary plane codes directly (the plane GEMVs of this
+    library) passes minus the format's code bias instead."""
     if zmul is None:
-        zmul = -kquant_geometry(qtype).code_bias
+        zmul = placed_code_zmul(qtype)
     return gguf_packed_scale_prepass(units, int(qtype), int(zmul))
+
+
+def dequantize_scale_first(artifact, qtype: int):
+    """GEMV scale-first artifact -> fp16 [experts,n,k], without running a GEMV (quactlize/routes.py:151-153)."""
+    return gguf_gemv_artifact_dequantize(*artifact, int(qtype))
+
+
+def dequantize_scale_first_scales(artifact, qtype: int):
+    """GEMV scale-first artifact -> the stored (scale, zero) planes as [experts,n,k/group_size] (quactlize/routes.py:156-158)."""
+    return gguf_gemv_artifact_dequantize_scale(artifact[2], artifact[3], int(qtype))
+
+
+def prepare_scale_first_dense(blocks, n: int, k: int, qtype: int, derive_from_bc: bool = True):
+    """Offline artifact (low, high, scale, zero) of the dense scale-first GEMM (quactlize/routes.py:176-199).  By default
+    the fp16 planes are DERIVED from the packed units of the fully-quantized artifact; derive_from_bc=False keeps the
+    independent producer from raw blocks reachable (the two are compared bit for bit by the tests)."""
+    _check_shape(blocks, n, k, qtype)
+    if not derive_from_bc:
+        return gguf_prepare_dense(blocks, n, k, int(qtype))
+    low, high, units = gguf_prepare_fully_quantized_dense(blocks, n, k, int(qtype))
+    scale, zero = dequantize_scale_from_units(units, qtype)
+    return low, high, scale, zero
+
+
+def dequantize_scale_first_dense(artifact, qtype: int):
+    """Dense scale-first artifact -> fp16 [1,n,k], without running a GEMM (quactlize/routes.py:202-204)."""
+    return gguf_dense_artifact_dequantize(*artifact, int(qtype))
+
+
+def dequantize_scale_first_dense_scales(artifact, qtype: int):
+    """Dense scale-first artifact -> the stored (scale, zero) planes [1,n,k/group_size] (quactlize/routes.py:207-209)."""
+    return gguf_dense_artifact_dequantize_scale(artifact[2], artifact[3], int(qtype))
+
+
+def dequantize_fully_quantized(artifact, qtype: int, grouped: bool = False):
+    """(low, high, units) -> the fp16 weight [experts,n,k]: the scale planes derived from the units, then the
+    scale-first dequantise-all -- a composition, not a second decoder (quactlize/routes.py:322-349)."""
+    low, high, units = _unpack_fq(artifact, "dequantize_fully_quantized")
+    scale, zero = dequantize_scale_from_units(units, qtype)
+    op = gguf_grouped_artifact_dequantize if grouped else gguf_dense_artifact_dequantize
+    return op(low, high, scale, zero, int(qtype))
 
 
 def prepare_fully_quantized_dense(blocks, n: int, k: int, qtype: int, tile_k=None):
@@ -170,12 +222,50 @@ def matmul_bc_gemv_moe(a, artifact, qtype: int, num_experts: int, rows_per_exper
     return gguf_gemv_bc_moe(a, low, high, units, offsets.to(a.device), int(qtype))
 
 
+def matmul_fully_quantized_dense(a, artifact, qtype: int):
+    """a @ w.T with nothing expanded: the tensor-core GEMM reads planes + packed units (quactlize/routes.py:367-375)."""
+    low, high, units = _unpack_fq(artifact, "matmul_fully_quantized_dense")
+    return gguf_dense_fully_quantized(a, low, high, units, int(qtype))
+
+
+def matmul_fully_quantized_grouped(a, artifact, qtype: int, rows_per_expert):
+    """The grouped GEMM on planes + packed units; rows are ragged and an expert may have none
+    (quactlize/routes.py:391-399)."""
+    low, high, units = _unpack_fq(artifact, "matmul_fully_quantized_grouped")
+    return gguf_grouped_fully_quantized(a, low, high, units, rows_per_expert.to(torch.int32), int(qtype))
+
+
+def matmul_scale_first_dense(a, artifact, qtype: int):
+    """SCALE_FIRST/DENSE: packed codes and resident fp16 planes on the tensor cores (quactlize/routes.py:402-405)."""
+    low, high, scale, zero = artifact
+    return gguf_dense_scale_first(a, low, high, scale, zero, int(qtype))
+
+
+def matmul_selected(a, artifact, qtype: int, fp16_planes: str = "workspace"):
+    """Additive: run a dense matmul over a fully-quantized artifact (low, high, units) on the path `formats.select_path`
+    names for this row count (quactlize/formats.py:175-219).  `gemv` is the merged-form decode GEMV (planes + units, no
+    fp16 planes at all), `fused_native_scale` / `fused_fp16_scale` the tensor-core GEMM on the same bytes, and
+    `dequant_then_dense` materialises the fp16 weight with the device dequantiser and hands it to a library GEMM --
+    the fallback above the crossover.  Returns (path name, result); the result's dtype is the path's own."""
+    low, high, units = _unpack_fq(artifact, "matmul_selected")
+    path = select_path(QuantType(int(qtype)), int(a.shape[0]), True, fp16_planes)
+    if path == "gemv":
+        return path, matmul_bc_gemv(a, artifact, qtype)
+    if path in ("fused_native_scale", "fused_fp16_scale"):
+        return path, matmul_fully_quantized_dense(a, artifact, qtype)
+    w = dequantize_fully_quantized(artifact, qtype)[0]
+    return path, a.to(w.dtype) @ w.t()
+
+
 ROUTES = {
     "dequant_first": matmul_dequant_first,
     "native_gemv": matmul_native_gemv,
     "native_gemv_moe": matmul_native_gemv_moe,
     "scale_first_gemv": matmul_scale_first_gemv,
     "scale_first_gemv_moe": matmul_scale_first_gemv_moe,
+    "scale_first_dense": matmul_scale_first_dense,
     "bc_gemv": matmul_bc_gemv,
     "bc_gemv_moe": matmul_bc_gemv_moe,
+    "fully_quantized_dense": matmul_fully_quantized_dense,
+    "fully_quantized_grouped": matmul_fully_quantized_grouped,
 }

@@ -252,6 +252,55 @@ def fpa(dev="cuda:0") -> Case:
                 2.0 * m * n * k, 1, launch, sample, "mixed_gemm_kernel")
 
 
+def aux_dequant(qtype: int = 12, n: int = 14336, k: int = 4096, dev="cuda:0") -> Case:
+    """Raw blocks -> the fp16 weight (the materialisation the dequantise-then-dense route pays): bytes in + bytes out."""
+    bb = synth.BLOCK_BYTES[qtype]
+    blocks = synth.kquant_blocks(qtype, n * k // 256, seed=700 + qtype)
+    b0 = _dev(blocks, dev)
+    nc = _ncopies(blocks.size + n * k * 2)
+    copies = [b0] + [b0.clone() for _ in range(nc - 1)]
+    outs = [torch.empty((n * k // 256, 256), dtype=torch.float16, device=dev) for _ in range(nc)]
+    L = qb._lib.lib()
+
+    def launch(i):
+        rc = L.quactlize_b200_dequantize_dev_v1(copies[i].data_ptr(), bb, outs[i].data_ptr(), n * k // 256, qtype,
+                                                torch.cuda.current_stream().cuda_stream)
+        if rc:
+            raise RuntimeError(f"dequantize enqueue failed rc={rc}")
+        return outs[i]
+
+    def sample():
+        rows = _cols(n * k // 256, 701, 512)
+        got = launch(0)[torch.from_numpy(rows).to(dev)].cpu().numpy()
+        return {"kind": "dequant_bits", "got": got, "blocks": blocks[rows], "qtype": qtype, "out": "fp16"}
+    nm = {10: "q2k", 11: "q3k", 12: "q4k", 13: "q5k", 14: "q6k"}[qtype]
+    wb = blocks.size
+    return Case(f"aux_dequant_{nm}_{k}to{n}", "hbm", wb, wb + n * k * 2, 0.0, nc, launch, sample, "dequant_kernel")
+
+
+def aux_units_prepass(qtype: int = 12, n: int = 14336, k: int = 4096, dev="cuda:0") -> Case:
+    """Packed units -> fp16 scale/zero planes (the workspace pre-pass of the fully-quantized GEMM)."""
+    blocks = synth.kquant_blocks(qtype, n * k // 256, seed=710 + qtype)
+    units = qb.gguf_pack_units(torch.from_numpy(blocks), n, k, qtype)              # [1, U, n, bytes]
+    u0 = units.to(dev)
+    g = qb.kquant_geometry(qtype)
+    out_bytes = 2 * (k // g.group_size) * n * 2
+    nc = _ncopies(units.numel() + out_bytes)
+    copies = [u0] + [u0.clone() for _ in range(nc - 1)]
+
+    def launch(i):
+        return qb.gguf_packed_scale_prepass(copies[i], qtype, 0)
+
+    def sample():
+        cols = _cols(n, 711)
+        sc, ze = launch(0)
+        got = np.stack([sc[0].cpu().numpy()[:, cols], ze[0].cpu().numpy()[:, cols]])
+        return {"kind": "units_bits", "got": got, "units": units[0].numpy()[:, cols], "qtype": qtype, "zmul": 0, "out": "fp16"}
+    nm = {10: "q2k", 11: "q3k", 12: "q4k", 13: "q5k", 14: "q6k"}[qtype]
+    return Case(f"aux_units_prepass_{nm}_{k}to{n}", "hbm", units.numel(), units.numel() + out_bytes, 0.0, nc, launch, sample,
+                "prepass_unit_kernel")
+
+
 # ---------------------------------------------------------------------------------------------------------------------
 
 FFN = [(14336, 4096), (4096, 14336)]
@@ -273,6 +322,9 @@ def registry() -> Dict[str, Callable[[], Case]]:
             for t in (1, 8, 64):
                 r[f"cfg5_w{bits}_{w}_t{t}"] = (lambda bits=bits, w=w, t=t: cfg5(bits, w, t))
     r["fpa"] = fpa
+    r["aux_dequant_q4k"] = aux_dequant
+    r["aux_dequant_q6k"] = (lambda: aux_dequant(14))
+    r["aux_units_prepass_q4k"] = aux_units_prepass
     return r
 
 

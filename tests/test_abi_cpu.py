@@ -102,7 +102,7 @@ def test_prepare_gemv_host_producer_bit_exact(qtype):
 
 def test_pack_units_host_producer_bit_exact(qtype):
     g = load_golden(qtype)
-    units = qb.gguf_pack_unit(torch.from_numpy(g["blocks"]), int(g["n"]), int(g["k"]), qtype)
+    units = qb.gguf_pack_units(torch.from_numpy(g["blocks"]), int(g["n"]), int(g["k"]), qtype)
     _eq(units[0], g["units"])
 
 
@@ -154,3 +154,29 @@ def test_header_is_c_and_a_c_caller_can_load_the_library(tmp_path):
     r = subprocess.run([str(exe), _lib.LIB_PATH], capture_output=True, text=True)
     assert r.returncode == 0, r.stdout + r.stderr
     assert r.stdout.startswith("ok 8192 ")
+
+
+def test_pack_unit_reference_form_matches_golden(qtype):
+    """The reference-form op (scale blocks + fp16 headers in, units out): the 3-D artifact form reproduces the units the
+    reference's own op produced, and the 2-D row-wise form equals the artifact form of a single column."""
+    import torch
+    import quactlize_b200 as qb
+    from quactlize_b200.formats import kquant_geometry
+    g = load_golden(qtype)
+    geo = kquant_geometry(qtype)
+    n, k = int(g["n"]), int(g["k"])
+    nsb = k // 256
+    d_off, m_off, s_off = {10: (80, 82, 0), 11: (108, -1, 96), 12: (0, 2, 4), 13: (0, 2, 4), 14: (208, -1, 192)}[qtype]
+    tb = torch.from_numpy(g["blocks"])
+    sblk = tb[:, s_off:s_off + geo.scale_bytes].contiguous().view(n, nsb, geo.scale_bytes)
+    d = tb[:, d_off:d_off + 2].contiguous().view(torch.float16).view(n, nsb)
+    dm = tb[:, m_off:m_off + 2].contiguous().view(torch.float16).view(n, nsb) if m_off >= 0 else torch.empty(0, dtype=torch.float16)
+    units = qb.gguf_pack_unit(sblk, d, dm, qtype)
+    assert np.array_equal(units.numpy(), g["units"])
+    col = 5
+    rowwise = qb.gguf_pack_unit(sblk[col].contiguous(), d[col].contiguous(), dm[col].contiguous() if m_off >= 0 else dm, qtype)
+    assert np.array_equal(rowwise.numpy(), g["units"][:, col, :])
+    assert qb.gguf_scale_block_shape(qtype)[:4] == [geo.scale_bytes, geo.groups, geo.group_size, int(geo.has_min)]
+    if geo.has_min:
+        with pytest.raises(RuntimeError):
+            qb.gguf_pack_unit(sblk, d, None, qtype)

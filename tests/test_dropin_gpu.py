@@ -43,6 +43,33 @@ CHILD = textwrap.dedent('''
         off = torch.tensor([0, 2, 2, 3], dtype=torch.int32)
         refm = kq.vecdot_moe(eb.numpy(), xa.numpy(), off.numpy(), n, k, qt)
         assert kq.max_rel(q.gguf_vecdot_moe(eb, xa, off, qt).numpy(), refm) < 2e-3
+        # ---- the tensor-core family through the reference's ops (dense scale-first, fully-quantized dense and grouped) ----
+        m = 70
+        am = torch.from_numpy(synth.activations(m, k, seed=3))
+        refw = am.numpy().astype(np.float64) @ kq.dequantize_f32(blocks, qt).reshape(n, k).T
+        dart = q.gguf_prepare_dense(tb, n, k, qt)
+        got = q.gguf_dense_scale_first(am, *dart, qt)
+        assert got.dtype == torch.float16 and kq.max_rel(got.float().numpy(), refw) < 6e-3
+        wdq = q.gguf_dense_artifact_dequantize(*dart, qt)                 # placed inverse through recover_dense
+        assert kq.max_rel(wdq[0].float().numpy(), kq.dequantize_f32(blocks, qt).reshape(n, k)) < 2e-3
+        got = q.gguf_dense_fully_quantized(am, lo2, hi2, units, qt)
+        assert kq.max_rel(got.float().numpy(), refw) < 6e-3
+        sc_u, ze_u = q.gguf_packed_scale_prepass(units, qt, 0)
+        sc_o, ze_o = kq.units_decode(units.numpy()[None], qt, 0)
+        assert np.array_equal(sc_u.numpy().view(np.uint16), sc_o.view(np.uint16)) and np.array_equal(ze_u.numpy().view(np.uint16), ze_o.view(np.uint16))
+        ge, grow = 3, [130, 0, 37]
+        gb = synth.kquant_blocks(qt, ge * n * k // 256, seed=qt + 90)
+        glo, ghi, gun = q.gguf_prepare_fully_quantized_grouped(torch.from_numpy(gb), n, k, qt, ge)
+        ga = torch.from_numpy(synth.activations(sum(grow), k, seed=4))
+        gout = q.gguf_grouped_fully_quantized(ga, glo, ghi, gun, torch.tensor(grow, dtype=torch.int32), qt)
+        goff = np.concatenate([[0], np.cumsum(grow)]).astype(np.int32)
+        gref = kq.vecdot_moe(gb.reshape(ge, n * k // 256, -1), ga.numpy(), goff, n, k, qt)
+        assert kq.max_rel(gout.float().numpy(), gref) < 6e-3
+        # scale-first and merged-form MoE GEMVs
+        art_m = q.gguf_prepare_gemv(eb, n, k, qt)
+        om = q.gguf_gemv_scale_first_moe(xa, *art_m, off, qt)
+        refp = kq.planes_matmul(xa.numpy(), *[t.numpy() for t in art_m], f.lo_bits, f.hi_bits, f.group_size, off.numpy())
+        assert kq.max_rel(om.float().numpy(), refp) < 2e-3
     print("DROPIN_OK", backend)
 ''')
 

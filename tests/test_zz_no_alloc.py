@@ -72,6 +72,26 @@ def test_static_scratch_entry_two_calls_in_a_row():
     assert L.quactlize_b200_device_wait_status() == 0
 
 
+def test_static_scratch_entry_leaves_device_memory_untouched():
+    """After a first (warm) call, further calls must not change the device's free memory at all: the entry owns no
+    allocation, so cudaMemGetInfo (read through torch.cuda.mem_get_info) is identical before and after."""
+    L = _lib.lib()
+    torch.cuda.set_device(0)
+    (a, low, high, units, _), (qt, m, n, k) = _case(13, 64, 512, 1024, 31), (13, 64, 512, 1024)
+    out = torch.empty((m, n), dtype=torch.float16, device=DEV)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    call = lambda: L.quactlize_b200_dense_fully_quantized_static_v1(_p(a), _p(low), _p(high), _p(units), _p(out), m, n, k, qt, stream)
+    assert call() == 0                                   # warm: symbol-address lookup, function attributes, module load
+    torch.cuda.synchronize()
+    free_before, total = torch.cuda.mem_get_info(0)
+    for _ in range(3):
+        assert call() == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info(0)
+    assert free_after == free_before, (free_before, free_after, total)
+    assert L.quactlize_b200_device_wait_status() == 0
+
+
 def test_static_scratch_entry_refuses_what_does_not_fit():
     L = _lib.lib()
     n = k = 16384                                        # Q6_K: 2 planes * (k/16) * n fp16 = 64 MiB
