@@ -135,8 +135,9 @@ int quactlize_b200_gemv_plane_dev_v1(void const* act, uint8_t const* low, uint8_
 /* ================================ tensor-core mixed-input GEMM (dense fpA_intB, MoE grouped) ===================== */
 
 /* Config inventory.  quactlize/include/quactlize_ppu_config.h:42-71, quactlize/csrc/device/ppu_dense_backend.cu:603-664.
- * Two tensor-core tactics are listed ("256x256x64:tcgen05" and "128x128x64:tcgen05"); a null or empty name lets the
- * library choose by problem size, an unknown name logs a decline and runs that default. */
+ * Two tensor-core tactics are listed ("256x256x64:tcgen05" and "128x128x64:tcgen05"), and for the grouped routes a
+ * third, "128x128x64:tcgen05:splitk" (decode); a null or empty name lets the library choose by problem size, an
+ * unknown name logs a decline and runs that default. */
 int32_t quactlize_ppu_list_configs(quactlize_ppu_config_v1 const** configs);
 int32_t quactlize_ppu_list_grouped_configs(quactlize_ppu_config_v1 const** configs);
 int32_t quactlize_ppu_list_valid_dense_lowbit_configs_v2(quactlize_ppu_config_v2* configs, int32_t capacity, int m, int n,
@@ -216,6 +217,29 @@ int quactlize_b200_gemm_plane_dev_v1(void const* act, uint8_t const* low, uint8_
                                      uint16_t const* zero, void* out, int total_rows, int n, int k, int bits_lo, int bits_hi,
                                      int group_size, int code_offset, int act_dtype, int experts, int const* offsets, void* stream);
 
+/* additive: v1 with an OUTPUT ROW MAP.  When out_rows is non-null it is a device array [total_rows] of addresses and
+ * output row r (n elements) is stored at out_rows[r] instead of out + r*n (`out` may then be null).  In a grouped launch
+ * total_rows may be an upper bound (the capacity of `act`); rows past offsets[experts] are never read or written. */
+int quactlize_b200_gemm_plane_dev_v2(void const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale,
+                                     uint16_t const* zero, void* out, int total_rows, int n, int k, int bits_lo, int bits_hi,
+                                     int group_size, int code_offset, int act_dtype, int experts, int const* offsets,
+                                     unsigned long long const* out_rows, void* stream);
+
+/* additive: the split-K form of the plane GEMM for decode-sized (grouped) problems -- the B200 counterpart of the
+ * reference's split-K grouped kernel, where slice z of K writes its own D plane and a light reduce follows
+ * (quactlize/include/ppu_aiu_gemm_mixed_input_group.hpp:120-131,289-309).  128 x 128 tiles with shallow rings (several
+ * CTAs per SM), K split over `splits` slices of whole 128-k pieces (0 = chosen so the grid fills the SMs, at most 8),
+ * fp32 partial planes [splits][total_rows][n] in the caller's 16-byte aligned workspace, summed in slice order by a
+ * second small kernel.  37 = workspace too small (size it with the query; splits 0 asks for the 8-slice maximum).
+ * The grouped tactic name "128x128x64:tcgen05:splitk" selects the same form through the reference's *_dev_v2 entries
+ * when their workspace (sized by their own queries) has room for the partial planes. */
+int64_t quactlize_b200_gemm_plane_splitk_workspace_bytes_v1(int total_rows, int n, int splits);
+int quactlize_b200_gemm_plane_splitk_dev_v1(void const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale,
+                                            uint16_t const* zero, void* out, int total_rows, int n, int k, int bits_lo,
+                                            int bits_hi, int group_size, int code_offset, int act_dtype, int experts,
+                                            int const* offsets, int splits, void* workspace, int64_t workspace_bytes,
+                                            void* stream);
+
 /* No counterpart in the reference.  The fully-quantized dense GEMM of quactlize_ppu_dense_fully_quantized_dev_v1 for
  * callers that cannot allocate device memory and have no workspace to hand over: the fp16 scale/zero planes derived
  * from the packed units go to a fixed array inside the library's device image, QUACTLIZE_B200_STATIC_SCRATCH_BYTES
@@ -239,6 +263,40 @@ int quactlize_b200_unpack_dev_v1(uint8_t const* blocks, int64_t block_bytes, int
 int quactlize_b200_planes_dequantize_dev_v1(uint8_t const* low, uint8_t const* high, uint16_t const* scale,
                                             uint16_t const* zero, uint16_t* out, int experts, int n, int k, int bits_lo,
                                             int bits_hi, int group_size, int code_shift, void* stream);
+
+/* ================================ expert parallelism over the GPUs of one node ================================== */
+
+/* No counterpart in the reference (it has no multi-device code).  One process per GPU.  peer_alloc: a zeroed device
+ * buffer from the runtime allocator plus its 64-byte IPC handle; peer_open / peer_close: map / unmap another rank's buffer
+ * (NVLink peer access); peer_free.  These allocate and synchronise: set-up time only.
+ * ep_count: routes per expert (expert ids int64 [routes]) -> counts int32 [experts].  ep_plan: with every rank's counts
+ * [world][experts] (the caller all-gathers them), one CTA assigns every route of this rank an ITEM number in expert
+ * order and writes, per item, the local token (route / top_k), the owner rank and the row in the owner's expert-major
+ * receive buffer (experts in order, sources in rank order inside an expert); per route its item; and local_off
+ * [experts/world + 1], the cumulative rows per local expert this rank's grouped GEMMs read as offsets.
+ * ep_dispatch: item i (row item_token[i] of act, row_bytes long, a multiple of 16) is stored at row item_pos[i] of
+ * peer_rows[item_rank[i]] and the tag (my_rank << 32 | i) at the same index of peer_tag[...]; the pointer tables are
+ * device arrays of this process's mappings.  Plain peer stores; the caller orders them against the owner's reads with a
+ * stream-ordered collective.  ep_return_addr: the owner turns received tags into addresses inside ITS mappings of the
+ * senders' combine buffers (peer_comb[src] + item*row_bytes) for the row map of quactlize_b200_gemm_plane_dev_v2.
+ * ep_combine: out[t] = sum_j weights[t][j] * comb[item_of_route[t*top_k+j]] (fp32, route order), bf16 rows of h elements.
+ * silu_mul: out[r][c] = silu(gate_up[r][c]) * gate_up[r][f+c], bf16, for min(*rows_dev, max_rows) rows. */
+int quactlize_b200_peer_alloc(long long bytes, void** ptr, unsigned char* handle64);
+int quactlize_b200_peer_open(unsigned char const* handle64, void** ptr);
+int quactlize_b200_peer_close(void* ptr);
+int quactlize_b200_peer_free(void* ptr);
+int quactlize_b200_ep_count_dev_v1(long long const* expert_of_route, int routes, int experts, int* counts, void* stream);
+int quactlize_b200_ep_plan_dev_v1(long long const* expert_of_route, int const* counts_all, int rank, int world, int experts, int routes,
+                                  int top_k, int* item_token, int* item_rank, int* item_pos, int* item_of_route, int* local_off,
+                                  void* stream);
+int quactlize_b200_ep_dispatch_dev_v1(void const* act, int const* item_token, int const* item_rank, int const* item_pos,
+                                      unsigned long long const* peer_rows, unsigned long long const* peer_tag, int my_rank,
+                                      int items, int row_bytes, void* stream);
+int quactlize_b200_ep_return_addr_dev_v1(unsigned long long const* tags, unsigned long long const* peer_comb, int world,
+                                         int const* rows_dev, int max_rows, int row_bytes, unsigned long long* addr, void* stream);
+int quactlize_b200_ep_combine_dev_v1(void const* comb, int const* item_of_route, float const* weights, void* out, int tokens,
+                                     int top_k, int h, void* stream);
+int quactlize_b200_silu_mul_dev_v1(void const* gate_up, void* out, int const* rows_dev, int max_rows, int f, void* stream);
 
 /* ================================ host-only artifact producers ================================================== */
 

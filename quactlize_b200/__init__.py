@@ -640,12 +640,15 @@ def gemv_plane(a, low, high, scale, zero, bits_lo: int, bits_hi: int, group_size
 # tensor-core mixed-input GEMM
 
 def gemm_plane(a, low, high, scale, zero, bits_lo: int, bits_hi: int, group_size: int, code_offset: int = 0,
-               row_offsets=None):
+               row_offsets=None, split_k=None):
     """Generic per-group plane GEMM on the tensor cores: D = a @ W^T, W = (lo + 2^bits_lo*hi + code_offset)*scale + zero.
 
     a fp16/bf16 [rows,k] (CUDA); low uint8 [E,n,k*bits_lo/8]; scale (and optional zero) fp16 [E,k/group_size,n];
     dense when row_offsets is None (E == 1), else grouped with cumulative int32 offsets [E+1] on the device (rows
-    gathered in expert order, empty experts allowed).  n % 128 == 0, k % 256 == 0.  Returns [rows,n] in a's dtype."""
+    gathered in expert order, empty experts allowed).  n % 128 == 0, k % 256 == 0.  Returns [rows,n] in a's dtype.
+
+    split_k selects the decode form: 128 x 128 tiles with shallow rings and K split over that many slices (0 = as many
+    as fill the SMs, at most 8; 1 = shallow rings only) whose fp32 partial planes a second small kernel sums."""
     _check(a.is_cuda and a.dim() == 2 and a.dtype in (torch.float16, torch.bfloat16), "a must be a CUDA fp16/bf16 [rows,k] tensor")
     _u8(low, "low", 3)
     e, n, k = low.shape[0], low.shape[1], a.shape[1]
@@ -666,6 +669,18 @@ def gemm_plane(a, low, high, scale, zero, bits_lo: int, bits_hi: int, group_size
     if rows == 0:
         return out
     a = a.contiguous()
+    if split_k is not None:
+        L = _lib.lib()
+        need = L.quactlize_b200_gemm_plane_splitk_workspace_bytes_v1(rows, n, int(split_k)) if int(split_k) != 1 else 0
+        _check(need >= 0, "split_k must be between 0 and 64")
+        ws = torch.empty(max(need, 16), dtype=torch.uint8, device=a.device)
+        with torch.cuda.device(a.device):
+            _rc(L.quactlize_b200_gemm_plane_splitk_dev_v1(
+                _p(a), _p(low), _p(high) if bits_hi else None, _p(scale.contiguous()),
+                _p(zero.contiguous()) if zero is not None else None, _p(out), rows, n, k, bits_lo, bits_hi, group_size,
+                int(code_offset), 1 if a.dtype == torch.bfloat16 else 0, experts, _p(off), int(split_k), _p(ws), need,
+                _stream(a)), "split-K plane GEMM")
+        return out
     with torch.cuda.device(a.device):
         _rc(_lib.lib().quactlize_b200_gemm_plane_dev_v1(
             _p(a), _p(low), _p(high) if bits_hi else None, _p(scale.contiguous()),

@@ -70,6 +70,19 @@ SIGNATURES = {
     "quactlize_ppu_grouped_fully_quantized_dev_v1": (I, [P, P, P, P, P, P, I, I, I, I, I, I, P, I64, P]),
     "quactlize_ppu_grouped_fully_quantized_dev_v2": (I, [P, P, P, P, P, P, I, I, I, I, I, I, P, I64, P, C.c_char_p]),
     "quactlize_b200_gemm_plane_dev_v1": (I, [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P]),
+    "quactlize_b200_gemm_plane_dev_v2": (I, [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P, P]),
+    "quactlize_b200_peer_alloc": (I, [C.c_longlong, C.POINTER(C.c_void_p), C.c_char_p]),
+    "quactlize_b200_peer_open": (I, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "quactlize_b200_peer_close": (I, [P]),
+    "quactlize_b200_peer_free": (I, [P]),
+    "quactlize_b200_ep_count_dev_v1": (I, [P, I, I, P, P]),
+    "quactlize_b200_ep_plan_dev_v1": (I, [P, P, I, I, I, I, I, P, P, P, P, P, P]),
+    "quactlize_b200_ep_dispatch_dev_v1": (I, [P, P, P, P, P, P, I, I, I, P]),
+    "quactlize_b200_ep_return_addr_dev_v1": (I, [P, P, I, P, I, I, P, P]),
+    "quactlize_b200_ep_combine_dev_v1": (I, [P, P, P, P, I, I, I, P]),
+    "quactlize_b200_silu_mul_dev_v1": (I, [P, P, P, I, I, P]),
+    "quactlize_b200_gemm_plane_splitk_workspace_bytes_v1": (I64, [I, I, I]),
+    "quactlize_b200_gemm_plane_splitk_dev_v1": (I, [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, I, P, I64, P]),
     "quactlize_b200_dense_fully_quantized_static_v1": (I, [P, P, P, P, P, I, I, I, I, P]),
     "quactlize_ppu_units_bytes": (I64, [I, I, I]),
     "quactlize_ppu_prepare_units": (I, [P, P, I, I, I]),

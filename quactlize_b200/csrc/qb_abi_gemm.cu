@@ -10,6 +10,7 @@
 // (one bit-exact pre-pass launch) and then run the same GEMM.
 #include <cstdint>
 #include <cstdio>
+#include <algorithm>
 #include <cstring>
 
 #include "qb_internal.hpp"
@@ -24,15 +25,21 @@ namespace {
 // choose by rows per expert, a known name forces that tile, an unknown name is declined with a message and the default runs.
 constexpr char const* kTensorConfig = "256x256x64:tcgen05";
 constexpr char const* kTensorConfigSmall = "128x128x64:tcgen05";
+// grouped only: the decode tactic -- 128 x 128 tiles with two-deep rings (several CTAs per SM) and K split over gridDim.z
+// into fp32 partial planes that a light reduce kernel sums (quactlize/include/ppu_aiu_gemm_mixed_input_group.hpp:120-131,
+// 289-309 in the reference: slice z writes its own D plane).  Needs workspace for the partials; without it, it runs unsplit.
+constexpr char const* kTensorConfigSplitK = "128x128x64:tcgen05:splitk";
 quactlize_ppu_config_v1 const kDenseConfigs[] = {{false, kTensorConfig, 256, 256, 128, 256, 3}, {false, kTensorConfigSmall, 128, 128, 128, 128, 4},
                                                  {true, "gemv_lowbit", 0, 0, 0, 0, 0}};
 quactlize_ppu_config_v1 const kGroupedConfigs[] = {{false, kTensorConfig, 256, 256, 128, 256, 3}, {false, kTensorConfigSmall, 128, 128, 128, 128, 4},
-                                                   {true, "vecdot_moe", 0, 0, 0, 0, 0}};
+                                                   {false, kTensorConfigSplitK, 128, 128, 128, 128, 2}, {true, "vecdot_moe", 0, 0, 0, 0, 0}};
+constexpr int kSplitKTile = 129;                   // tile_of() value of the split-K tactic (a 128 tile, shallow, split)
 
 int tile_of(char const* name) {                    // 0 = default choice, 128 / 256 = forced tile, -1 = unknown name
   if (!name || !name[0]) return 0;
   if (std::strcmp(name, kTensorConfig) == 0) return 256;
   if (std::strcmp(name, kTensorConfigSmall) == 0) return 128;
+  if (std::strcmp(name, kTensorConfigSplitK) == 0) return kSplitKTile;
   return -1;
 }
 bool tensor_name_ok(char const* name) { return tile_of(name) >= 0; }
@@ -59,8 +66,22 @@ GemmDesc kq_desc(void const* act, uint8_t const* low, uint8_t const* high, void 
   d.act = act; d.low = low; d.high = kq::hi_bits(qtype) ? high : nullptr; d.scale = scale; d.zero = zero; d.out = out;
   d.offsets = offsets; d.total_rows = rows; d.n = n; d.k = k; d.experts = experts;
   d.group_size = kq::group_size(qtype); d.lo_bits = kq::lo_bits(qtype); d.hi_bits = kq::hi_bits(qtype);
-  d.code_offset = code_offset; d.act_bf16 = 0; d.tile = tile;
+  d.code_offset = code_offset; d.act_bf16 = 0; d.tile = tile == kSplitKTile ? 128 : tile;
+  d.shallow = tile == kSplitKTile ? 1 : 0;
   return d;
+}
+
+// split-K partial planes carved from what is left of a workspace; no room (or nothing to gain) leaves the launch unsplit
+void attach_splitk(GemmDesc& d, int tile, void* ws, int64_t ws_bytes) {
+  if (tile != kSplitKTile || d.experts <= 0) return;
+  int const s = splitk_auto(std::min(d.experts, d.total_rows), d.n, d.k);
+  int64_t const need = int64_t(s) * d.total_rows * d.n * 4;
+  uintptr_t const base = (reinterpret_cast<uintptr_t>(ws) + 15) & ~uintptr_t(15);
+  if (s > 1 && ws && int64_t(base - reinterpret_cast<uintptr_t>(ws)) + need <= ws_bytes) { d.splits = s; d.partial = reinterpret_cast<float*>(base); }
+}
+int64_t splitk_extra_bytes(int experts, int max_rows, int n) {      // room for 8 slices of a decode-sized problem, else none
+  int64_t const rows = int64_t(experts) * max_rows;
+  return rows <= 4096 ? 8 * rows * n * 4 + 16 : 0;
 }
 
 // cumulative offsets from per-expert row counts; false if a count is negative or the sum disagrees
@@ -108,6 +129,7 @@ int dev_units_gemm(uint16_t const* act, uint8_t const* low, uint8_t const* high,
   // the zero plane carries the matching correction, which keeps |zero| small and its fp16 rounding with it
   if (!enqueue_prepass_unit(units, sc, zr, we, n, k / 256, qtype, placed_zmul(qtype), s)) return 33;
   GemmDesc d = kq_desc(act, low, high, sc, zr, out, rows, n, k, qtype, experts, offsets, converter_offset(qtype), tile);
+  attach_splitk(d, tile, reinterpret_cast<uint8_t*>(workspace) + pe * 4, workspace_bytes - pe * 4);
   int const rc = enqueue_mixed_gemm(d, s);
   if (rc) return rc;
   return rt_check_launch(what) ? 0 : kRuntimeError;
@@ -146,10 +168,10 @@ extern "C" int32_t quactlize_ppu_list_configs(quactlize_ppu_config_v1 const** co
 }
 extern "C" int32_t quactlize_ppu_list_grouped_configs(quactlize_ppu_config_v1 const** configs) {
   if (configs) *configs = kGroupedConfigs;
-  return 3;
+  return 4;
 }
 extern "C" int32_t quactlize_ppu_dense_lowbit_config_valid_v1(int m, int n, int k, int group_size, int qtype, char const* name) {
-  return tensor_name_ok(name) && kq::raw_bytes(qtype) != 0 && m > 0 && shape_ok(n, k) && group_size == kq::group_size(qtype);
+  return tensor_name_ok(name) && tile_of(name) != kSplitKTile && kq::raw_bytes(qtype) != 0 && m > 0 && shape_ok(n, k) && group_size == kq::group_size(qtype);
 }
 extern "C" int32_t quactlize_ppu_dense_fully_quantized_config_valid_v1(int m, int n, int k, int group_size, int qtype, char const* name) {
   return quactlize_ppu_dense_lowbit_config_valid_v1(m, n, k, group_size, qtype, name) && fq_ok(k, qtype);
@@ -176,7 +198,10 @@ extern "C" int32_t quactlize_ppu_list_valid_dense_fully_quantized_configs_v2(qua
 }
 extern "C" int32_t quactlize_ppu_list_valid_grouped_fully_quantized_configs_v2(quactlize_ppu_config_v2* c, int32_t cap, int total_rows,
                                                                                int n, int k, int gs, int experts, int max_rows, int qtype) {
-  return list_one(c, cap, quactlize_ppu_grouped_fully_quantized_config_valid_v1(total_rows, n, k, gs, experts, max_rows, qtype, nullptr));
+  bool const valid = quactlize_ppu_grouped_fully_quantized_config_valid_v1(total_rows, n, k, gs, experts, max_rows, qtype, nullptr);
+  int32_t const base = list_one(c, cap, valid);
+  if (valid && c && cap > 2) c[2] = {false, kTensorConfigSplitK, 128, 128, 64, 128, 128, 2};
+  return valid ? base + 1 : 0;
 }
 
 // ---- dense, scale-first ------------------------------------------------------------------------------------------------
@@ -246,19 +271,19 @@ extern "C" int quactlize_ppu_grouped_lowbit(uint16_t const* act, uint8_t const* 
 }
 extern "C" int64_t quactlize_ppu_grouped_lowbit_workspace_bytes_v1(int max_rows, int n, int k, int group_size, int experts, int qtype) {
   if (!quactlize_ppu_grouped_lowbit_config_valid_v1(max_rows, n, k, group_size, experts, max_rows, qtype, nullptr)) return -1;
-  return 256;                                   // this implementation needs no device workspace; a token size keeps callers simple
+  return 256 + splitk_extra_bytes(experts, max_rows, n);   // only the split-K tactic uses a workspace (its fp32 partial planes)
 }
 extern "C" int quactlize_ppu_grouped_lowbit_dev_v2(uint16_t const* act, uint8_t const* low, uint8_t const* high,
                                                    uint16_t const* scale, int const* offsets, uint16_t* out, int total_rows, int n,
                                                    int k, int group_size, int experts, int max_rows, int qtype, void* workspace,
                                                    int64_t workspace_bytes, void* stream, char const* config_name) {
-  (void)workspace;
   int64_t const need = quactlize_ppu_grouped_lowbit_workspace_bytes_v1(max_rows, n, k, group_size, experts, qtype);
   if (!act || !low || !scale || !offsets || !out || total_rows <= 0 || need < 0 || workspace_bytes < need ||
       (kq::hi_bits(qtype) && !high)) return 30;
   int const tile = decline(config_name);
   rt_clear_error();
   GemmDesc d = kq_desc(act, low, high, scale, nullptr, out, total_rows, n, k, qtype, experts, offsets, centred_offset(qtype), tile);
+  attach_splitk(d, tile, workspace, workspace_bytes);
   int const rc = enqueue_mixed_gemm(d, static_cast<cudaStream_t>(stream));
   if (rc) return rc;
   return rt_check_launch("scale-first grouped GEMM enqueue") ? 0 : kRuntimeError;
@@ -288,7 +313,7 @@ extern "C" int quactlize_ppu_grouped_fully_quantized(uint16_t const* act, uint8_
 }
 extern "C" int64_t quactlize_ppu_grouped_fully_quantized_workspace_bytes_v1(int max_rows, int n, int k, int experts, int qtype) {
   if (max_rows <= 0 || !shape_ok(n, k) || experts <= 0 || !fq_ok(k, qtype)) return -1;
-  return plane_elems(n, k, experts, qtype) * 4;
+  return plane_elems(n, k, experts, qtype) * 4 + splitk_extra_bytes(experts, max_rows, n);
 }
 extern "C" int quactlize_ppu_grouped_fully_quantized_dev_v2(uint16_t const* act, uint8_t const* low, uint8_t const* high,
                                                             uint8_t const* units, int const* offsets, uint16_t* out,
@@ -311,6 +336,49 @@ extern "C" int quactlize_ppu_grouped_fully_quantized_dev_v1(uint16_t const* act,
 }
 
 // ---- additive: generic per-group planes, fp16 or bf16 activations, dense (experts == 0) or grouped ------------------------
+extern "C" int64_t quactlize_b200_gemm_plane_splitk_workspace_bytes_v1(int total_rows, int n, int splits) {
+  if (total_rows <= 0 || n <= 0 || splits < 0 || splits > 64) return -1;
+  return int64_t(splits > 1 ? splits : 8) * total_rows * n * 4;       // splits 0 = chosen by the library, at most 8
+}
+extern "C" int quactlize_b200_gemm_plane_splitk_dev_v1(void const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale,
+                                                       uint16_t const* zero, void* out, int total_rows, int n, int k, int bits_lo,
+                                                       int bits_hi, int group_size, int code_offset, int act_dtype, int experts,
+                                                       int const* offsets, int splits, void* workspace, int64_t workspace_bytes,
+                                                       void* stream) {
+  if (act_dtype < 0 || act_dtype > 1 || experts < 0 || splits < 0 || total_rows <= 0 || n <= 0) return 30;
+  rt_clear_error();
+  GemmDesc d{};
+  d.act = act; d.low = low; d.high = bits_hi ? high : nullptr; d.scale = scale; d.zero = zero; d.out = out;
+  d.offsets = offsets; d.total_rows = total_rows; d.n = n; d.k = k; d.experts = experts; d.group_size = group_size;
+  d.lo_bits = bits_lo; d.hi_bits = bits_hi; d.code_offset = code_offset; d.act_bf16 = act_dtype;
+  d.tile = 128; d.shallow = 1;
+  int const row_tiles = experts > 0 ? std::min(experts, total_rows) : (total_rows + 127) / 128;
+  d.splits = splits ? splits : splitk_auto(row_tiles, n, k);
+  if (d.splits > 1) {
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15) || workspace_bytes < int64_t(d.splits) * total_rows * n * 4) return 37;
+    d.partial = static_cast<float*>(workspace);
+  }
+  int const rc = enqueue_mixed_gemm(d, static_cast<cudaStream_t>(stream));
+  if (rc) return rc;
+  return rt_check_launch("split-K plane GEMM enqueue") ? 0 : kRuntimeError;
+}
+
+extern "C" int quactlize_b200_gemm_plane_dev_v2(void const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale,
+                                                uint16_t const* zero, void* out, int total_rows, int n, int k, int bits_lo,
+                                                int bits_hi, int group_size, int code_offset, int act_dtype, int experts,
+                                                int const* offsets, unsigned long long const* out_rows, void* stream) {
+  if (act_dtype < 0 || act_dtype > 1 || experts < 0) return 30;
+  rt_clear_error();
+  GemmDesc d{};
+  d.act = act; d.low = low; d.high = bits_hi ? high : nullptr; d.scale = scale; d.zero = zero; d.out = out;
+  d.offsets = offsets; d.total_rows = total_rows; d.n = n; d.k = k; d.experts = experts; d.group_size = group_size;
+  d.lo_bits = bits_lo; d.hi_bits = bits_hi; d.code_offset = code_offset; d.act_bf16 = act_dtype;
+  d.out_rows = out_rows;
+  int const rc = enqueue_mixed_gemm(d, static_cast<cudaStream_t>(stream));
+  if (rc) return rc;
+  return rt_check_launch("plane GEMM enqueue") ? 0 : kRuntimeError;
+}
+
 extern "C" int quactlize_b200_gemm_plane_dev_v1(void const* act, uint8_t const* low, uint8_t const* high, uint16_t const* scale,
                                                 uint16_t const* zero, void* out, int total_rows, int n, int k, int bits_lo,
                                                 int bits_hi, int group_size, int code_offset, int act_dtype, int experts,

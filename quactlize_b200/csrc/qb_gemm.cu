@@ -30,6 +30,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdint>
 #include <cstdio>
 #include <mutex>
@@ -53,14 +54,20 @@ struct GemmArgs {
   void* out;
   int m_rows, n, k, experts, group_size;
   int code_offset, has_zero;
+  int splits;              // K slices (gridDim.z); > 1: slice z accumulates its own 128-k pieces and writes fp32 to `partial`
+  float* partial;          // [splits][m_rows][n] fp32 (split-K only), summed by splitk_reduce_kernel
+  unsigned long long const* out_rows;   // optional: the address output row r is stored at (n elements), instead of out + r*n
   unsigned int* status;
 };
 
-template <int LO, int HI, int MT, int NT> struct GemmSmem {
+// DEPTH 0: rings sized for one CTA per SM (prefill tiles).  DEPTH 1 (128 x 128 only): two-deep rings, about 75 KB, so that
+// two or three CTAs share an SM -- decode-sized grouped problems are bound by the latency of one CTA's
+// copy -> dequantise -> MMA chain, and co-resident CTAs overlap those chains.
+template <int LO, int HI, int MT, int NT, int DEPTH = 0> struct GemmSmem {
   static constexpr bool kBig = MT * NT == 4;
-  static constexpr int AST = kBig ? 3 : 4;            // activation ring: 64-k tiles of 128*MT rows
-  static constexpr int BST = kBig ? 2 : 4;            // dequantised operand ring: 64-k tiles of 128*NT columns
-  static constexpr int RST = kBig ? 2 : 3;            // raw ring: 128-k pieces of planes + scale rows
+  static constexpr int AST = DEPTH ? 2 : (kBig ? 3 : 4);   // activation ring: 64-k tiles of 128*MT rows
+  static constexpr int BST = DEPTH ? 2 : (kBig ? 2 : 4);   // dequantised operand ring: 64-k tiles of 128*NT columns
+  static constexpr int RST = DEPTH ? 2 : (kBig ? 2 : 3);   // raw ring: 128-k pieces of planes + scale rows
   static constexpr int kLoBytes = kTN * kRawK * LO / 8, kHiBytes = HI ? kTN * kRawK * HI / 8 : 1024;
   alignas(1024) uint8_t a[AST][MT * kATileBytes];
   alignas(1024) uint8_t b[BST][NT * kBTileBytes];
@@ -234,13 +241,13 @@ __device__ __forceinline__ void dequant_col(uint8_t const* lo_tile, uint8_t cons
 
 // ---- the kernel -----------------------------------------------------------------------------------------------------
 
-template <int LO, int HI, bool BF16, int MT, int NT>
-__global__ void __launch_bounds__(128 + 128 * MT, 1)
+template <int LO, int HI, bool BF16, int MT, int NT, int DEPTH>
+__global__ void __launch_bounds__(128 + 128 * MT, DEPTH ? 2 : 1)
 mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_lo,
                   const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ CUtensorMap map_s,
                   const __grid_constant__ CUtensorMap map_z, GemmArgs g) {
   extern __shared__ uint8_t smem_raw[];
-  using SM = GemmSmem<LO, HI, MT, NT>;
+  using SM = GemmSmem<LO, HI, MT, NT, DEPTH>;
   constexpr int AST = SM::AST, BST = SM::BST, RST = SM::RST, kRows = kTM * MT, kCols = kTN * NT;
   constexpr int kDqWarps = 4 * MT;                            // also the epilogue warps: one per 32 accumulator lanes
   constexpr int NC = 8 * NT / MT;                             // 8-element chunks a dequant thread converts per stage
@@ -250,14 +257,38 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   // ---- which tile: blockIdx.x = weight-column tile, blockIdx.y = row tile (grouped: searched in the per-expert counts)
   int e = 0, m0, mrows;
   if (g.offsets) {
-    int t = blockIdx.y, acc = 0;
-    bool found = false;
-    for (int x = 0; x < g.experts; ++x) {
-      int const r0 = g.offsets[x], rows = g.offsets[x + 1] - r0, cnt = (rows + kRows - 1) / kRows;
-      if (t < acc + cnt) { e = x; m0 = r0 + (t - acc) * kRows; mrows = min(kRows, rows - (t - acc) * kRows); found = true; break; }
-      acc += cnt;
+    // warp 0 scans the per-expert tile counts 32 experts at a time (a decode launch has over a hundred experts and
+    // most CTAs of the grid's upper bound find no tile: the lookup is their whole cost)
+    __shared__ int tile_of[4];                                // expert, first row, rows, found
+    if (warp == 0) {
+      int const t = blockIdx.y;
+      int carry = 0, hit_e = -1, hit_m0 = 0, hit_rows = 0;
+      for (int base = 0; base < g.experts && hit_e < 0; base += 32) {
+        int const x = base + lane;
+        int r0 = 0, rows = 0;
+        if (x < g.experts) { r0 = g.offsets[x]; rows = g.offsets[x + 1] - r0; }
+        int const cnt = (rows + kRows - 1) / kRows;
+        int incl = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { int const u = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += u; }
+        int const lo = carry + incl - cnt;                    // tiles before this expert
+        bool const mine = cnt > 0 && t >= lo && t < lo + cnt;
+        unsigned const who = __ballot_sync(0xffffffffu, mine);
+        if (who) {
+          int const src = __ffs(who) - 1;
+          hit_e = __shfl_sync(0xffffffffu, x, src);
+          int const lo_s = __shfl_sync(0xffffffffu, lo, src), r0_s = __shfl_sync(0xffffffffu, r0, src),
+                    rows_s = __shfl_sync(0xffffffffu, rows, src);
+          hit_m0 = r0_s + (t - lo_s) * kRows;
+          hit_rows = min(kRows, rows_s - (t - lo_s) * kRows);
+        }
+        carry += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0) { tile_of[0] = hit_e; tile_of[1] = hit_m0; tile_of[2] = hit_rows; }
     }
-    if (!found) return;                                       // uniform for the CTA, before any barrier or allocation
+    __syncthreads();
+    e = tile_of[0]; m0 = tile_of[1]; mrows = tile_of[2];
+    if (e < 0) return;                                        // uniform for the CTA, before any mbarrier or TMEM allocation
   } else {
     m0 = blockIdx.y * kRows; mrows = min(kRows, g.m_rows - m0);
     if (mrows <= 0) return;
@@ -265,7 +296,12 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   int const n0 = blockIdx.x * kCols;
   int const nt_here = min(NT, (g.n - n0) / kTN);              // a 256-wide tile may hang over the last 128 columns
   int const mt_here = min(MT, (mrows + kTM - 1) / kTM);       // ... and a ragged row tile over the last 128 rows
-  int const nks = g.k / kTK;                                  // 64-k stages (k is a multiple of 256)
+  // split-K: slice z owns a contiguous run of 128-k pieces (pieces are dealt as evenly as they divide); its stages are
+  // numbered from 0 for the rings, and offset by ks0 stages / p0 pieces where global k coordinates are formed
+  int const pieces = g.k / kRawK, z = blockIdx.z, S = g.splits;
+  int const p0 = int((long long)pieces * z / S), p1 = int((long long)pieces * (z + 1) / S);
+  int const ks0 = 2 * p0;
+  int const nks = 2 * (p1 - p0);                              // 64-k stages of this slice (k is a multiple of 256)
   int const gs = g.group_size;
   int const srows = gs >= kRawK ? 1 : kRawK / gs;             // scale rows per 128-k piece
 
@@ -298,7 +334,7 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           int const j = i >> 1, r = j % RST;
           if (j >= RST && !gemm_wait(sm, &sm.raw_empty[r], unsigned(j / RST - 1) & 1u, g.status)) break;
           mbar_expect_tx(&sm.raw_full[r], raw_bytes);
-          int const kk = j * kRawK;
+          int const kk = (p0 + j) * kRawK;
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {                    // columns past n are out of bounds: zero-filled, still counted
             tma_load_3d(sm.raw_lo[r][nt], &map_lo, kk * LO / 8, n0 + nt * kTN, e, &sm.raw_full[r]);
@@ -312,7 +348,7 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         if (i >= AST) { mbar_arrive(&sm.a_full[sa]); continue; }
 #endif
         mbar_expect_tx(&sm.a_full[sa], MT * kATileBytes);
-        tma_load_2d(sm.a[sa], &map_a, i * kTK, m0, &sm.a_full[sa]);
+        tma_load_2d(sm.a[sa], &map_a, (ks0 + i) * kTK, m0, &sm.a_full[sa]);
       }
     }
   } else if (warp == 1) {
@@ -388,7 +424,15 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
               "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
             : "r"(taddr) : "memory");
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row < mrows) {
+        if (S > 1) {                                           // fp32 partial sums of this K slice
+          if (row < mrows) {
+            float4* dst = reinterpret_cast<float4*>(g.partial + (size_t(z) * g.m_rows + size_t(m0 + row)) * g.n + n0 + c);
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              dst[u] = make_float4(__uint_as_float(v[4 * u]), __uint_as_float(v[4 * u + 1]), __uint_as_float(v[4 * u + 2]),
+                                   __uint_as_float(v[4 * u + 3]));
+          }
+        } else if (row < mrows) {
           uint32_t pk[16];
 #pragma unroll
           for (int u = 0; u < 16; ++u) {
@@ -396,7 +440,10 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             if constexpr (BF16) { __nv_bfloat162 const hh = __floats2bfloat162_rn(f0, f1); pk[u] = *reinterpret_cast<uint32_t const*>(&hh); }
             else { __half2 const hh = __floats2half2_rn(f0, f1); pk[u] = *reinterpret_cast<uint32_t const*>(&hh); }
           }
-          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(g.out) + orow + c);
+          // a row map sends every output row to its own destination (another rank's buffer in expert parallelism: plain
+          // 16-byte stores, peer memory is written but never read here)
+          uint4* dst = g.out_rows ? reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(g.out_rows[m0 + row]) + n0 + c)
+                                  : reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(g.out) + orow + c);
 #pragma unroll
           for (int u = 0; u < 4; ++u) dst[u] = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
         }
@@ -416,6 +463,29 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(uint32_t(kTN * MT * NT)) : "memory");
   }
+}
+
+// Light reduce of the split-K partial planes: out[r][c] = sum_z partial[z][r][c], converted to the output type.  A thread
+// owns four consecutive columns; slices are summed in slice order, so the result does not depend on scheduling.
+template <bool BF16>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(float const* __restrict__ partial, void* __restrict__ out,
+                                                            int64_t elems, int splits) {
+  int64_t const i = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+  if (i >= elems) return;
+  float4 acc = *reinterpret_cast<float4 const*>(partial + i);
+  for (int z = 1; z < splits; ++z) {
+    float4 const v = *reinterpret_cast<float4 const*>(partial + int64_t(z) * elems + i);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  uint2 o;
+  if constexpr (BF16) {
+    __nv_bfloat162 const a = __floats2bfloat162_rn(acc.x, acc.y), b = __floats2bfloat162_rn(acc.z, acc.w);
+    o.x = *reinterpret_cast<uint32_t const*>(&a); o.y = *reinterpret_cast<uint32_t const*>(&b);
+  } else {
+    __half2 const a = __floats2half2_rn(acc.x, acc.y), b = __floats2half2_rn(acc.z, acc.w);
+    o.x = *reinterpret_cast<uint32_t const*>(&a); o.y = *reinterpret_cast<uint32_t const*>(&b);
+  }
+  *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(out) + i) = o;
 }
 
 // ---- host side: tensor maps and launch ---------------------------------------------------------------------------------
@@ -455,7 +525,7 @@ inline CUtensorMapSwizzle plane_swizzle(int row_bytes) {
   return row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : (row_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
-template <int LO, int HI, bool BF16, int MT, int NT>
+template <int LO, int HI, bool BF16, int MT, int NT, int DEPTH = 0>
 int launch_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
   int const E = d.experts > 0 ? d.experts : 1;
   int const gs = d.group_size;
@@ -500,11 +570,17 @@ int launch_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
   g.offsets = d.experts > 0 ? d.offsets : nullptr;
   g.out = d.out; g.m_rows = d.total_rows; g.n = d.n; g.k = d.k; g.experts = E; g.group_size = gs;
   g.code_offset = d.code_offset; g.has_zero = d.zero ? 1 : 0;
+  int const splits = d.splits > 1 ? d.splits : 1;
+  if (splits > d.k / kRawK || splits > 64 || (splits > 1 && !d.partial)) return 30;    // every slice owns at least one piece
+  g.splits = splits; g.partial = d.partial;
+  g.out_rows = d.out_rows;
+  if (d.out_rows && splits > 1) return 30;                     // the reduce kernel writes the dense layout only
   g.status = rt_device_status_ptr();
   if (!g.status) return kRuntimeError;
-  auto kern = mixed_gemm_kernel<LO, HI, BF16, MT, NT>;
-  size_t const smem = sizeof(GemmSmem<LO, HI, MT, NT>) + 1024;
-  static_assert(sizeof(GemmSmem<LO, HI, MT, NT>) + 1024 <= 232448, "shared memory of one CTA");
+  auto kern = mixed_gemm_kernel<LO, HI, BF16, MT, NT, DEPTH>;
+  size_t const smem = sizeof(GemmSmem<LO, HI, MT, NT, DEPTH>) + 1024;
+  static_assert(sizeof(GemmSmem<LO, HI, MT, NT, DEPTH>) + 1024 <= 232448, "shared memory of one CTA");
+  static_assert(DEPTH == 0 || sizeof(GemmSmem<LO, HI, MT, NT, DEPTH>) + 1024 <= 113 * 1024, "two CTAs of the shallow form share an SM");
   {  // the opt-in to large dynamic shared memory is a per-device attribute of the function
     static std::mutex mu;
     static bool attr_set[kMaxDevices] = {};
@@ -519,9 +595,15 @@ int launch_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
       attr_set[dev] = true;
     }
   }
-  int const mtiles = (d.total_rows + kTM * MT - 1) / (kTM * MT) + (d.experts > 0 ? d.experts : 0);
+  // row tiles: sum over experts of ceil(rows_e / tile) <= floor(total / tile) + the experts that hold rows
+  int const mtiles = d.experts > 0 ? d.total_rows / (kTM * MT) + std::min(d.experts, d.total_rows)
+                                   : (d.total_rows + kTM * MT - 1) / (kTM * MT);
   if (mtiles > 65535) return 30;
-  kern<<<dim3((d.n + kTN * NT - 1) / (kTN * NT), mtiles), 128 + 128 * MT, smem, stream>>>(ma, ml, mh, ms, mz, g);
+  kern<<<dim3((d.n + kTN * NT - 1) / (kTN * NT), mtiles, splits), 128 + 128 * MT, smem, stream>>>(ma, ml, mh, ms, mz, g);
+  if (splits > 1) {
+    int64_t const elems = int64_t(d.total_rows) * d.n;         // n % 128 == 0: whole float4 groups
+    splitk_reduce_kernel<BF16><<<unsigned((elems / 4 + 255) / 256), 256, 0, stream>>>(d.partial, d.out, elems, splits);
+  }
   return 0;
 }
 
@@ -533,15 +615,24 @@ bool tma_make_map(CUtensorMap* m, CUtensorMapDataType dt, int rank, void const* 
 }
 
 int enqueue_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
-  if (!d.act || !d.low || !d.scale || !d.out || d.total_rows <= 0 || d.n <= 0 || d.n % kTN || d.k <= 0 || d.k % 256 ||
+  if (!d.act || !d.low || !d.scale || (!d.out && !d.out_rows) || d.total_rows <= 0 || d.n <= 0 || d.n % kTN || d.k <= 0 || d.k % 256 ||
       d.group_size < 16 || (d.group_size & (d.group_size - 1)) || d.k % d.group_size || (d.hi_bits && !d.high) ||
       (d.experts > 0 && !d.offsets)) return 30;
   auto al = [](void const* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
-  if (!al(d.act) || !al(d.low) || !al(d.scale) || !al(d.out) || (d.zero && !al(d.zero)) || (d.hi_bits && !al(d.high))) return 30;
+  if (!al(d.act) || !al(d.low) || !al(d.scale) || (d.out && !al(d.out)) || (d.zero && !al(d.zero)) || (d.hi_bits && !al(d.high))) return 30;
   int const key = d.lo_bits * 10 + d.hi_bits;
   // 256 x 256 CTA tiles (four accumulators = all 512 TMEM columns) for prefill-sized problems; small ones keep 128 x 128
   int const avg_rows = d.experts > 0 ? d.total_rows / d.experts : d.total_rows;
   bool const big = d.tile == 256 || (d.tile == 0 && avg_rows >= 192);
+  if (d.shallow && !big) {                        // decode tactic: 128 x 128 tiles, two-deep rings, several CTAs per SM
+#define QB_GEMM_SHALLOW(K, L, H) case K: return d.act_bf16 ? launch_mixed_gemm<L, H, true, 1, 1, 1>(d, stream) : launch_mixed_gemm<L, H, false, 1, 1, 1>(d, stream);
+    switch (key) {
+      QB_GEMM_SHALLOW(40, 4, 0) QB_GEMM_SHALLOW(41, 4, 1) QB_GEMM_SHALLOW(42, 4, 2) QB_GEMM_SHALLOW(20, 2, 0) QB_GEMM_SHALLOW(21, 2, 1)
+      QB_GEMM_SHALLOW(10, 1, 0)
+      default: return 33;
+    }
+#undef QB_GEMM_SHALLOW
+  }
 #define QB_GEMM_CASE(K, L, H) case K: return d.act_bf16 ? (big ? launch_mixed_gemm<L, H, true, 2, 2>(d, stream) : launch_mixed_gemm<L, H, true, 1, 1>(d, stream)) \
                                                         : (big ? launch_mixed_gemm<L, H, false, 2, 2>(d, stream) : launch_mixed_gemm<L, H, false, 1, 1>(d, stream));
   switch (key) {
@@ -552,4 +643,14 @@ int enqueue_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
 #undef QB_GEMM_CASE
 }
 
+}  // namespace qb
+
+namespace qb {
+int splitk_auto(int row_tiles, int n, int k) {
+  int const tiles = std::max(1, row_tiles) * ((n + kTN - 1) / kTN);
+  int const want = 2 * rt_sm_count();                      // two shallow CTAs per SM
+  int s = (want + tiles - 1) / tiles;
+  s = std::min(s, std::min(8, k / kRawK / 2));             // a slice keeps at least two 128-k pieces
+  return std::max(1, s);
+}
 }  // namespace qb

@@ -56,7 +56,14 @@ struct GemmDesc {
   int const* offsets;         // cumulative device int [experts+1] (grouped)
   int total_rows, n, k, experts, group_size, lo_bits, hi_bits, code_offset, act_bf16;
   int tile;                   // 0 = chosen from the problem size, 128 / 256 = that CTA tile (the two compiled tactics)
+  int splits;                 // split-K slices; 0 or 1 = none.  > 1 needs `partial` and at most k/128 slices
+  float* partial;             // fp32 [splits][total_rows][n] workspace of the split-K form (caller-owned)
+  int shallow;                // 1 = the decode tactic: 128 x 128 tiles with two-deep rings (several CTAs per SM)
+  unsigned long long const* out_rows;   // optional device array [total_rows]: where each output row goes (see GemmArgs)
 };
+// Split-K slices that fill the SMs for a decode-sized grouped problem: row_tiles is the number of (expert, row tile)
+// pairs that hold rows (an upper bound is fine).  1 when the plain launch already gives every SM a tile.
+int splitk_auto(int row_tiles, int n, int k);
 int enqueue_mixed_gemm(GemmDesc const& d, cudaStream_t stream);    // 0 ok, 30/33 refused, 41 runtime
 
 }  // namespace qb

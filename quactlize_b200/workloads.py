@@ -227,9 +227,20 @@ def cfg5(bits: int, which: str, tokens: int, dev="cuda:0", run: Optional[Callabl
                 "row_offsets": offs[0], "out": "bf16"}
     act = float(np.mean([(c > 0).sum() for c in counts[:nb]]))
     wb = int(act * per_expert)
+    if run is not None:
+        return Case(f"cfg5_w{bits}a16_{which}_t{tokens}_splitk", "hbm", wb, int(act * (per_expert + sz_expert)) + rows * k * 2 + rows * n * 2,
+                    2.0 * rows * n * k, nb, launch, sample, "mixed_gemm_kernel (split-K) + splitk_reduce_kernel",
+                    {"rows": rows, "active_experts_mean": round(act, 1), "banks": nb, "scale_zero_bytes": int(act * sz_expert)})
     return Case(f"cfg5_w{bits}a16_{which}_t{tokens}", "hbm", wb, int(act * (per_expert + sz_expert)) + rows * k * 2 + rows * n * 2,
                 2.0 * rows * n * k, nb, launch, sample, "rowmma_gemv_kernel",
                 {"rows": rows, "active_experts_mean": round(act, 1), "banks": nb, "scale_zero_bytes": int(act * sz_expert)})
+
+
+def cfg5_splitk(bits: int, which: str, tokens: int, dev="cuda:0") -> Case:
+    """cfg5 through the tensor-core split-K grouped GEMM (128 x 128 tiles, shallow rings, K slices chosen by the library)."""
+    gs = 64
+    return cfg5(bits, which, tokens, dev,
+                run=lambda a_, lo, sc, ze, off, mr: qb.gemm_plane(a_, lo, None, sc, ze, bits, 0, gs, row_offsets=off, split_k=0))
 
 
 def fpa(dev="cuda:0") -> Case:
@@ -321,6 +332,9 @@ def registry() -> Dict[str, Callable[[], Case]]:
         for w in ("gate_up", "down"):
             for t in (1, 8, 64):
                 r[f"cfg5_w{bits}_{w}_t{t}"] = (lambda bits=bits, w=w, t=t: cfg5(bits, w, t))
+    for w in ("gate_up", "down"):                 # the same decode MoE through the split-K tensor-core grouped GEMM
+        for t in (1, 8, 64):
+            r[f"cfg5_w2_{w}_t{t}_splitk"] = (lambda w=w, t=t: cfg5_splitk(2, w, t))
     r["fpa"] = fpa
     r["aux_dequant_q4k"] = aux_dequant
     r["aux_dequant_q6k"] = (lambda: aux_dequant(14))

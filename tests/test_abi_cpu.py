@@ -82,7 +82,19 @@ def test_tensor_tactic_inventory():
         assert L.quactlize_ppu_dense_lowbit_config_valid_v1(64, 4096, 4096, 32, 12, name) == 1
         assert L.quactlize_ppu_grouped_fully_quantized_config_valid_v1(64, 4096, 4096, 32, 8, 64, 12, name) == 1
     assert L.quactlize_ppu_dense_lowbit_config_valid_v1(64, 4096, 4096, 32, 12, b"64x64x64:other") == 0
-    assert L.quactlize_ppu_list_configs(None) == 3 and L.quactlize_ppu_list_grouped_configs(None) == 3
+    assert L.quactlize_ppu_list_configs(None) == 3 and L.quactlize_ppu_list_grouped_configs(None) == 4
+    # the split-K decode tactic belongs to the grouped routes only
+    sk = b"128x128x64:tcgen05:splitk"
+    assert L.quactlize_ppu_grouped_fully_quantized_config_valid_v1(64, 4096, 4096, 32, 8, 64, 12, sk) == 1
+    assert L.quactlize_ppu_grouped_lowbit_config_valid_v1(64, 4096, 4096, 32, 8, 64, 12, sk) == 1
+    assert L.quactlize_ppu_dense_lowbit_config_valid_v1(64, 4096, 4096, 32, 12, sk) == 0
+    assert L.quactlize_ppu_list_valid_grouped_fully_quantized_configs_v2(cfg, 4, 64, 4096, 4096, 32, 8, 64, 12) == 3 and cfg[2].name == sk
+    # its fp32 partial planes: the generic query, and the extra room the reference-shaped queries add for decode sizes
+    assert L.quactlize_b200_gemm_plane_splitk_workspace_bytes_v1(512, 1536, 4) == 4 * 512 * 1536 * 4
+    assert L.quactlize_b200_gemm_plane_splitk_workspace_bytes_v1(512, 1536, 0) == 8 * 512 * 1536 * 4
+    assert L.quactlize_b200_gemm_plane_splitk_workspace_bytes_v1(512, 1536, 65) == -1
+    assert L.quactlize_ppu_grouped_lowbit_workspace_bytes_v1(8, 1536, 2048, 32, 128, 12) == 256 + 8 * 128 * 8 * 1536 * 4 + 16
+    assert L.quactlize_ppu_grouped_lowbit_workspace_bytes_v1(4096, 14336, 4096, 32, 8, 12) == 256      # prefill sizes: no split-K
 
 
 def _eq(a, b):

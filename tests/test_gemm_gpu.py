@@ -125,3 +125,62 @@ def test_named_tensor_tactics_agree(rows):
         assert valid == (0 if name == b"64x64x64:unknown" else 1)
     for name, out in outs.items():
         assert torch.equal(out, outs[None]), name
+
+
+# ---- split-K (decode) form -----------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("split", [0, 1, 2, 3, 5])
+@pytest.mark.parametrize("bits,gs,k", [(4, 128, 1024), (2, 64, 2048), (1, 64, 768)])
+def test_gemm_plane_split_k_grouped(split, bits, gs, k):
+    """K split over `split` slices of whole 128-k pieces (uneven when they do not divide), fp32 partial planes, reduce."""
+    e, n = 5, 256
+    rows = [3, 0, 130, 1, 8]
+    low, scale, zero = synth.group_planes(e, n, k, bits, gs, seed=bits + k)
+    a = torch.from_numpy(synth.activations(sum(rows), k, seed=11, dtype=np.float32)).to(torch.bfloat16)
+    off = np.concatenate([[0], np.cumsum(rows)]).astype(np.int32)
+    ref = kq.planes_matmul(a.float().numpy(), low, None, scale, zero, bits, 0, gs, off)
+    args = (a.to(DEV), _cuda(low), None, _cuda(scale), _cuda(zero), bits, 0, gs)
+    out = qb.gemm_plane(*args, row_offsets=_cuda(off), split_k=split)
+    _check(out, ref, True)
+    plain = qb.gemm_plane(*args, row_offsets=_cuda(off))
+    assert kq.max_rel(out.float().cpu().numpy(), plain.float().cpu().numpy()) < 4e-3     # same sums, fp32 order differs
+    again = qb.gemm_plane(*args, row_offsets=_cuda(off), split_k=split)
+    assert torch.equal(out, again)                                                      # slices are summed in a fixed order
+
+
+def test_gemm_plane_split_k_dense_and_limits():
+    m, n, k, bits, gs = 40, 384, 1024, 4, 32
+    low, scale, zero = synth.group_planes(1, n, k, bits, gs, seed=5)
+    a = torch.from_numpy(synth.activations(m, k, seed=3))
+    ref = kq.planes_matmul(a.numpy(), low, None, scale, zero, bits, 0, gs)
+    out = qb.gemm_plane(a.to(DEV), _cuda(low), None, _cuda(scale), _cuda(zero), bits, 0, gs, split_k=8)   # one piece per slice
+    _check(out, ref)
+    with pytest.raises(RuntimeError):                                                    # more slices than 128-k pieces
+        qb.gemm_plane(a.to(DEV), _cuda(low), None, _cuda(scale), _cuda(zero), bits, 0, gs, split_k=9)
+
+
+def test_split_k_tactic_through_the_reference_shaped_entry():
+    """The grouped fully-quantized device entry with the split-K tactic name and a workspace sized by its own query."""
+    import ctypes
+    L = _lib.lib()
+    qt, e, n, k = 13, 6, 256, 1024
+    rows = [2, 0, 9, 1, 4, 3]
+    blocks = synth.kquant_blocks(qt, e * n * k // 256, seed=61)
+    low, high, units = (t.to(DEV) for t in qb.gguf_prepare_fully_quantized_grouped(torch.from_numpy(blocks), n, k, qt, e))
+    a = synth.activations(sum(rows), k, seed=8)
+    ad = _cuda(a)
+    off = np.concatenate([[0], np.cumsum(rows)]).astype(np.int32)
+    need = L.quactlize_ppu_grouped_fully_quantized_workspace_bytes_v1(max(rows), n, k, e, qt)
+    assert need > 4 * (k // 32) * n * e * 1                                             # planes plus room for partial planes
+    ws = torch.empty(need, dtype=torch.uint8, device=DEV)
+    outs = []
+    for name in (b"128x128x64:tcgen05:splitk", b"128x128x64:tcgen05"):
+        out = torch.empty((sum(rows), n), dtype=torch.float16, device=DEV)
+        rc = L.quactlize_ppu_grouped_fully_quantized_dev_v2(ad.data_ptr(), low.data_ptr(), high.data_ptr(), units.data_ptr(), _cuda(off).data_ptr(),
+                                                            out.data_ptr(), sum(rows), n, k, e, max(rows), qt, ws.data_ptr(), need,
+                                                            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), name)
+        assert rc == 0
+        outs.append(out)
+    ref = kq.vecdot_moe(blocks.reshape(e, n * k // 256, -1), a, off, n, k, qt)
+    _check(outs[0], ref)
+    _check(outs[1], ref)

@@ -71,6 +71,6 @@ def test_grouped_route_uses_the_grouped_predicate():
     lib = _lib.lib()
     seen = []
     table = tune.tune(lib, "mixtral-8x7b", "grouped_fully_quantized", 12, [64], reps=2,
-                      timer_for=lambda n, k: (lambda m, t: seen.append((m, t)) or (10.0 if t.startswith("128") else 20.0)))
-    assert {t for _, t in seen} == {"256x256x64:tcgen05", "128x128x64:tcgen05"}
+                      timer_for=lambda n, k: (lambda m, t: seen.append((m, t)) or {"128x128x64:tcgen05": 10.0, "256x256x64:tcgen05": 20.0}.get(t, 15.0)))
+    assert {t for _, t in seen} == {"256x256x64:tcgen05", "128x128x64:tcgen05", "128x128x64:tcgen05:splitk"}
     assert all(s["buckets"][0]["config"] == "128x128x64:tcgen05" for s in table["shapes"])
