@@ -393,6 +393,15 @@ int enqueue_native_gemv(uint8_t const* blocks, __half const* x, float* out, int 
   // several activation rows per weight pass: the tensor-core kernel (QUACTLIZE_B200_Q4K_SMALLM=off keeps the CUDA-core ones)
   static bool const no_mma = [] { char const* v = std::getenv("QUACTLIZE_B200_Q4K_SMALLM"); return v && v[0] == 'o'; }();
   bool const batch = offsets ? m_rows >= 2 * a.experts : m_rows >= 2;
+  // dense, 2..8 rows: a CTA per row range, a warp per superblock of the K pass, all eight rows as one MMA operand.  Where
+  // K needs more than one pass (more than 16 superblocks per row) it pays an activation prologue per pass and is used from
+  // five rows up only (measured on 14336-deep rows: 19.3-19.7 us for any row count against 14.7-17.4 us of the tile kernel
+  // at 2-4 rows and 26 us at 5-8).  QUACTLIZE_B200_Q4K_ROWS=off skips it, =all sends every count from one row through it.
+  static int const rows_mode = [] { char const* v = std::getenv("QUACTLIZE_B200_Q4K_ROWS"); return !v ? 1 : (v[0] == 'o' ? 0 : (v[0] == 'a' ? 2 : 1)); }();
+  bool const rows_fit = rows_mode == 2 || (m_rows >= 2 && (bpr <= 16 || m_rows >= 5));
+  if (qtype == 12 && !per_row_x && !force_generic && !offsets && a.status && rows_mode && m_rows <= 8 && rows_fit) {
+    if (enqueue_q4k_rows(blocks, x, out, n, bpr, m_rows, a.status, stream)) return 0;
+  }
   if (qtype == 12 && !per_row_x && !force_generic && aligned && a.status && batch && !no_mma) {
     if (enqueue_q4k_mma(blocks, x, out, offsets, n, bpr, a.experts, m_rows, a.status, stream)) return 0;
   }

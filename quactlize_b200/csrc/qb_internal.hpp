@@ -15,6 +15,8 @@ bool enqueue_q4k_gemv1(uint8_t const* blocks, __half const* x, float* out, int c
                        int experts, int rows, int max_rows, unsigned int* status, cudaStream_t stream);
 bool enqueue_q4k_mma(uint8_t const* blocks, __half const* x, float* out, int const* offsets, int n, int bpr, int experts,
                      int rows, unsigned int* status, cudaStream_t stream);   // tensor-core small-batch form
+bool enqueue_q4k_rows(uint8_t const* blocks, __half const* x, float* out, int n, int bpr, int rows, unsigned int* status,
+                      cudaStream_t stream);                 // dense, 1..8 rows, tensor cores on the single-row kernel's copy structure
 bool enqueue_dequantize(uint8_t const* blocks, __half* out, int count, int qtype, cudaStream_t s);
 bool enqueue_unpack(uint8_t const* blocks, int8_t* codes, __half* scale, __half* zero, int count, int qtype, cudaStream_t s);
 // planes (Native order) + fp16 scale/zero planes -> fp16 [E][n][k]; `shift` is added to the unsigned code

@@ -99,7 +99,7 @@ Q4_SHAPES = [(512, 4096), (96, 14336), (37, 256), (200, 768), (64, 11008 // 256 
 
 
 @pytest.mark.parametrize("n,k", Q4_SHAPES)
-@pytest.mark.parametrize("m", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 7, 8])
 def test_q4k_fast_kernel_vs_oracle(n, k, m):
     blocks = synth.kquant_blocks(12, n * k // 256, seed=n + k + m)
     x = synth.activations(m, k, seed=m + 1)
