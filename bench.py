@@ -326,7 +326,7 @@ def run_b200(args):
     d2h = sum(n * 4 for n, _, _, _ in seq)
     del pin_w
 
-    ep = None
+    ep = ep5 = None
     if world > 1 and args.configs != "none":
         from quactlize_b200 import bench_ep
         try:
@@ -334,6 +334,10 @@ def run_b200(args):
                               sampler=ClockSampler(local) if rank == 0 else None)
         except Exception as e:
             ep = {"error": f"{type(e).__name__}: {e}"[:300]}
+        try:                                                 # the decode-MoE configuration, 1024 tokens in total
+            ep5 = bench_ep.run(dev, rank, world, steps=max(5, min(args.steps, 20)), peaks=peaks, tokens=1024, **bench_ep.CFG5)
+        except Exception as e:
+            ep5 = {"error": f"{type(e).__name__}: {e}"[:300]}
 
     if rank != 0:
         if world > 1:
@@ -373,6 +377,7 @@ def run_b200(args):
     }
     if ep is not None:
         line["ep_moe"] = ep
+        line["ep_moe_cfg5"] = ep5
     if world == 1 and args.configs != "none":
         from quactlize_b200 import workloads
         names = sorted(workloads.registry()) if args.configs == "all" else args.configs.split(",")

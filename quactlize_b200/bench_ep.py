@@ -24,17 +24,20 @@ from quactlize_b200 import ep, sharding
 
 GS, BITS, TOP_K = 128, 4, 2
 
+# the decode-MoE configuration (128 experts, top-8, hidden 2048, intermediate 768, W2A16 gs=64) as keyword arguments of run()
+CFG5 = {"experts": 128, "hidden": 2048, "ffn": 768, "top_k": 8, "bits": 2, "gs": 64, "alpha": 0.0}
 
-def expert_weights(e: int, n: int, k: int, dev, tag: int):
-    """One expert's int4 plane artifact, seeded by its GLOBAL id so any rank can rebuild any expert."""
+
+def expert_weights(e: int, n: int, k: int, dev, tag: int, bits: int = BITS, gs: int = GS):
+    """One expert's plane artifact, seeded by its GLOBAL id so any rank can rebuild any expert."""
     g = torch.Generator(device=dev).manual_seed(100003 * tag + e)
-    low = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=dev, generator=g)
-    scale = (torch.randn((k // GS, n), device=dev, generator=g).abs() * (0.02 / 7)).to(torch.float16)
-    return low, scale, (-8.0 * scale.float()).to(torch.float16)
+    low = torch.randint(0, 256, (n, k * bits // 8), dtype=torch.uint8, device=dev, generator=g)
+    scale = (torch.randn((k // gs, n), device=dev, generator=g).abs() * (0.02 / 7)).to(torch.float16)
+    return low, scale, (-float(2 ** (bits - 1)) * scale.float()).to(torch.float16)
 
 
-def stack_experts(ids, n, k, dev, tag):
-    parts = [expert_weights(e, n, k, dev, tag) for e in ids]
+def stack_experts(ids, n, k, dev, tag, bits: int = BITS, gs: int = GS):
+    parts = [expert_weights(e, n, k, dev, tag, bits, gs) for e in ids]
     return tuple(torch.stack([p[i] for p in parts]).contiguous() for i in range(3))
 
 
@@ -48,14 +51,16 @@ def zipf_routes(tokens: int, experts: int, top_k: int, seed: int, alpha: float =
 
 
 def run(dev, rank: int, world: int, steps: int = 10, peaks=None, sampler=None, tokens: int = 4096, experts: int = 8,
-        hidden: int = 4096, ffn: int = 14336, transport: str = "peer", check_tokens: int = 48) -> dict:
+        hidden: int = 4096, ffn: int = 14336, transport: str = "peer", check_tokens: int = 48, top_k: int = TOP_K,
+        bits: int = BITS, gs: int = GS, alpha: float = 1.1) -> dict:
     if experts % world or tokens % world:
         return {"skipped": f"{experts} experts / {tokens} tokens do not divide over {world} ranks"}
+    TOP_K, BITS, GS = top_k, bits, gs                        # noqa: N806 (shadow the module defaults below)
     lo, hi = sharding.expert_range(experts, rank, world)
-    gate_up = stack_experts(range(lo, hi), 2 * ffn, hidden, dev, 1)
-    down = stack_experts(range(lo, hi), hidden, ffn, dev, 2)
+    gate_up = stack_experts(range(lo, hi), 2 * ffn, hidden, dev, 1, bits, gs)
+    down = stack_experts(range(lo, hi), hidden, ffn, dev, 2, bits, gs)
     t_r = tokens // world
-    routes = torch.from_numpy(zipf_routes(t_r, experts, TOP_K, seed=1000 + rank)).to(dev)
+    routes = torch.from_numpy(zipf_routes(t_r, experts, TOP_K, seed=1000 + rank, alpha=alpha)).to(dev)
     gen = torch.Generator(device=dev).manual_seed(77 + rank)
     x = torch.randn((t_r, hidden), device=dev, generator=gen).to(torch.bfloat16)
     wts = torch.softmax(torch.randn((t_r, TOP_K), device=dev, generator=gen), dim=1)
@@ -79,8 +84,8 @@ def run(dev, rank: int, world: int, steps: int = 10, peaks=None, sampler=None, t
     torch.cuda.synchronize(dev)
     # ---- bit-equality with the single-GPU grouped GEMMs on a sample of this rank's tokens, all experts held locally
     nchk = min(check_tokens, t_r)
-    full_gu = stack_experts(range(experts), 2 * ffn, hidden, dev, 1)
-    full_dn = stack_experts(range(experts), hidden, ffn, dev, 2)
+    full_gu = stack_experts(range(experts), 2 * ffn, hidden, dev, 1, bits, gs)
+    full_dn = stack_experts(range(experts), hidden, ffn, dev, 2, bits, gs)
     flat = routes[:nchk].reshape(-1)
     order = torch.argsort(flat, stable=True)
     offs = torch.zeros(experts + 1, dtype=torch.int32, device=dev)
@@ -127,8 +132,8 @@ def run(dev, rank: int, world: int, steps: int = 10, peaks=None, sampler=None, t
     layer.close()
     total_rows = float(sm.item())
     flops = 2.0 * total_rows * hidden * ffn * 3                           # gate, up and down over the real rows
-    rec = {"workload": f"MoE FFN, {experts} experts top-{TOP_K}, hidden {hidden}, ffn {ffn}, int4 gs{GS} scale+zero, bf16, "
-                       f"{tokens} tokens in total (strong scaling), Zipf(1.1) router",
+    rec = {"workload": f"MoE FFN, {experts} experts top-{TOP_K}, hidden {hidden}, ffn {ffn}, int{BITS} gs{GS} scale+zero, bf16, "
+                       f"{tokens} tokens in total (strong scaling), " + (f"Zipf({alpha}) router" if alpha else "uniform router"),
            "n_gpus": world, "transport": used, "collectives": "all_gather(route counts) + 2 x all_reduce(1 element) as stream-ordered barriers"
            if layer.transport == "peer" else "all_gather(route counts) + 2 x all_to_all(rows)",
            "ms_per_step": round(step_ms, 4), "gemm_ms_max_rank": round(gemm_ms, 4), "plan_ms": round(plan_ms, 4),
@@ -147,12 +152,13 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--transport", default="peer", choices=["peer", "nccl"])
     ap.add_argument("--small", action="store_true", help="a small layer (hidden 512, ffn 768) for tests")
+    ap.add_argument("--cfg5", action="store_true", help="the decode-MoE configuration: 128 experts top-8, 2048/768, W2A16 gs=64")
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
-    kw = {"hidden": 512, "ffn": 768} if args.small else {}
+    kw = {"hidden": 512, "ffn": 768} if args.small else dict(CFG5) if args.cfg5 else {}
     rec = run(dev, rank, world, steps=args.steps, tokens=args.tokens, transport=args.transport, **kw)
     if rank == 0:
         print(json.dumps(rec), flush=True)

@@ -422,6 +422,10 @@ int enqueue_native_gemv(uint8_t const* blocks, __half const* x, float* out, int 
     // pass pulls them into L2 for the others) rather than fall back to plain loads
     if (rows_hint <= 16 && enqueue_q4k_gemv1(blocks, x, out, offsets, n, bpr, a.experts, m_rows, max_rows, a.status, stream)) return 0;
   }
+  if (qtype != 12 && !per_row_x && !force_generic && aligned && a.status && rows_hint <= 64) {
+    // the other four formats: the single-row kernel once per activation row (rows after the first hit L2)
+    if (enqueue_kquant_gemv1(blocks, x, out, offsets, n, bpr, a.experts, m_rows, max_rows, qtype, a.status, stream)) return 0;
+  }
   if (per_row_x) {
     a.mtiles = 1;
     launch_generic_qt<1>(qtype, a, 1, stream);

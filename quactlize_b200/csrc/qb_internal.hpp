@@ -17,6 +17,8 @@ bool enqueue_q4k_mma(uint8_t const* blocks, __half const* x, float* out, int con
                      int rows, unsigned int* status, cudaStream_t stream);   // tensor-core small-batch form
 bool enqueue_q4k_rows(uint8_t const* blocks, __half const* x, float* out, int n, int bpr, int rows, unsigned int* status,
                       cudaStream_t stream);                 // dense, 1..8 rows, tensor cores on the single-row kernel's copy structure
+bool enqueue_kquant_gemv1(uint8_t const* blocks, __half const* x, float* out, int const* offsets, int n, int bpr, int experts,
+                          int rows, int max_rows, int qtype, unsigned int* status, cudaStream_t stream);   // Q2_K/Q3_K/Q5_K/Q6_K, one row per pass
 bool enqueue_dequantize(uint8_t const* blocks, __half* out, int count, int qtype, cudaStream_t s);
 bool enqueue_unpack(uint8_t const* blocks, int8_t* codes, __half* scale, __half* zero, int count, int qtype, cudaStream_t s);
 // planes (Native order) + fp16 scale/zero planes -> fp16 [E][n][k]; `shift` is added to the unsigned code

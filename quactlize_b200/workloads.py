@@ -107,9 +107,9 @@ def cfg2(m: int, n: int, k: int, dev="cuda:0", qtype: int = 12) -> Case:
         sub = blocks.reshape(n, bpr, bb)[cols].reshape(-1, bb)
         return {"kind": "raw", "got": got, "blocks": sub, "x": x, "n": len(cols), "k": k, "qtype": qtype, "out": "fp32"}
     wb = blocks.size
-    name = {12: "q4k"}.get(qtype, f"qt{qtype}")
-    return Case(f"cfg2_{name}_m{m}_{k}to{n}", "hbm", wb, wb + m * k * 2 + m * n * 4, 2.0 * m * n * k, nc, launch, sample,
-                "q4k_gemv1_kernel" if m == 1 else "q4k_mma_kernel")
+    name = {10: "q2k", 11: "q3k", 12: "q4k", 13: "q5k", 14: "q6k"}.get(qtype, f"qt{qtype}")
+    kernel = "kquant_gemv_generic_kernel" if qtype != 12 else "q4k_gemv1_kernel" if m == 1 else "q4k_rows_kernel"
+    return Case(f"cfg2_{name}_m{m}_{k}to{n}", "hbm", wb, wb + m * k * 2 + m * n * 4, 2.0 * m * n * k, nc, launch, sample, kernel)
 
 
 def cfg3(qtype: int, n: int, dev="cuda:0") -> Case:
@@ -335,6 +335,13 @@ def registry() -> Dict[str, Callable[[], Case]]:
     for w in ("gate_up", "down"):                 # the same decode MoE through the split-K tensor-core grouped GEMM
         for t in (1, 8, 64):
             r[f"cfg5_w2_{w}_t{t}_splitk"] = (lambda w=w, t=t: cfg5_splitk(2, w, t))
+    # beside the named configurations: gate and up of one layer as ONE launch (they share the activation: N = 28672),
+    # a 264 MB Q4_K matrix (what the single-row kernel streams once the fixed cost of a launch is amortised), and the raw
+    # blocks of the other four formats through the raw-block entry
+    r["aux_q4k_m1_gate_up_fused"] = (lambda: cfg2(1, 2 * 14336, 4096))
+    r["aux_q4k_m1_stream_264mb"] = (lambda: cfg2(1, 8 * 14336, 4096))
+    for qt, nm in ((10, "q2k"), (11, "q3k"), (13, "q5k"), (14, "q6k")):
+        r[f"aux_raw_{nm}_m1_4096to14336"] = (lambda qt=qt: cfg2(1, 14336, 4096, qtype=qt))
     r["fpa"] = fpa
     r["aux_dequant_q4k"] = aux_dequant
     r["aux_dequant_q6k"] = (lambda: aux_dequant(14))

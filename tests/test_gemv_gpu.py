@@ -113,6 +113,38 @@ def test_q4k_fast_kernel_vs_oracle(n, k, m):
     _wait_ok()
 
 
+KQ_SHAPES = [(256, 4096), (96, 14336), (37, 2048), (1, 4096), (130, 8192), (300, 6144)]
+
+
+@pytest.mark.parametrize("n,k", KQ_SHAPES)
+@pytest.mark.parametrize("m", [1, 3])
+@pytest.mark.parametrize("qt", [10, 11, 13, 14])
+def test_kquant_fast_kernel_vs_oracle(qt, n, k, m):
+    """Q2_K / Q3_K / Q5_K / Q6_K raw blocks through the bulk-copy single-row kernel (rows that are a multiple of 16 bytes)."""
+    blocks = synth.kquant_blocks(qt, n * k // 256, seed=n + k + m + qt)
+    x = synth.activations(m, k, seed=m + 1)
+    x[0, :7] *= 30.0
+    ref = kq.vecdot_dense(blocks, x, n, k, qt)
+    out = qb.gguf_vecdot_rows(_cuda(blocks), _cuda(x), n, k, qt)
+    assert kq.max_rel(out.cpu().numpy(), ref) < 4e-3
+    gen = qb.gguf_vecdot_rows(_cuda(blocks), _cuda(x), n, k, qt, force_generic=True)
+    assert kq.max_rel(gen.cpu().numpy(), ref) < TOL
+    _wait_ok()
+
+
+@pytest.mark.parametrize("qt", [10, 11, 13, 14])
+def test_kquant_fast_kernel_moe(qt):
+    n, k, rows_per_expert = 64, 2048, [3, 0, 1, 5]
+    e = len(rows_per_expert)
+    blocks = synth.kquant_blocks(qt, e * n * k // 256, seed=23 + qt).reshape(e, n * k // 256, -1)
+    x = synth.activations(sum(rows_per_expert), k, seed=8)
+    off = np.concatenate([[0], np.cumsum(rows_per_expert)]).astype(np.int32)
+    ref = kq.vecdot_moe(blocks, x, off, n, k, qt)
+    out = qb.gguf_vecdot_moe(_cuda(blocks), _cuda(x), torch.from_numpy(off).to(DEV), qt)
+    assert kq.max_rel(out.cpu().numpy(), ref) < 4e-3
+    _wait_ok()
+
+
 def test_q4k_activation_extremes():
     n, k = 64, 1024
     blocks = synth.kquant_blocks(12, n * k // 256, seed=9)
