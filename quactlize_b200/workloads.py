@@ -62,8 +62,8 @@ def _cols(n: int, seed: int, count: int = SAMPLE_COLS) -> np.ndarray:
 
 # ---------------------------------------------------------------------------------------------------------------------
 
-def cfg1(dev="cuda:0") -> Case:
-    n = k = 4096
+def cfg1(dev="cuda:0", n: int = 4096) -> Case:
+    k = 4096
     gs, bits = 128, 4
     low, scale, zero = synth.group_planes(1, n, k, bits, gs, seed=101)
     x = synth.activations(1, k, seed=102)
@@ -84,7 +84,7 @@ def cfg1(dev="cuda:0") -> Case:
                 "out": "fp16"}
     wb = n * k * bits // 8
     sz = 2 * (k // gs) * n * 2
-    return Case("cfg1_w4a16_m1_4096x4096", "hbm", wb, wb + sz + k * 2 + n * 2, 2.0 * n * k, nc, launch, sample,
+    return Case(f"cfg1_w4a16_m1_{n}x4096", "hbm", wb, wb + sz + k * 2 + n * 2, 2.0 * n * k, nc, launch, sample,
                 "rowthread_gemv_kernel", {"scale_zero_bytes": sz})
 
 
@@ -338,6 +338,7 @@ def registry() -> Dict[str, Callable[[], Case]]:
     # beside the named configurations: gate and up of one layer as ONE launch (they share the activation: N = 28672),
     # a 264 MB Q4_K matrix (what the single-row kernel streams once the fixed cost of a launch is amortised), and the raw
     # blocks of the other four formats through the raw-block entry
+    r["aux_w4a16_m1_32768x4096"] = (lambda: cfg1(n=32768))      # the plane GEMV on a 67 MB matrix
     r["aux_q4k_m1_gate_up_fused"] = (lambda: cfg2(1, 2 * 14336, 4096))
     r["aux_q4k_m1_stream_264mb"] = (lambda: cfg2(1, 8 * 14336, 4096))
     for qt, nm in ((10, "q2k"), (11, "q3k"), (13, "q5k"), (14, "q6k")):
