@@ -14,13 +14,54 @@
 
 namespace qb {
 
+// Eight consecutive codes (elements j0 .. j0+7 of group g, j0 a multiple of 8) of a block as the bytes of two words,
+// unsigned and before the format's bias: the same bits kq::code<QT> reads one element at a time, taken a word at a time.
+// The block may be only 2-byte aligned (84-, 110-, 210-byte blocks), so bytes are fetched in pairs.
+__device__ __forceinline__ void load8(uint8_t const* p, uint32_t& w0, uint32_t& w1) {
+  unsigned short const* h = reinterpret_cast<unsigned short const*>(p);
+  w0 = uint32_t(h[0]) | (uint32_t(h[1]) << 16);
+  w1 = uint32_t(h[2]) | (uint32_t(h[3]) << 16);
+}
+template <int QT>
+__device__ __forceinline__ void codes8(uint8_t const* b, int g, int j0, uint32_t& c0, uint32_t& c1) {
+  uint32_t l0, l1, h0, h1;
+  if constexpr (QT == 12) {
+    load8(b + 16 + j0 + 32 * (g >> 1), l0, l1);
+    int const s = 4 * (g & 1);
+    c0 = (l0 >> s) & 0x0F0F0F0Fu; c1 = (l1 >> s) & 0x0F0F0F0Fu;
+  } else if constexpr (QT == 13) {
+    load8(b + 48 + j0 + 32 * (g >> 1), l0, l1);
+    load8(b + 16 + j0, h0, h1);
+    int const s = 4 * (g & 1);
+    c0 = ((l0 >> s) & 0x0F0F0F0Fu) | (((h0 >> g) & 0x01010101u) << 4);
+    c1 = ((l1 >> s) & 0x0F0F0F0Fu) | (((h1 >> g) & 0x01010101u) << 4);
+  } else if constexpr (QT == 14) {
+    int const p = g & 1, q1 = (g >> 1) & 1, n = (g >> 2) & 1, h = g >> 3;
+    load8(b + j0 + 16 * p + 32 * q1 + 64 * h, l0, l1);
+    load8(b + 128 + j0 + 16 * p + 32 * h, h0, h1);
+    int const s = 4 * n, sh = 2 * q1 + 4 * n;
+    c0 = ((l0 >> s) & 0x0F0F0F0Fu) | (((h0 >> sh) & 0x03030303u) << 4);
+    c1 = ((l1 >> s) & 0x0F0F0F0Fu) | (((h1 >> sh) & 0x03030303u) << 4);
+  } else if constexpr (QT == 11) {
+    load8(b + 32 + j0 + 16 * (g & 1) + 32 * (g >> 3), l0, l1);
+    load8(b + j0 + 16 * (g & 1), h0, h1);
+    int const s = 2 * ((g >> 1) & 3), sh = ((g >> 1) & 3) + 4 * (g >> 3);
+    c0 = ((l0 >> s) & 0x03030303u) | (((h0 >> sh) & 0x01010101u) << 2);     // lo + 4*hb; the bias of 4 is the format's
+    c1 = ((l1 >> s) & 0x03030303u) | (((h1 >> sh) & 0x01010101u) << 2);
+  } else {
+    load8(b + 16 + j0 + 16 * (g & 1) + 32 * (g >> 3), l0, l1);
+    int const s = 2 * ((g >> 1) & 3);
+    c0 = (l0 >> s) & 0x03030303u; c1 = (l1 >> s) & 0x03030303u;
+  }
+}
+
 // Raw blocks -> fp16 weights.  A CTA takes kDqBlocks consecutive blocks: their bytes are one contiguous run, staged in
 // shared memory by 16-byte loads (coalesced whatever the block size; the ragged ends by byte loads), then a warp owns a
 // block, lane -> 8 consecutive elements, one 16-byte store per lane (a warp writes 512 contiguous bytes).  DRAM traffic
 // is the algorithmic 144..210 B in + 512 B out per block; the reference's warp-per-256 kernel has the same shape
 // (quactlize/include/gguf_vecdot.hpp:782-854, 78 % of peak published at :762-770).
 constexpr int kDqBlocks = 32;
-template <int QT>
+template <int QT, bool WORDS>          // WORDS: the blocks start on an even address, codes are taken a word at a time
 __global__ void __launch_bounds__(256) dequant_kernel(uint8_t const* __restrict__ blocks, __half* __restrict__ out, int count) {
   using F = kq::Fmt<QT>;
   constexpr int GS = 256 / F::kGroups;
@@ -49,10 +90,26 @@ __global__ void __launch_bounds__(256) dequant_kernel(uint8_t const* __restrict_
     int sc, mn;
     kq::scale_min<QT>(blk + F::kScaleOff, g, sc, mn);
     float const dl = __fmul_rn(d, float(sc)), ml = __fmul_rn(dmin, float(mn));
-    __align__(16) __half w[8];
+    // the lane's eight codes as bytes of two words (unsigned, before the format's bias), then byte -> float through the
+    // 2^23 magic (exact) and the reference's three roundings
+    __align__(16) __half2 w[4];
+    if constexpr (!WORDS) {
 #pragma unroll
-    for (int t = 0; t < 8; ++t)
-      w[t] = __float2half_rn(__fsub_rn(__fmul_rn(dl, float(kq::code<QT>(blk, g, j0 + t))), ml));
+      for (int t = 0; t < 4; ++t)
+        w[t] = __halves2half2(__float2half_rn(__fsub_rn(__fmul_rn(dl, float(kq::code<QT>(blk, g, j0 + 2 * t))), ml)),
+                              __float2half_rn(__fsub_rn(__fmul_rn(dl, float(kq::code<QT>(blk, g, j0 + 2 * t + 1))), ml)));
+    } else {
+    uint32_t c0, c1;
+    codes8<QT>(blk, g, j0, c0, c1);
+    float const bias = 8388608.f + float(F::kCodeBias);
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      uint32_t const cw = t < 2 ? c0 : c1;
+      float const qa = __uint_as_float(__byte_perm(cw, 0x4B000000u, (t & 1) ? 0x7442u : 0x7440u)) - bias;
+      float const qb2 = __uint_as_float(__byte_perm(cw, 0x4B000000u, (t & 1) ? 0x7443u : 0x7441u)) - bias;
+      w[t] = __floats2half2_rn(__fsub_rn(__fmul_rn(dl, qa), ml), __fsub_rn(__fmul_rn(dl, qb2), ml));
+    }
+    }
     *reinterpret_cast<uint4*>(out + size_t(b0 + lb) * 256 + i0) = *reinterpret_cast<uint4 const*>(w);
   }
 }
@@ -145,29 +202,41 @@ __global__ void __launch_bounds__(256) prepass_kernel(uint8_t const* __restrict_
   scale[idx] = s; zero[idx] = z;
 }
 
-// units [E][K/256/P][N][unit_total] -> planes [E][K/gs][N]; one thread per (expert, plane row, column), column fastest
+// units [E][K/256/P][N][unit_total] -> planes [E][K/gs][N]; one thread per (expert, superblock, column), column fastest:
+// it reads its superblock's share of the unit once (2-byte loads: shares are 14-20 bytes and 2-byte aligned), decodes all
+// the groups from registers and writes one element of G consecutive plane rows; a warp's stores are 64 contiguous bytes.
 template <int QT>
 __global__ void __launch_bounds__(256) prepass_unit_kernel(uint8_t const* __restrict__ units, __half* __restrict__ scale,
                                                            __half* __restrict__ zero, int experts, int n, int nsb, int zmul) {
   using F = kq::Fmt<QT>;
   using U = kq::Unit<QT>;
-  int64_t const total = int64_t(experts) * nsb * F::kGroups * n;
+  int64_t const total = int64_t(experts) * nsb * n;
   int64_t const idx = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   int const col = int(idx % n);
   int64_t const r = idx / n;
-  int const g = int(r % F::kGroups);
-  int const sb = int((r / F::kGroups) % nsb);
-  int const e = int(r / (int64_t(F::kGroups) * nsb));
+  int const sb = int(r % nsb);
+  int const e = int(r / nsb);
   int const nu = nsb / U::kSbPerUnit;
   uint8_t const* u = units + ((int64_t(e) * nu + sb / U::kSbPerUnit) * n + col) * U::kUnitTotal + (sb % U::kSbPerUnit) * U::kSbBytes;
-  int sc, mn;
-  kq::unit_scale_min<QT>(u, g, sc, mn);
-  float const df = __half2float(__ushort_as_half(kq::load_u16(u)));
-  float const mf = F::kHasMin ? __half2float(__ushort_as_half(kq::load_u16(u + 2))) : 0.f;
-  __half s, z;
-  scale_zero_from_codes(df, mf, sc, mn, F::kHasMin, zmul, s, z);
-  scale[idx] = s; zero[idx] = z;
+  static_assert(U::kSbBytes % 2 == 0 && U::kUnitTotal % 2 == 0, "shares are read two bytes at a time");
+  uint8_t loc[U::kSbBytes];
+#pragma unroll
+  for (int i = 0; i < U::kSbBytes / 2; ++i) {
+    unsigned short const v = __ldg(reinterpret_cast<unsigned short const*>(u) + i);
+    loc[2 * i] = uint8_t(v & 0xFF); loc[2 * i + 1] = uint8_t(v >> 8);
+  }
+  float const df = __half2float(__ushort_as_half(kq::load_u16(loc)));
+  float const mf = F::kHasMin ? __half2float(__ushort_as_half(kq::load_u16(loc + 2))) : 0.f;
+  int64_t const o0 = ((int64_t(e) * nsb + sb) * F::kGroups) * n + col;
+#pragma unroll
+  for (int g = 0; g < F::kGroups; ++g) {
+    int sc, mn;
+    kq::unit_scale_min<QT>(loc, g, sc, mn);
+    __half s, z;
+    scale_zero_from_codes(df, mf, sc, mn, F::kHasMin, zmul, s, z);
+    scale[o0 + int64_t(g) * n] = s; zero[o0 + int64_t(g) * n] = z;
+  }
 }
 
 #define QB_QT_SWITCH(qtype, CALL)                                                        \
@@ -175,7 +244,8 @@ __global__ void __launch_bounds__(256) prepass_unit_kernel(uint8_t const* __rest
                    case 13: CALL(13); break; case 14: CALL(14); break; default: return false; }
 
 bool enqueue_dequantize(uint8_t const* blocks, __half* out, int count, int qtype, cudaStream_t s) {
-#define CALL(Q) dequant_kernel<Q><<<(count + kDqBlocks - 1) / kDqBlocks, 256, 0, s>>>(blocks, out, count)
+#define CALL(Q) { if (reinterpret_cast<uintptr_t>(blocks) & 1) dequant_kernel<Q, false><<<(count + kDqBlocks - 1) / kDqBlocks, 256, 0, s>>>(blocks, out, count); \
+                  else dequant_kernel<Q, true><<<(count + kDqBlocks - 1) / kDqBlocks, 256, 0, s>>>(blocks, out, count); }
   QB_QT_SWITCH(qtype, CALL)
 #undef CALL
   return true;
@@ -206,7 +276,7 @@ bool enqueue_prepass(uint8_t const* sblocks, uint16_t const* d, uint16_t const* 
 
 bool enqueue_prepass_unit(uint8_t const* units, __half* scale, __half* zero, int experts, int n, int nsb, int qtype,
                           int zmul, cudaStream_t s) {
-#define CALL(Q) { int64_t const total = int64_t(experts) * nsb * kq::Fmt<Q>::kGroups * n; \
+#define CALL(Q) { int64_t const total = int64_t(experts) * nsb * n; \
                   prepass_unit_kernel<Q><<<unsigned((total + 255) / 256), 256, 0, s>>>(units, scale, zero, experts, n, nsb, zmul); }
   QB_QT_SWITCH(qtype, CALL)
 #undef CALL

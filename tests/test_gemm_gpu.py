@@ -184,3 +184,28 @@ def test_split_k_tactic_through_the_reference_shaped_entry():
     ref = kq.vecdot_moe(blocks.reshape(e, n * k // 256, -1), a, off, n, k, qt)
     _check(outs[0], ref)
     _check(outs[1], ref)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs in one process")
+def test_one_process_drives_two_devices():
+    """Per-device state (shared-memory opt-ins, plans, status words, static scratch) is keyed by device: the same process
+    runs the tensor-core GEMM and the bulk-copy GEMVs on cuda:0 and then on cuda:1, and again on cuda:0."""
+    m, n, k, bits, gs = 300, 512, 1024, 4, 128
+    low, scale, zero = synth.group_planes(1, n, k, bits, gs, seed=71)
+    a = synth.activations(m, k, seed=72)
+    ref = kq.planes_matmul(a, low, None, scale, zero, bits, 0, gs)
+    blocks = synth.kquant_blocks(12, 256 * 4096 // 256, seed=73)
+    b6 = synth.kquant_blocks(14, 256 * 4096 // 256, seed=74)
+    x = synth.activations(4, 4096, seed=75)
+    ref4, ref6 = kq.vecdot_dense(blocks, x, 256, 4096, 12), kq.vecdot_dense(b6, x[:1], 256, 4096, 14)
+    for dev in ("cuda:0", "cuda:1", "cuda:0"):
+        t = lambda v: torch.from_numpy(v).to(dev)
+        out = qb.gemm_plane(t(a), t(low), None, t(scale), t(zero), bits, 0, gs)
+        assert out.device == torch.device(dev)
+        _check(out, ref)
+        assert kq.max_rel(qb.gguf_vecdot_rows(t(blocks), t(x), 256, 4096, 12).cpu().numpy(), ref4) < 4e-3      # row-range MMA kernel
+        assert kq.max_rel(qb.gguf_vecdot_rows(t(blocks), t(x[:1]), 256, 4096, 12).cpu().numpy(), ref4[:1]) < 2e-3   # single-row kernel
+        assert kq.max_rel(qb.gguf_vecdot_rows(t(b6), t(x[:1]), 256, 4096, 14).cpu().numpy(), ref6) < 4e-3
+        with torch.cuda.device(dev):
+            torch.cuda.synchronize()
+            assert _lib.lib().quactlize_b200_device_wait_status() == 0
