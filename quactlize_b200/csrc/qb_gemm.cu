@@ -33,7 +33,9 @@
 #include <algorithm>
 #include <cstdint>
 #include <cstdio>
+#include <map>
 #include <mutex>
+#include <tuple>
 
 #include "qb_device.cuh"
 #include "qb_internal.hpp"
@@ -538,33 +540,55 @@ int launch_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
     if (!make_map(&ma, BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, d.act, dims, str, box,
                   CU_TENSOR_MAP_SWIZZLE_128B)) return kRuntimeError;
   }
+  // The four maps over the weight artifact depend only on its pointers and shape: a model's weights are launched again and
+  // again, so they are encoded once and kept (per instantiation; the map of the activations is encoded per launch).
   {
-    cuuint64_t const rb = cuuint64_t(d.k) * LO / 8;
-    cuuint64_t dims[3] = {rb, cuuint64_t(d.n), cuuint64_t(E)};
-    cuuint64_t str[2] = {rb, rb * d.n};
-    cuuint32_t box[3] = {cuuint32_t(kRawK * LO / 8), cuuint32_t(kTN), 1};
-    if (!make_map(&ml, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.low, dims, str, box, plane_swizzle(16 * LO))) return kRuntimeError;
-  }
-  if constexpr (HI != 0) {
-    cuuint64_t const rb = cuuint64_t(d.k) * HI / 8;
-    cuuint64_t dims[3] = {rb, cuuint64_t(d.n), cuuint64_t(E)};
-    cuuint64_t str[2] = {rb, rb * d.n};
-    cuuint32_t box[3] = {cuuint32_t(kRawK * HI / 8), cuuint32_t(kTN), 1};
-    if (!make_map(&mh, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.high, dims, str, box, plane_swizzle(16 * HI))) return kRuntimeError;
-  } else {
-    mh = ml;
-  }
-  {
-    cuuint64_t const kg = cuuint64_t(d.k / gs);
-    cuuint64_t dims[3] = {cuuint64_t(d.n), kg, cuuint64_t(E)};
-    cuuint64_t str[2] = {cuuint64_t(d.n) * 2, cuuint64_t(d.n) * 2 * kg};
-    cuuint32_t box[3] = {cuuint32_t(kTN), cuuint32_t(srows), 1};
-    if (!make_map(&ms, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, d.scale, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
-    if (d.zero) {
-      if (!make_map(&mz, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, d.zero, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
-    } else {
-      mz = ms;
+    struct WKey {
+      void const *lo, *hi, *sc, *ze; int n, k, e, gs;
+      bool operator<(WKey const& o) const {
+        return std::tie(lo, hi, sc, ze, n, k, e, gs) < std::tie(o.lo, o.hi, o.sc, o.ze, o.n, o.k, o.e, o.gs);
+      }
+    };
+    struct WMaps { CUtensorMap ml, mh, ms, mz; };
+    static std::map<WKey, WMaps> cache;
+    static std::mutex cmu;
+    WKey const key{d.low, HI ? d.high : nullptr, d.scale, d.zero, d.n, d.k, E, gs};
+    std::lock_guard<std::mutex> lock(cmu);
+    auto it = cache.find(key);
+    if (it == cache.end()) {
+      WMaps w{};
+      {
+        cuuint64_t const rb = cuuint64_t(d.k) * LO / 8;
+        cuuint64_t dims[3] = {rb, cuuint64_t(d.n), cuuint64_t(E)};
+        cuuint64_t str[2] = {rb, rb * d.n};
+        cuuint32_t box[3] = {cuuint32_t(kRawK * LO / 8), cuuint32_t(kTN), 1};
+        if (!make_map(&w.ml, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.low, dims, str, box, plane_swizzle(16 * LO))) return kRuntimeError;
+      }
+      if constexpr (HI != 0) {
+        cuuint64_t const rb = cuuint64_t(d.k) * HI / 8;
+        cuuint64_t dims[3] = {rb, cuuint64_t(d.n), cuuint64_t(E)};
+        cuuint64_t str[2] = {rb, rb * d.n};
+        cuuint32_t box[3] = {cuuint32_t(kRawK * HI / 8), cuuint32_t(kTN), 1};
+        if (!make_map(&w.mh, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.high, dims, str, box, plane_swizzle(16 * HI))) return kRuntimeError;
+      } else {
+        w.mh = w.ml;
+      }
+      {
+        cuuint64_t const kg = cuuint64_t(d.k / gs);
+        cuuint64_t dims[3] = {cuuint64_t(d.n), kg, cuuint64_t(E)};
+        cuuint64_t str[2] = {cuuint64_t(d.n) * 2, cuuint64_t(d.n) * 2 * kg};
+        cuuint32_t box[3] = {cuuint32_t(kTN), cuuint32_t(srows), 1};
+        if (!make_map(&w.ms, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, d.scale, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
+        if (d.zero) {
+          if (!make_map(&w.mz, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, d.zero, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
+        } else {
+          w.mz = w.ms;
+        }
+      }
+      if (cache.size() >= 8192) cache.clear();                  // bounded: far more artifacts than a model has
+      it = cache.emplace(key, w).first;
     }
+    ml = it->second.ml; mh = it->second.mh; ms = it->second.ms; mz = it->second.mz;
   }
   GemmArgs g{};
   g.offsets = d.experts > 0 ? d.offsets : nullptr;

@@ -171,7 +171,8 @@ def combine(comb: torch.Tensor, item_of_route: torch.Tensor, weights: torch.Tens
 class Plan:
     """Device-side plan of one step (see ep_plan in the C header): per item the token, owner rank and row in the owner's
     buffer; per route its item; the cumulative rows per local expert."""
-    __slots__ = ("item_token", "item_rank", "item_pos", "item_of_route", "local_off", "counts_all", "routes")
+    __slots__ = ("item_token", "item_rank", "item_pos", "item_of_route", "local_off", "local_total", "counts", "counts_flat",
+                 "counts_all", "routes")
 
 
 class ExpertParallelFFN:
@@ -191,6 +192,7 @@ class ExpertParallelFFN:
         self.buf = PeerBuffers(capacity, self.hidden, max_local_routes, self.hidden, group) if transport == "peer" else None
         dev = gate_up[0].device
         self._flag = torch.zeros(1, device=dev)
+        self._plans = {}
         self._addr = torch.zeros(capacity, dtype=torch.int64, device=dev) if transport == "peer" else None
 
     def close(self):
@@ -204,18 +206,24 @@ class ExpertParallelFFN:
     def plan(self, routes: torch.Tensor) -> Plan:
         """ep_count -> all_gather of the counts -> ep_plan: three launches, nothing copied to the host."""
         L = _lib.lib()
-        flat = routes.reshape(-1).to(torch.int64).contiguous()
+        flat = routes.reshape(-1)
+        if flat.dtype != torch.int64 or not flat.is_contiguous():
+            flat = flat.to(torch.int64).contiguous()
         r, dev = flat.numel(), flat.device
-        counts = torch.empty(self.experts, dtype=torch.int32, device=dev)
-        rc = L.quactlize_b200_ep_count_dev_v1(_p(flat), r, self.experts, _p(counts), _stream())
-        counts_all = torch.empty(self.world * self.experts, dtype=torch.int32, device=dev)
-        dist.all_gather_into_tensor(counts_all, counts, group=self.group)
-        p = Plan()
-        p.routes = r
-        p.item_token, p.item_rank, p.item_pos, p.item_of_route = (torch.empty(max(r, 1), dtype=torch.int32, device=dev) for _ in range(4))
-        p.local_off = torch.empty(self.experts // self.world + 1, dtype=torch.int32, device=dev)
-        p.counts_all = counts_all.view(self.world, self.experts)
-        rc = rc or L.quactlize_b200_ep_plan_dev_v1(_p(flat), _p(counts_all), self.rank, self.world, self.experts, r, self.top_k,
+        p = self._plans.get(r)
+        if p is None:                                        # the buffers of a plan are reused by every step of this size
+            p = Plan()
+            p.routes = r
+            p.item_token, p.item_rank, p.item_pos, p.item_of_route = (torch.empty(max(r, 1), dtype=torch.int32, device=dev) for _ in range(4))
+            p.local_off = torch.empty(self.experts // self.world + 1, dtype=torch.int32, device=dev)
+            p.local_total = p.local_off[-1:]
+            p.counts = torch.empty(self.experts, dtype=torch.int32, device=dev)
+            p.counts_flat = torch.empty(self.world * self.experts, dtype=torch.int32, device=dev)
+            p.counts_all = p.counts_flat.view(self.world, self.experts)
+            self._plans[r] = p
+        rc = L.quactlize_b200_ep_count_dev_v1(_p(flat), r, self.experts, _p(p.counts), _stream())
+        dist.all_gather_into_tensor(p.counts_flat, p.counts, group=self.group)
+        rc = rc or L.quactlize_b200_ep_plan_dev_v1(_p(flat), _p(p.counts_flat), self.rank, self.world, self.experts, r, self.top_k,
                                                    _p(p.item_token), _p(p.item_rank), _p(p.item_pos), _p(p.item_of_route),
                                                    _p(p.local_off), _stream())
         if rc:
@@ -234,7 +242,7 @@ class ExpertParallelFFN:
             if rc:
                 raise RuntimeError(f"dispatch failed (rc={rc})")
             self._barrier()
-            rc = L.quactlize_b200_ep_return_addr_dev_v1(_p(b.ret), _p(b.peer_comb), self.world, _p(p.local_off[-1:]), self.capacity,
+            rc = L.quactlize_b200_ep_return_addr_dev_v1(_p(b.ret), _p(b.peer_comb), self.world, _p(p.local_total), self.capacity,
                                                         self.hidden * 2, _p(self._addr), _stream())
             if rc:
                 raise RuntimeError(f"return addresses failed (rc={rc})")
