@@ -168,22 +168,46 @@ template <> struct Pack2<true> {
 // Raw plane rows of a 128-k piece are 16*BITS bytes; consecutive columns therefore sit 64 / 32 / 16 bytes apart, which
 // would put a warp's loads on a few banks.  The TMA writes 64- and 32-byte rows with the matching swizzle (16-byte chunk
 // index XOR row bits), and this reads through the same XOR with the widest load that covers the thread's bytes.
+__device__ __forceinline__ uint4 g_lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint2 g_lds64(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t g_lds32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ float g_ldsh(uint32_t a) {          // one fp16 -> float
+  unsigned short v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+  return __half2float(__ushort_as_half(v));
+}
+__device__ __forceinline__ void g_sts128(uint32_t a, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
 template <int NB, int RB>
-__device__ __forceinline__ void load_raw(uint8_t const* tile, uint32_t off, uint32_t* out) {
+__device__ __forceinline__ void load_raw(uint32_t tile, uint32_t off, uint32_t* out) {
   constexpr uint32_t mask = RB == 64 ? 3u : (RB == 32 ? 1u : 0u);
   if constexpr (NB >= 16) {
 #pragma unroll
     for (int i = 0; i < NB / 16; ++i) {
       uint32_t const o = off + 16 * i;
-      uint4 const v = *reinterpret_cast<uint4 const*>(tile + (o ^ (((o >> 7) & mask) << 4)));
+      uint4 const v = g_lds128(tile + (o ^ (((o >> 7) & mask) << 4)));
       out[4 * i] = v.x; out[4 * i + 1] = v.y; out[4 * i + 2] = v.z; out[4 * i + 3] = v.w;
     }
   } else if constexpr (NB == 8) {
-    uint2 const v = *reinterpret_cast<uint2 const*>(tile + (off ^ (((off >> 7) & mask) << 4)));
+    uint2 const v = g_lds64(tile + (off ^ (((off >> 7) & mask) << 4)));
     out[0] = v.x; out[1] = v.y;
   } else {
     static_assert(NB == 4, "a thread converts at least four 8-element chunks of a 1-bit plane");
-    out[0] = *reinterpret_cast<uint32_t const*>(tile + (off ^ (((off >> 7) & mask) << 4)));
+    out[0] = g_lds32(tile + (off ^ (((off >> 7) & mask) << 4)));
   }
 }
 
@@ -198,9 +222,11 @@ __device__ __forceinline__ uint32_t chunk_bits(uint32_t const* w, int i) {
 // One thread converts NC consecutive 8-element chunks (from chunk c0 of the 64-k half h) of weight column `col`.
 // lo_tile/hi_tile: the stage's raw 128-k pieces; sc/zr: [group 0][this column] of the scale rows for this half
 // (row stride kTN halves).  Output chunk c lands at 16-byte position c ^ (col & 7) of the operand row (SWIZZLE_128B).
-template <int LO, int HI, bool BF16, int NC>
-__device__ __forceinline__ void dequant_col(uint8_t const* lo_tile, uint8_t const* hi_tile, __half const* sc, __half const* zr,
-                                            int gs, float coff, uint8_t* brow, int col, int h, int c0) {
+// ONE: the whole 64-k stage lies in one scale group (gs >= 64): scale and zero are fetched once and the chunks form one
+// straight-line block, which lets the compiler overlap the byte permutes, the half2 arithmetic and the stores of all of them.
+template <int LO, int HI, bool BF16, int NC, bool ONE>
+__device__ __forceinline__ void dequant_col(uint32_t lo_tile, uint32_t hi_tile, uint32_t sc, uint32_t zr, bool has_zero,
+                                            int gs, float coff, uint32_t brow, int col, int h, int c0) {
   using P = Pack2<BF16>;
   uint32_t lw[(NC * LO + 3) / 4], hw[HI ? (NC * HI + 3) / 4 : 1];
   load_raw<NC * LO, 16 * LO>(lo_tile, uint32_t(col * (16 * LO) + h * (8 * LO) + c0 * LO), lw);
@@ -208,15 +234,22 @@ __device__ __forceinline__ void dequant_col(uint8_t const* lo_tile, uint8_t cons
   int const gshift = gs >= 64 ? 31 : (gs == 32 ? 2 : 1);          // chunks per group: >= 8 -> one group, 4, or 2
   int gprev = -1;
   typename P::T2 s2, z2;
+  if constexpr (ONE) {
+    float const s = g_ldsh(sc);
+    float const z = (has_zero ? g_ldsh(zr) : 0.f) + coff * s;
+    s2 = P::from_f(s, s); z2 = P::from_f(z, z);
+  }
 #pragma unroll
   for (int i = 0; i < NC; ++i) {
     int const c = c0 + i;
-    int const g = gs >= 64 ? 0 : (c >> gshift);
-    if (g != gprev) {
-      float const s = __half2float(sc[g * kTN]);
-      float const z = (zr ? __half2float(zr[g * kTN]) : 0.f) + coff * s;
-      s2 = P::from_f(s, s); z2 = P::from_f(z, z);
-      gprev = g;
+    if constexpr (!ONE) {
+      int const g = c >> gshift;
+      if (g != gprev) {
+        float const s = g_ldsh(sc + uint32_t(g * kTN * 2));
+        float const z = (has_zero ? g_ldsh(zr + uint32_t(g * kTN * 2)) : 0.f) + coff * s;
+        s2 = P::from_f(s, s); z2 = P::from_f(z, z);
+        gprev = g;
+      }
     }
     uint32_t v[4];
     if constexpr (LO == 4 && HI == 0) {
@@ -237,22 +270,34 @@ __device__ __forceinline__ void dequant_col(uint8_t const* lo_tile, uint8_t cons
     uint4 o;
     o.x = P::affine(v[0], s2, z2); o.y = P::affine(v[1], s2, z2);
     o.z = P::affine(v[2], s2, z2); o.w = P::affine(v[3], s2, z2);
-    *reinterpret_cast<uint4*>(brow + ((c ^ (col & 7)) << 4)) = o;
+    g_sts128(brow + uint32_t((c ^ (col & 7)) << 4), o);
   }
 }
 
 // ---- the kernel -----------------------------------------------------------------------------------------------------
 
+// Dequantising warps per epilogue warp.  The 256 x 256 tile converts 16 K codes per 64-k stage; with one warp per 32 rows
+// (eight warps, two per scheduler) that conversion, a dependent chain of loads, byte permutes and half2 arithmetic behind
+// two barrier waits, took longer than the stage's MMAs and set the pace of the whole kernel (timed with either side
+// removed: conversion alone 776 us, MMAs alone 633 us, together 977 us on the 4096 -> 14336 grouped problem).  Twice the
+// warps, each converting half of a column's 64 codes, put the tensor pipe back in charge.
+#ifndef QB_GEMM_DQ
+#define QB_GEMM_DQ 1
+#endif
+template <int MT, int NT, int DEPTH> constexpr int gemm_dq() { return (MT == 2 && NT == 2 && DEPTH == 0) ? QB_GEMM_DQ : 1; }
+
 template <int LO, int HI, bool BF16, int MT, int NT, int DEPTH>
-__global__ void __launch_bounds__(128 + 128 * MT, DEPTH ? 2 : 1)
+__global__ void __launch_bounds__(128 + 128 * MT * gemm_dq<MT, NT, DEPTH>(), DEPTH ? 2 : 1)
 mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_lo,
                   const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ CUtensorMap map_s,
                   const __grid_constant__ CUtensorMap map_z, GemmArgs g) {
   extern __shared__ uint8_t smem_raw[];
   using SM = GemmSmem<LO, HI, MT, NT, DEPTH>;
   constexpr int AST = SM::AST, BST = SM::BST, RST = SM::RST, kRows = kTM * MT, kCols = kTN * NT;
-  constexpr int kDqWarps = 4 * MT;                            // also the epilogue warps: one per 32 accumulator lanes
-  constexpr int NC = 8 * NT / MT;                             // 8-element chunks a dequant thread converts per stage
+  constexpr int DQ = gemm_dq<MT, NT, DEPTH>();
+  constexpr int kDqWarps = 4 * MT * DQ;                       // the first 4*MT of them also run the epilogue: one per 32 accumulator lanes
+  constexpr int NC = 8 * NT / MT / DQ;                        // 8-element chunks a dequant thread converts per stage
+  static_assert(NC >= 1 && NC * MT * DQ == 8 * NT, "the dequant threads tile a stage's chunks exactly");
   SM& sm = *reinterpret_cast<SM*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -394,11 +439,16 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       if (!ok) break;
       int const srow = gs >= kRawK ? 0 : h * (srows / 2);
 #ifndef QB_GABL_NODEQ
-      if (live)
-        dequant_col<LO, HI, BF16, NC>(sm.raw_lo[r][nt], sm.raw_hi[r][nt],
-                                      reinterpret_cast<__half const*>(sm.scale[r][nt]) + srow * kTN + cin,
-                                      g.has_zero ? reinterpret_cast<__half const*>(sm.zero[r][nt]) + srow * kTN + cin : nullptr,
-                                      gs, coff, sm.b[sb] + col * 128, cin, h, part * NC);
+      if (live) {
+        uint32_t const sc_a = smem_u32(sm.scale[r][nt]) + uint32_t((srow * kTN + cin) * 2);
+        uint32_t const zr_a = smem_u32(sm.zero[r][nt]) + uint32_t((srow * kTN + cin) * 2);
+        if (gs >= 64)
+          dequant_col<LO, HI, BF16, NC, true>(smem_u32(sm.raw_lo[r][nt]), smem_u32(sm.raw_hi[r][nt]), sc_a, zr_a, g.has_zero != 0,
+                                              gs, coff, smem_u32(sm.b[sb]) + uint32_t(col * 128), cin, h, part * NC);
+        else
+          dequant_col<LO, HI, BF16, NC, false>(smem_u32(sm.raw_lo[r][nt]), smem_u32(sm.raw_hi[r][nt]), sc_a, zr_a, g.has_zero != 0,
+                                               gs, coff, smem_u32(sm.b[sb]) + uint32_t(col * 128), cin, h, part * NC);
+      }
 #endif
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes -> visible to the MMA
       __syncwarp();
@@ -623,7 +673,7 @@ int launch_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
   int const mtiles = d.experts > 0 ? d.total_rows / (kTM * MT) + std::min(d.experts, d.total_rows)
                                    : (d.total_rows + kTM * MT - 1) / (kTM * MT);
   if (mtiles > 65535) return 30;
-  kern<<<dim3((d.n + kTN * NT - 1) / (kTN * NT), mtiles, splits), 128 + 128 * MT, smem, stream>>>(ma, ml, mh, ms, mz, g);
+  kern<<<dim3((d.n + kTN * NT - 1) / (kTN * NT), mtiles, splits), 128 + 128 * MT * gemm_dq<MT, NT, DEPTH>(), smem, stream>>>(ma, ml, mh, ms, mz, g);
   if (splits > 1) {
     int64_t const elems = int64_t(d.total_rows) * d.n;         // n % 128 == 0: whole float4 groups
     splitk_reduce_kernel<BF16><<<unsigned((elems / 4 + 255) / 256), 256, 0, stream>>>(d.partial, d.out, elems, splits);
