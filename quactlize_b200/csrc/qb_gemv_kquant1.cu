@@ -369,38 +369,42 @@ __global__ void __launch_bounds__(kKqWarps * 32, 1) kquant_gemv1_kernel(KqArgs a
   int const row0 = cx * a.rows_q + min(cx, a.rows_r);
   int const nrows = a.rows_q + (cx < a.rows_r ? 1 : 0);
   int const npairs = (nrows + 1) >> 1;
-  int n_my = 0;
-  if (rslot < npairs) n_my = (npairs - 1 - rslot) / a.RS + 1;
   size_t const row_stride = size_t(bpr) * KB;
   unsigned const seg_off = unsigned(seg) * unsigned(a.nbs) * KB, lead = seg_off & 15u;
   unsigned const copy_bytes = (lead + unsigned(nb_seg) * KB + 15u) & ~15u;
   bool const contiguous = a.S == 1;                               // a whole row per segment: the two rows are adjacent
-  uint8_t const* src_next = a.blocks + (size_t(e) * a.n + size_t(row0 + 2 * rslot)) * row_stride + (seg_off - lead);
-  size_t const src_step = size_t(2 * a.RS) * row_stride;
-  int rows_left = nrows - 2 * rslot;
-  auto issue_pair = [&](uint32_t dst, uint32_t bar) {
-    bool const two = rows_left >= 2;
+  // Beyond the first two pairs of every warp, row pairs are claimed from a per-segment counter by whichever warp has a
+  // free stage (see qb_gemv_q4k.cu): the CTA's pairs rarely divide evenly over its warps.  Which warp computes a row does
+  // not change the row's arithmetic.
+  static_assert(kKqStages == 2, "the claim bookkeeping below keeps two pairs per warp");
+  uint8_t const* seg_base = a.blocks + (size_t(e) * a.n + size_t(row0)) * row_stride + (seg_off - lead);
+  auto issue_pair = [&](int pair, uint32_t dst, uint32_t bar) {
+    uint8_t const* src = seg_base + size_t(2 * pair) * row_stride;
+    bool const two = 2 * pair + 1 < nrows;
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(two ? 2u * copy_bytes : copy_bytes) : "memory");
     if (two && contiguous) {
       asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                   ::"r"(dst), "l"(src_next), "r"(2u * copy_bytes), "r"(bar) : "memory");
+                   ::"r"(dst), "l"(src), "r"(2u * copy_bytes), "r"(bar) : "memory");
     } else {
       asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                   ::"r"(dst), "l"(src_next), "r"(copy_bytes), "r"(bar) : "memory");
+                   ::"r"(dst), "l"(src), "r"(copy_bytes), "r"(bar) : "memory");
       if (two)
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                     ::"r"(dst + uint32_t(a.seg_stride)), "l"(src_next + row_stride), "r"(copy_bytes), "r"(bar) : "memory");
+                     ::"r"(dst + uint32_t(a.seg_stride)), "l"(src + row_stride), "r"(copy_bytes), "r"(bar) : "memory");
     }
-    src_next += src_step;
-    rows_left -= 2 * a.RS;
   };
+  int* claim = reinterpret_cast<int*>(red) + 16;                  // [S] next unclaimed pair per K segment (S <= 16)
+  if (int(threadIdx.x) < a.S) claim[threadIdx.x] = kKqStages * a.RS;   // visible after the prologue's barriers
+  int cur = rslot < npairs ? rslot : -1;                          // pair held by the stage consumed next
+  int nxt = rslot + a.RS < npairs ? rslot + a.RS : -1;            // ... and by the other stage
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < kKqStages; ++s)
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar32 + 8u * s) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    for (int s = 0; s < kKqStages && s < n_my; ++s) issue_pair(ring32 + s * stage_bytes, bar32 + 8u * s);
+    if (cur >= 0) issue_pair(cur, ring32, bar32);
+    if (nxt >= 0) issue_pair(nxt, ring32 + stage_bytes, bar32 + 8u);
   }
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
@@ -477,8 +481,6 @@ __global__ void __launch_bounds__(kKqWarps * 32, 1) kquant_gemv1_kernel(KqArgs a
   uint32_t st_addr = ring32, st_bar = bar32;
   unsigned phase = 0;
   int st = 0;
-  int lr = 2 * rslot;
-  int const lr_step = 2 * a.RS;
   float p0 = 0.f, p1 = 0.f;                                       // previous pair's per-lane partial sums
   int plr = nrows;                                                // ... and its CTA-local row (nrows = scratch slot)
   auto reduce_store = [&](float t0, float t1, int row_l) {
@@ -491,29 +493,34 @@ __global__ void __launch_bounds__(kKqWarps * 32, 1) kquant_gemv1_kernel(KqArgs a
     v += __shfl_xor_sync(0xffffffffu, v, 1);
     if ((lane & 15) == 0) part[(row_l + (lane >> 4)) * a.S + seg] = v;   // rows nrows, nrows+1 are scratch
   };
-  int i = 0;
-  for (; i < n_my; ++i) {
-    if (!k_try_wait(st_bar, phase) && !k_slow_wait(st_bar, phase, a.status, kWaitNs)) break;
+  bool gave_up = false;
+  while (cur >= 0) {
+    if (!k_try_wait(st_bar, phase) && !k_slow_wait(st_bar, phase, a.status, kWaitNs)) { gave_up = true; break; }
     float const t0 = kq_half_block_dot<QT>(st_addr + lane_off, h, xr, sxg, fm);
     float const t1 = kq_half_block_dot<QT>(st_addr + uint32_t(contiguous ? copy_bytes : unsigned(a.seg_stride)) + lane_off, h, xr, sxg, fm);
     reduce_store(p0, p1, plr);
+    int const lr = 2 * cur;
     p0 = active ? t0 : 0.f;
     p1 = (active && lr + 1 < nrows) ? t1 : 0.f;
     plr = lr;
     __syncwarp();
-    if (lane == 0 && i + kKqStages < n_my) issue_pair(st_addr, st_bar);
-    lr += lr_step;
+    int c = -1;
+    if (lane == 0) {
+      c = atomicAdd(&claim[seg], 1);
+      if (c < npairs) issue_pair(c, st_addr, st_bar); else c = -1;
+    }
+    c = __shfl_sync(0xffffffffu, c, 0);
+    cur = nxt; nxt = c;
     st_addr += stage_bytes; st_bar += 8u;
     if (++st == kKqStages) { st = 0; st_addr = ring32; st_bar = bar32; phase ^= 1u; }
   }
   reduce_store(p0, p1, plr);
-  if (i < n_my) {
-    // a wait gave up: drain this warp's other copies still in flight (bounded, short) before the shared memory can be
-    // handed to another CTA
-    for (int j = i + 1; j < n_my && j < i + kKqStages; ++j) {
-      uint32_t const b = bar32 + 8u * (j % kKqStages);
-      if (!k_try_wait(b, unsigned(j / kKqStages) & 1u)) (void)k_slow_wait(b, unsigned(j / kKqStages) & 1u, nullptr, 250000000ull);
-    }
+  if (gave_up && nxt >= 0) {
+    // a wait gave up: drain this warp's other copy still in flight (bounded, short) before the shared memory can be handed
+    // to another CTA
+    uint32_t const ob = st == 0 ? bar32 + 8u : bar32;
+    unsigned const op = st == 0 ? phase : (phase ^ 1u);
+    if (!k_try_wait(ob, op)) (void)k_slow_wait(ob, op, nullptr, 250000000ull);
   }
   __syncthreads();
   for (int r = threadIdx.x; r < nrows; r += T) {
