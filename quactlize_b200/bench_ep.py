@@ -13,6 +13,7 @@ layer for a sample of its own tokens with ALL experts held locally and compares 
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 
@@ -52,7 +53,7 @@ def zipf_routes(tokens: int, experts: int, top_k: int, seed: int, alpha: float =
 
 def run(dev, rank: int, world: int, steps: int = 10, peaks=None, sampler=None, tokens: int = 4096, experts: int = 8,
         hidden: int = 4096, ffn: int = 14336, transport: str = "peer", check_tokens: int = 48, top_k: int = TOP_K,
-        bits: int = BITS, gs: int = GS, alpha: float = 1.1) -> dict:
+        bits: int = BITS, gs: int = GS, alpha: float = 1.1, graph: bool = True) -> dict:
     if experts % world or tokens % world:
         return {"skipped": f"{experts} experts / {tokens} tokens do not divide over {world} ranks"}
     TOP_K, BITS, GS = top_k, bits, gs                        # noqa: N806 (shadow the module defaults below)
@@ -114,10 +115,40 @@ def run(dev, rank: int, world: int, steps: int = 10, peaks=None, sampler=None, t
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    # The step as a CUDA graph (kernels and NCCL collectives captured on one stream) where capture works, so the short
+    # kernels of the exchange are not spaced by the host; the same step enqueued call by call otherwise.
+    step, mode = (lambda: layer(x, routes, wts)), "eager"
+    if graph:
+        g, g_out = None, None
+        try:
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):                    # warm the step on a side stream, as capture requires
+                for _ in range(2):
+                    layer(x, routes, wts)
+            torch.cuda.current_stream(dev).wait_stream(side)
+            torch.cuda.synchronize(dev)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                g_out = layer(x, routes, wts)
+            ok_here = 1
+        except Exception:                                    # capture not possible here (e.g. the NCCL build): stay eager
+            ok_here = 0
+        torch.cuda.synchronize(dev)
+        captured = torch.tensor([ok_here], device=dev)
+        dist.all_reduce(captured, op=dist.ReduceOp.MIN)      # nobody replays (its collectives would wait) unless everybody captured
+        if int(captured.item()) == 1:
+            g.replay()
+            torch.cuda.synchronize(dev)
+            same_g = torch.tensor([1 if torch.equal(g_out, out) else 0], device=dev)
+            dist.all_reduce(same_g, op=dist.ReduceOp.MIN)
+            if int(same_g.item()) == 1:
+                step, mode = g.replay, "cuda_graph"
     if sampler is not None:
         sampler.start()
-    step_ms = timed(lambda: layer(x, routes, wts), steps)
+    step_ms = timed(step, steps)
     clocks = sampler.stop() if sampler is not None else None
+    eager_ms = timed(lambda: layer(x, routes, wts), steps) if mode == "cuda_graph" else step_ms
     # the local GEMMs alone, on the rows this rank really received (max over ranks = what bounds the step)
     local_off = layer.plan(routes).local_off
     my_rows = int(local_off[-1].item())
@@ -136,7 +167,7 @@ def run(dev, rank: int, world: int, steps: int = 10, peaks=None, sampler=None, t
                        f"{tokens} tokens in total (strong scaling), " + (f"Zipf({alpha}) router" if alpha else "uniform router"),
            "n_gpus": world, "transport": used, "collectives": "all_gather(route counts) + 2 x all_reduce(1 element) as stream-ordered barriers"
            if layer.transport == "peer" else "all_gather(route counts) + 2 x all_to_all(rows)",
-           "ms_per_step": round(step_ms, 4), "gemm_ms_max_rank": round(gemm_ms, 4), "plan_ms": round(plan_ms, 4),
+           "launch_mode": mode, "ms_per_step": round(step_ms, 4), "ms_per_step_eager": round(eager_ms, 4), "gemm_ms_max_rank": round(gemm_ms, 4), "plan_ms": round(plan_ms, 4),
            "exchange_and_combine_ms": round(max(step_ms - gemm_ms, 0.0), 4), "gemm_share_of_step": round(gemm_ms / step_ms, 4),
            "tflops_aggregate": round(flops / step_ms / 1e9, 1), "rows_total": int(total_rows),
            "rows_per_rank": [int(p.item()) for p in per_rank], "imbalance_max_over_mean": round(float(mx.item()) * world / total_rows, 3),
@@ -152,14 +183,15 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--transport", default="peer", choices=["peer", "nccl"])
     ap.add_argument("--small", action="store_true", help="a small layer (hidden 512, ffn 768) for tests")
+    ap.add_argument("--no-graph", action="store_true", help="enqueue the step call by call instead of replaying a CUDA graph")
     ap.add_argument("--cfg5", action="store_true", help="the decode-MoE configuration: 128 experts top-8, 2048/768, W2A16 gs=64")
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    dist.init_process_group("nccl", device_id=dev)
+    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(minutes=5))   # a collective that is never joined ends the run, not the box's time
     kw = {"hidden": 512, "ffn": 768} if args.small else dict(CFG5) if args.cfg5 else {}
-    rec = run(dev, rank, world, steps=args.steps, tokens=args.tokens, transport=args.transport, **kw)
+    rec = run(dev, rank, world, steps=args.steps, tokens=args.tokens, transport=args.transport, graph=not args.no_graph, **kw)
     if rank == 0:
         print(json.dumps(rec), flush=True)
     dist.destroy_process_group()
