@@ -280,7 +280,12 @@ int quactlize_b200_planes_dequantize_dev_v1(uint8_t const* low, uint8_t const* h
  * stream-ordered collective.  ep_return_addr: the owner turns received tags into addresses inside ITS mappings of the
  * senders' combine buffers (peer_comb[src] + item*row_bytes) for the row map of quactlize_b200_gemm_plane_dev_v2.
  * ep_combine: out[t] = sum_j weights[t][j] * comb[item_of_route[t*top_k+j]] (fp32, route order), bf16 rows of h elements.
- * silu_mul: out[r][c] = silu(gate_up[r][c]) * gate_up[r][f+c], bf16, for min(*rows_dev, max_rows) rows. */
+ * silu_mul: out[r][c] = silu(gate_up[r][c]) * gate_up[r][f+c], bf16, for min(*rows_dev, max_rows) rows.
+ * ep_sync: a rendezvous of the ranks through peer memory instead of a collective.  Every rank allocates a sync area of
+ * ep_sync_bytes(world, experts) bytes (zeroed once), peers map it, peer_sync[w] is rank w's area.  One launch per rank
+ * and barrier id (0..2): optionally stores counts_local[experts] into every rank's table counts_all[world][experts]
+ * (byte 1024 of the area), then posts an epoch to every rank and waits (bounded, 2 s, status word on expiry) until
+ * every rank's epoch has arrived.  Stream-ordered after the rank's earlier stores into peer memory. */
 int quactlize_b200_peer_alloc(long long bytes, void** ptr, unsigned char* handle64);
 int quactlize_b200_peer_open(unsigned char const* handle64, void** ptr);
 int quactlize_b200_peer_close(void* ptr);
@@ -297,6 +302,9 @@ int quactlize_b200_ep_return_addr_dev_v1(unsigned long long const* tags, unsigne
 int quactlize_b200_ep_combine_dev_v1(void const* comb, int const* item_of_route, float const* weights, void* out, int tokens,
                                      int top_k, int h, void* stream);
 int quactlize_b200_silu_mul_dev_v1(void const* gate_up, void* out, int const* rows_dev, int max_rows, int f, void* stream);
+int quactlize_b200_ep_sync_bytes(int world, int experts);
+int quactlize_b200_ep_sync_dev_v1(unsigned long long const* peer_sync, int rank, int world, int id, int const* counts_local,
+                                  int experts, void* stream);
 
 /* ================================ host-only artifact producers ================================================== */
 

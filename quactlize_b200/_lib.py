@@ -80,6 +80,8 @@ SIGNATURES = {
     "quactlize_b200_ep_dispatch_dev_v1": (I, [P, P, P, P, P, P, I, I, I, P]),
     "quactlize_b200_ep_return_addr_dev_v1": (I, [P, P, I, P, I, I, P, P]),
     "quactlize_b200_ep_combine_dev_v1": (I, [P, P, P, P, I, I, I, P]),
+    "quactlize_b200_ep_sync_bytes": (I, [I, I]),
+    "quactlize_b200_ep_sync_dev_v1": (I, [P, I, I, I, P, I, P]),
     "quactlize_b200_silu_mul_dev_v1": (I, [P, P, P, I, I, P]),
     "quactlize_b200_gemm_plane_splitk_workspace_bytes_v1": (I64, [I, I, I]),
     "quactlize_b200_gemm_plane_splitk_dev_v1": (I, [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, I, P, I64, P]),

@@ -53,7 +53,7 @@ def zipf_routes(tokens: int, experts: int, top_k: int, seed: int, alpha: float =
 
 def run(dev, rank: int, world: int, steps: int = 10, peaks=None, sampler=None, tokens: int = 4096, experts: int = 8,
         hidden: int = 4096, ffn: int = 14336, transport: str = "peer", check_tokens: int = 48, top_k: int = TOP_K,
-        bits: int = BITS, gs: int = GS, alpha: float = 1.1, graph: bool = True) -> dict:
+        bits: int = BITS, gs: int = GS, alpha: float = 1.1, graph: bool = True, sync: str = "peer") -> dict:
     if experts % world or tokens % world:
         return {"skipped": f"{experts} experts / {tokens} tokens do not divide over {world} ranks"}
     TOP_K, BITS, GS = top_k, bits, gs                        # noqa: N806 (shadow the module defaults below)
@@ -68,7 +68,7 @@ def run(dev, rank: int, world: int, steps: int = 10, peaks=None, sampler=None, t
     capacity = tokens * TOP_K
     used = transport
     try:
-        layer = ep.ExpertParallelFFN(gate_up, down, experts, TOP_K, BITS, GS, capacity, t_r * TOP_K, transport=transport)
+        layer = ep.ExpertParallelFFN(gate_up, down, experts, TOP_K, BITS, GS, capacity, t_r * TOP_K, transport=transport, sync=sync)
     except RuntimeError as e:                                # IPC peer mapping unavailable: same step over NCCL all_to_all
         if transport != "peer":
             raise
@@ -165,7 +165,9 @@ def run(dev, rank: int, world: int, steps: int = 10, peaks=None, sampler=None, t
     flops = 2.0 * total_rows * hidden * ffn * 3                           # gate, up and down over the real rows
     rec = {"workload": f"MoE FFN, {experts} experts top-{TOP_K}, hidden {hidden}, ffn {ffn}, int{BITS} gs{GS} scale+zero, bf16, "
                        f"{tokens} tokens in total (strong scaling), " + (f"Zipf({alpha}) router" if alpha else "uniform router"),
-           "n_gpus": world, "transport": used, "collectives": "all_gather(route counts) + 2 x all_reduce(1 element) as stream-ordered barriers"
+           "n_gpus": world, "transport": used, "collectives": ("none inside the step: route counts and three meetings of the ranks through epoch words in peer memory"
+                           if getattr(layer, "sync", "nccl") == "peer" else
+                           "all_gather(route counts) + 2 x all_reduce(1 element) as stream-ordered barriers")
            if layer.transport == "peer" else "all_gather(route counts) + 2 x all_to_all(rows)",
            "launch_mode": mode, "ms_per_step": round(step_ms, 4), "ms_per_step_eager": round(eager_ms, 4), "gemm_ms_max_rank": round(gemm_ms, 4), "plan_ms": round(plan_ms, 4),
            "exchange_and_combine_ms": round(max(step_ms - gemm_ms, 0.0), 4), "gemm_share_of_step": round(gemm_ms / step_ms, 4),
@@ -183,6 +185,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--transport", default="peer", choices=["peer", "nccl"])
     ap.add_argument("--small", action="store_true", help="a small layer (hidden 512, ffn 768) for tests")
+    ap.add_argument("--sync", default="peer", choices=["peer", "nccl"], help="how the ranks meet inside a step (peer transport)")
     ap.add_argument("--no-graph", action="store_true", help="enqueue the step call by call instead of replaying a CUDA graph")
     ap.add_argument("--cfg5", action="store_true", help="the decode-MoE configuration: 128 experts top-8, 2048/768, W2A16 gs=64")
     args = ap.parse_args()
@@ -191,7 +194,7 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(minutes=5))   # a collective that is never joined ends the run, not the box's time
     kw = {"hidden": 512, "ffn": 768} if args.small else dict(CFG5) if args.cfg5 else {}
-    rec = run(dev, rank, world, steps=args.steps, tokens=args.tokens, transport=args.transport, graph=not args.no_graph, **kw)
+    rec = run(dev, rank, world, steps=args.steps, tokens=args.tokens, transport=args.transport, graph=not args.no_graph, sync=args.sync, **kw)
     if rank == 0:
         print(json.dumps(rec), flush=True)
     dist.destroy_process_group()

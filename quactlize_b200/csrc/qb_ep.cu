@@ -24,6 +24,7 @@
 #include <cstdint>
 #include <cstring>
 
+#include "qb_device.cuh"
 #include "qb_runtime.hpp"
 
 namespace qb {
@@ -57,25 +58,74 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(long long const* __restri
   int* first_row = sh;                 // [experts] row of (expert, this source) in the owner's buffer
   int* first_item = sh + experts;      // [experts] first item of the expert among this rank's items
   int* cursor = sh + 2 * experts;      // [experts]
+  __shared__ int warp_tot[2][32];
   int const per = experts / world;
-  if (threadIdx.x == 0) {
-    int items = 0;
-    for (int o = 0; o < world; ++o) {
-      int row = 0;                                                     // rows before expert e in owner o's buffer
-      for (int j = 0; j < per; ++j) {
-        int const e = o * per + j;
-        int below = 0, total = 0;
-        for (int s = 0; s < world; ++s) { int const c = counts_all[s * experts + e]; if (s < rank) below += c; total += c; }
-        first_row[e] = row + below;
-        first_item[e] = items;
-        items += counts_all[rank * experts + e];
-        cursor[e] = 0;
-        if (o == rank) local_off[j] = row;
-        row += total;
+  // Per expert, in parallel: rows of lower ranks (below), rows of all ranks (total), rows of this rank (mine); then two
+  // block-wide exclusive scans over the experts (of mine: first item; of total: rows before the expert, taken relative to
+  // the first expert of its owner).  A thread owns a run of consecutive experts so the scans are one pass of shuffles.
+  int const chunk = (experts + int(blockDim.x) - 1) / int(blockDim.x), e0 = threadIdx.x * chunk;
+  int below_l[4], mine_l[4], total_l[4];                           // experts <= 4096 and 1024 threads: chunk <= 4
+  int sum_m = 0, sum_t = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int const e = e0 + i;
+    below_l[i] = mine_l[i] = total_l[i] = 0;
+    if (i < chunk && e < experts) {
+      for (int s2 = 0; s2 < world; ++s2) {
+        int const c = counts_all[s2 * experts + e];
+        if (s2 < rank) below_l[i] += c;
+        if (s2 == rank) mine_l[i] = c;
+        total_l[i] += c;
       }
-      if (o == rank) local_off[per] = row;
+    }
+    sum_m += mine_l[i]; sum_t += total_l[i];
+  }
+  int const lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int inc_m = sum_m, inc_t = sum_t;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int const um = __shfl_up_sync(0xffffffffu, inc_m, o), ut = __shfl_up_sync(0xffffffffu, inc_t, o);
+    if (lane >= o) { inc_m += um; inc_t += ut; }
+  }
+  if (lane == 31) { warp_tot[0][wid] = inc_m; warp_tot[1][wid] = inc_t; }
+  __syncthreads();
+  if (wid == 0) {
+    int vm = lane < int(blockDim.x >> 5) ? warp_tot[0][lane] : 0, vt = lane < int(blockDim.x >> 5) ? warp_tot[1][lane] : 0;
+    int im = vm, it = vt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int const um = __shfl_up_sync(0xffffffffu, im, o), ut = __shfl_up_sync(0xffffffffu, it, o);
+      if (lane >= o) { im += um; it += ut; }
+    }
+    warp_tot[0][lane] = im - vm; warp_tot[1][lane] = it - vt;       // exclusive over the warps
+  }
+  __syncthreads();
+  int run_m = warp_tot[0][wid] + inc_m - sum_m, run_t = warp_tot[1][wid] + inc_t - sum_t;   // exclusive prefix of this thread's run
+  // rows before each expert, over all experts, parked in `cursor` for the owner-relative subtraction below
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int const e = e0 + i;
+    if (i < chunk && e < experts) {
+      first_item[e] = run_m;
+      cursor[e] = run_t;
+      first_row[e] = below_l[i];
+      run_m += mine_l[i]; run_t += total_l[i];
     }
   }
+  if (e0 <= experts - 1 && e0 + chunk > experts - 1) sh[3 * experts] = run_t;   // grand total, by the thread that owns the last expert
+  __syncthreads();
+  int const grand = sh[3 * experts];
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    int const o = e / per, before = cursor[e] - cursor[o * per];
+    first_row[e] += before;
+    if (o == rank) local_off[e - o * per] = before;
+  }
+  if (threadIdx.x == 0) {
+    int const end = (rank + 1) * per < experts ? cursor[(rank + 1) * per] : grand;
+    local_off[per] = end - cursor[rank * per];
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) cursor[e] = 0;
   __syncthreads();
   for (int r = threadIdx.x; r < routes; r += blockDim.x) {
     long long const e64 = expert_of_route[r];
@@ -215,6 +265,63 @@ extern "C" int quactlize_b200_peer_free(void* ptr) {
   return 0;
 }
 
+// ---- rendezvous of the ranks through peer memory ---------------------------------------------------------------------------
+// Every rank owns a small sync area that all peers have mapped: per barrier id a row of epoch words, one per source rank,
+// this rank's own epoch counters (kept on the device so a replayed CUDA graph advances them), and from byte 1024 the
+// table counts_all[world][experts].  One CTA: (optionally) store this rank's route counts into every rank's table, fence
+// at system scope, store the new epoch into row `id`, word `rank`, of every rank's area, then wait until every word of the
+// own row has reached the epoch.  The wait is bounded (2 s): a peer that never arrives leaves a status code, not a hang.
+// It runs as one launch per GPU; ranks are different GPUs, so the launches run at the same time by construction.
+constexpr int kEpSyncIds = 3, kEpSyncRow = 64, kEpSyncCountsByte = 1024;      // words per row; epochs follow the rows
+__global__ void __launch_bounds__(256) ep_sync_kernel(unsigned long long const* __restrict__ peer_sync, int rank, int world, int id,
+                                                      int const* __restrict__ counts_local, int experts, unsigned int* status) {
+  __shared__ unsigned epoch_s;
+  unsigned* mine = reinterpret_cast<unsigned*>(peer_sync[rank]);
+  if (counts_local) {
+    for (int i = threadIdx.x; i < world * experts; i += blockDim.x) {
+      int const w = i / experts, e = i - w * experts;
+      int* table = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(peer_sync[w]) + kEpSyncCountsByte);
+      table[rank * experts + e] = counts_local[e];
+    }
+  }
+  __threadfence_system();                                      // this thread's stores (and, through the launch order of the
+  if (threadIdx.x == 0) epoch_s = ++mine[kEpSyncIds * kEpSyncRow + id];   // stream, the preceding kernels') before the epoch
+  __syncthreads();
+  unsigned const epoch = epoch_s;
+  if (int(threadIdx.x) < world) {
+    unsigned* theirs = reinterpret_cast<unsigned*>(peer_sync[threadIdx.x]) + id * kEpSyncRow + rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
+    unsigned const* flag = mine + id * kEpSyncRow + threadIdx.x;
+    unsigned long long const t0 = global_ns();
+    unsigned seen = 0, spins = 0;
+    for (;;) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+      if (int(seen - epoch) >= 0) break;                       // epochs only grow; a fast peer may already be one ahead
+      if ((++spins & 255u) == 0 && global_ns() - t0 > kWaitNs) {
+        if (status) atomicCAS(status, 0u, unsigned(kWaitStageTimeout));
+        break;
+      }
+    }
+  }
+  __syncthreads();
+}
+
+extern "C" int quactlize_b200_ep_sync_bytes(int world, int experts) {
+  if (world <= 0 || world > kEpSyncRow || experts < 0 || experts > 4096) return -1;
+  return kEpSyncCountsByte + world * experts * 4;
+}
+
+extern "C" int quactlize_b200_ep_sync_dev_v1(unsigned long long const* peer_sync, int rank, int world, int id, int const* counts_local,
+                                             int experts, void* stream) {
+  if (!peer_sync || world <= 0 || world > kEpSyncRow || rank < 0 || rank >= world || id < 0 || id >= kEpSyncIds ||
+      (counts_local && (experts <= 0 || experts > 4096))) return 20;
+  rt_clear_error();
+  unsigned int* status = rt_device_status_ptr();
+  if (!status) return kRuntimeError;
+  ep_sync_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(peer_sync, rank, world, id, counts_local, experts, status);
+  return rt_check_launch("expert-parallel rendezvous enqueue") ? 0 : kRuntimeError;
+}
+
 extern "C" int quactlize_b200_ep_count_dev_v1(long long const* expert_of_route, int routes, int experts, int* counts, void* stream) {
   if (!expert_of_route || !counts || routes < 0 || experts <= 0 || experts > 4096) return 20;
   rt_clear_error();
@@ -228,7 +335,7 @@ extern "C" int quactlize_b200_ep_plan_dev_v1(long long const* expert_of_route, i
   if (!expert_of_route || !counts_all || !item_token || !item_rank || !item_pos || !item_of_route || !local_off || world <= 0 ||
       rank < 0 || rank >= world || experts <= 0 || experts > 4096 || experts % world || routes < 0 || top_k <= 0) return 20;
   rt_clear_error();
-  ep_plan_kernel<<<1, 1024, size_t(experts) * 12, static_cast<cudaStream_t>(stream)>>>(expert_of_route, counts_all, rank, world, experts,
+  ep_plan_kernel<<<1, 1024, size_t(experts) * 12 + 16, static_cast<cudaStream_t>(stream)>>>(expert_of_route, counts_all, rank, world, experts,
                                                                                       routes, top_k, item_token, item_rank, item_pos,
                                                                                       item_of_route, local_off);
   return rt_check_launch("expert-parallel plan enqueue") ? 0 : kRuntimeError;

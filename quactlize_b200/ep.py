@@ -72,11 +72,14 @@ class _Array:
 class PeerBuffers:
     """This rank's receive buffers (rows, return addresses, combine rows) and the mapped buffers of every peer."""
 
-    def __init__(self, capacity: int, row_elems: int, routes_capacity: int, out_elems: int, group=None):
+    def __init__(self, capacity: int, row_elems: int, routes_capacity: int, out_elems: int, group=None, experts: int = 0):
         self.group, self.L = group, _lib.lib()
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         dev = torch.device("cuda", torch.cuda.current_device())
-        sizes = {"rows": capacity * row_elems * 2, "ret": capacity * 8, "comb": routes_capacity * out_elems * 2}
+        sync_bytes = self.L.quactlize_b200_ep_sync_bytes(self.world, experts)
+        if sync_bytes <= 0:
+            raise RuntimeError(f"no sync area for {self.world} ranks and {experts} experts")
+        sizes = {"rows": capacity * row_elems * 2, "ret": capacity * 8, "comb": routes_capacity * out_elems * 2, "sync": sync_bytes}
         self.own, handles = {}, {}
         for name, nbytes in sizes.items():
             p, h = C.c_void_p(), C.create_string_buffer(64)
@@ -104,6 +107,11 @@ class PeerBuffers:
         self.ret = torch.as_tensor(_Array(self.own["ret"], (capacity,), "<i8"), device=dev)
         self.comb = torch.as_tensor(_Array(self.own["comb"], (routes_capacity, out_elems), "<i2"), device=dev).view(torch.bfloat16)
         self.comb_base, self.comb_row_bytes = self.own["comb"], out_elems * 2
+        self.peer_sync = as_dev(self.ptrs["sync"])
+        self.sync = torch.as_tensor(_Array(self.own["sync"], (sync_bytes // 4,), "<i4"), device=dev)
+        self.sync.zero_()                                    # epochs start at zero everywhere before anybody posts
+        self.counts_all = self.sync[256:256 + self.world * experts].view(self.world, experts) if experts else None
+        torch.cuda.synchronize()
         dist.barrier(group=group)
 
     def close(self):
@@ -111,7 +119,7 @@ class PeerBuffers:
         dist.barrier(group=self.group)                       # nobody still writes into a buffer that is about to go
         for p in self.mapped:
             self.L.quactlize_b200_peer_close(p)
-        self.rows = self.ret = self.comb = None
+        self.rows = self.ret = self.comb = self.sync = self.counts_all = None
         for p in self.own.values():
             self.L.quactlize_b200_peer_free(p)
         self.mapped, self.own = [], {}
@@ -182,14 +190,17 @@ class ExpertParallelFFN:
     capacity: rows the receive buffer holds (the routes of ALL ranks is always enough)."""
 
     def __init__(self, gate_up, down, experts: int, top_k: int, bits: int, group_size: int, capacity: int, max_local_routes: int,
-                 transport: str = "peer", group=None):
+                 transport: str = "peer", group=None, sync: str = "peer"):
         self.gate_up, self.down, self.experts, self.top_k, self.bits, self.gs = gate_up, down, experts, top_k, bits, group_size
         self.group, self.world, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
         if experts % self.world:
             raise ValueError(f"{experts} experts do not divide over {self.world} ranks")
         self.hidden, self.ffn = gate_up[0].shape[2] * 8 // bits, down[0].shape[2] * 8 // bits
         self.capacity, self.transport = capacity, transport
-        self.buf = PeerBuffers(capacity, self.hidden, max_local_routes, self.hidden, group) if transport == "peer" else None
+        self.buf = PeerBuffers(capacity, self.hidden, max_local_routes, self.hidden, group, experts) if transport == "peer" else None
+        # how the ranks meet inside a step: "peer" = epoch words in mapped memory (one small kernel per meeting, no collective
+        # in the step at all), "nccl" = all_gather of the counts and one-element all_reduces
+        self.sync = sync if transport == "peer" else "nccl"
         dev = gate_up[0].device
         self._flag = torch.zeros(1, device=dev)
         self._plans = {}
@@ -200,8 +211,13 @@ class ExpertParallelFFN:
             self.buf.close()
             self.buf = None
 
-    def _barrier(self):
-        dist.all_reduce(self._flag, group=self.group)        # stream-ordered: peers' stores before this, reads after it
+    def _barrier(self, which: int):
+        if self.sync == "peer":
+            rc = _lib.lib().quactlize_b200_ep_sync_dev_v1(_p(self.buf.peer_sync), self.rank, self.world, which, None, 0, _stream())
+            if rc:
+                raise RuntimeError(f"rendezvous failed (rc={rc})")
+        else:
+            dist.all_reduce(self._flag, group=self.group)    # stream-ordered: peers' stores before this, reads after it
 
     def plan(self, routes: torch.Tensor) -> Plan:
         """ep_count -> all_gather of the counts -> ep_plan: three launches, nothing copied to the host."""
@@ -222,8 +238,13 @@ class ExpertParallelFFN:
             p.counts_all = p.counts_flat.view(self.world, self.experts)
             self._plans[r] = p
         rc = L.quactlize_b200_ep_count_dev_v1(_p(flat), r, self.experts, _p(p.counts), _stream())
-        dist.all_gather_into_tensor(p.counts_flat, p.counts, group=self.group)
-        rc = rc or L.quactlize_b200_ep_plan_dev_v1(_p(flat), _p(p.counts_flat), self.rank, self.world, self.experts, r, self.top_k,
+        if self.sync == "peer":                              # every rank's counts land in every rank's table, then a meeting
+            rc = rc or L.quactlize_b200_ep_sync_dev_v1(_p(self.buf.peer_sync), self.rank, self.world, 0, _p(p.counts), self.experts, _stream())
+            table = self.buf.counts_all
+        else:
+            dist.all_gather_into_tensor(p.counts_flat, p.counts, group=self.group)
+            table = p.counts_flat
+        rc = rc or L.quactlize_b200_ep_plan_dev_v1(_p(flat), _p(table), self.rank, self.world, self.experts, r, self.top_k,
                                                    _p(p.item_token), _p(p.item_rank), _p(p.item_pos), _p(p.item_of_route),
                                                    _p(p.local_off), _stream())
         if rc:
@@ -241,13 +262,13 @@ class ExpertParallelFFN:
                                                      _p(b.peer_ret), self.rank, p.routes, self.hidden * 2, _stream())
             if rc:
                 raise RuntimeError(f"dispatch failed (rc={rc})")
-            self._barrier()
+            self._barrier(1)
             rc = L.quactlize_b200_ep_return_addr_dev_v1(_p(b.ret), _p(b.peer_comb), self.world, _p(p.local_total), self.capacity,
                                                         self.hidden * 2, _p(self._addr), _stream())
             if rc:
                 raise RuntimeError(f"return addresses failed (rc={rc})")
             local_ffn(b.rows, p.local_off, self.gate_up, self.down, self.bits, self.gs, out_rows=self._addr)
-            self._barrier()
+            self._barrier(2)
             comb = b.comb
         else:
             comb = self._nccl_step(x, p)
