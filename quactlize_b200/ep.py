@@ -3,15 +3,19 @@
 Experts are sharded contiguously (rank r owns experts [r*E/W, (r+1)*E/W), leading-axis views of every artifact tensor);
 tokens stay where they are.  One step, all on the current stream:
 
-  plan      per-expert route counts (one small kernel), ONE small all_gather of them, and from that a single-CTA kernel
-            gives every route its final row in its owner's EXPERT-MAJOR receive buffer -- nothing is copied to the host
+  plan      per-expert route counts (one small kernel); `ep_sync` stores them into every rank's table through mapped
+            memory and lets the ranks meet (epoch words, bounded wait); from the table a single-CTA kernel gives every
+            route its final row in its owner's EXPERT-MAJOR receive buffer -- nothing is copied to the host
             (`plan_routes` states the same plan in torch index arithmetic; the tests hold the kernel to it);
   dispatch  `ep_dispatch`: every routed token row is stored straight into the owner's receive buffer at that row
             (NVLink peer stores into IPC-mapped buffers), with a tag saying where its result must come back to;
-  barrier   a one-element all_reduce orders those stores before the owners' reads;
+  meeting   `ep_sync` again orders those stores before the owners' reads (sync="nccl": a one-element all_reduce, and an
+            all_gather for the counts above);
   compute   gate/up grouped GEMM (tensor cores) -> silu(gate)*up -> down grouped GEMM whose EPILOGUE stores every output
             row at its return address, i.e. directly into the sender's combine buffer (`out_rows` of the plane GEMM);
-  barrier   again, then each rank sums its tokens' top-k rows with the router weights.
+  meeting   a third one, then each rank sums its tokens' top-k rows with the router weights.
+
+With the default sync="peer" a step contains no collective at all; NCCL serves the set-up (IPC handle exchange).
 
 So the regrouping permutations of an all_to_all formulation do not exist: rows land expert-major, results land in the
 order of the sender's own routes.  The receive buffers hold `capacity` rows (every rank could be sent everything); the

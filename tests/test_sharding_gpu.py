@@ -97,3 +97,33 @@ def test_plan_kernel_matches_the_index_arithmetic():
             for e, q in zip(item_expert.tolist(), pos.tolist()):
                 got.setdefault(e, set()).add(q)
             assert got == want
+
+
+def test_rendezvous_gives_up_when_a_rank_never_arrives():
+    """The meeting of the ranks through peer memory is a bounded wait: with a second "rank" whose epoch word nobody ever
+    writes (two sync areas on this one GPU, only rank 0 launched), the kernel returns after its limit, the status word
+    reports the expiry once, and a one-rank meeting afterwards passes."""
+    import ctypes as C
+    from quactlize_b200 import _lib
+    L = _lib.lib()
+    dev = torch.device("cuda", 0)
+    nbytes = L.quactlize_b200_ep_sync_bytes(2, 8)
+    assert nbytes == 1024 + 2 * 8 * 4
+    areas = [torch.zeros(nbytes // 4, dtype=torch.int32, device=dev) for _ in range(2)]
+    ptrs = torch.tensor([a.data_ptr() for a in areas], dtype=torch.int64, device=dev)
+    counts = torch.arange(8, dtype=torch.int32, device=dev)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert L.quactlize_b200_device_wait_status() == 0
+    assert L.quactlize_b200_ep_sync_dev_v1(C.c_void_p(ptrs.data_ptr()), 0, 2, 0, C.c_void_p(counts.data_ptr()), 8, stream) == 0
+    torch.cuda.synchronize()                                             # returns after the 2 s limit, no hang
+    assert L.quactlize_b200_device_wait_status() != 0                    # the expiry, reported once
+    assert L.quactlize_b200_device_wait_status() == 0
+    # rank 0's counts reached both tables, its epoch word both rows
+    for a in areas:
+        assert a[256:264].tolist() == list(range(8)) and int(a[0]) == 1
+    one = torch.tensor([areas[0].data_ptr()], dtype=torch.int64, device=dev)
+    assert L.quactlize_b200_ep_sync_dev_v1(C.c_void_p(one.data_ptr()), 0, 1, 1, None, 0, stream) == 0
+    torch.cuda.synchronize()
+    assert L.quactlize_b200_device_wait_status() == 0
+    assert L.quactlize_b200_ep_sync_dev_v1(C.c_void_p(ptrs.data_ptr()), 2, 2, 0, None, 0, stream) == 20   # rank out of range
