@@ -51,12 +51,16 @@ __device__ __forceinline__ unsigned long long global_ns() {
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity, unsigned int* status, unsigned code,
                                                   unsigned long long limit_ns = kWaitNs) {
   if (mbar_try_wait(bar, parity)) return true;
-  unsigned long long const t0 = global_ns();
+  unsigned long long t0 = 0;                                    // the clock is first read after 64 failed polls
   unsigned spins = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 63u) == 0 && global_ns() - t0 > limit_ns) {
-      if (status) atomicCAS(status, 0u, code);
-      return false;
+    if ((++spins & 63u) == 0) {
+      unsigned long long const now = global_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > limit_ns) {
+        if (status) atomicCAS(status, 0u, code);
+        return false;
+      }
     }
   }
   return true;

@@ -124,12 +124,14 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 template <class SM>
 __device__ __forceinline__ bool gemm_wait(SM& sm, uint64_t* bar, unsigned parity, unsigned int* status) {
   if (mbar_try_wait(bar, parity)) return true;
-  unsigned long long const t0 = global_ns();
-  unsigned spins = 0;
+  unsigned long long t0 = 0;                                  // the clock is first read after 32 failed polls: ordinary waits
+  unsigned spins = 0;                                         // of the pipeline never pay for it
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 31u) == 0) {
       if (sm.abort_flag) return false;
-      if (global_ns() - t0 > kWaitNs) {
+      unsigned long long const now = global_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitNs) {
         sm.abort_flag = 1;
         if (status) atomicCAS(status, 0u, unsigned(kWaitMmaTimeout));
         return false;

@@ -101,12 +101,16 @@ __device__ __forceinline__ bool r_try_wait(uint32_t bar, unsigned parity) {
   return ok != 0;
 }
 __device__ __noinline__ bool r_slow_wait(uint32_t bar, unsigned parity, unsigned int* status, unsigned long long limit) {
-  unsigned long long const t0 = global_ns();
+  unsigned long long t0 = 0;                                    // the clock is first read after 64 failed polls
   unsigned spins = 0;
   while (!r_try_wait(bar, parity)) {
-    if ((++spins & 63u) == 0 && global_ns() - t0 > limit) {
-      if (status) atomicCAS(status, 0u, unsigned(kWaitStageTimeout));
-      return false;
+    if ((++spins & 63u) == 0) {
+      unsigned long long const now = global_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > limit) {
+        if (status) atomicCAS(status, 0u, unsigned(kWaitStageTimeout));
+        return false;
+      }
     }
   }
   return true;
