@@ -33,6 +33,7 @@
 #include <algorithm>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -67,16 +68,25 @@ struct GemmArgs {
 // copy -> dequantise -> MMA chain, and co-resident CTAs overlap those chains.
 template <int LO, int HI, int MT, int NT, int DEPTH = 0> struct GemmSmem {
   static constexpr bool kBig = MT * NT == 4;
-  static constexpr int AST = DEPTH ? 2 : (kBig ? 3 : 4);   // activation ring: 64-k tiles of 128*MT rows
-  static constexpr int BST = DEPTH ? 2 : (kBig ? 2 : 4);   // dequantised operand ring: 64-k tiles of 128*NT columns
-  static constexpr int RST = DEPTH ? 2 : (kBig ? 2 : 3);   // raw ring: 128-k pieces of planes + scale rows
+#ifndef QB_GEMM_AST                                          // ring depths of the 256 x 256 tile (compile-time experiment switches)
+#define QB_GEMM_AST 3
+#endif
+#ifndef QB_GEMM_BST
+#define QB_GEMM_BST 2
+#endif
+  // DEPTH 2: the CTA is one of a PAIR (cluster of two along the rows, tcgen05 cta_group::2): it holds only its half of the
+  // weight columns (NTB tiles), which pays for deeper rings.
+  static constexpr int NTB = DEPTH == 2 ? NT / 2 : NT;
+  static constexpr int AST = DEPTH == 2 ? 4 : DEPTH ? 2 : (kBig ? QB_GEMM_AST : 4);   // activation ring: 64-k tiles of 128*MT rows
+  static constexpr int BST = DEPTH == 2 ? 3 : DEPTH ? 2 : (kBig ? QB_GEMM_BST : 4);   // dequantised operand ring: 64-k tiles of 128*NTB columns
+  static constexpr int RST = DEPTH == 2 ? 3 : DEPTH ? 2 : (kBig ? 2 : 3);             // raw ring: 128-k pieces of planes + scale rows
   static constexpr int kLoBytes = kTN * kRawK * LO / 8, kHiBytes = HI ? kTN * kRawK * HI / 8 : 1024;
   alignas(1024) uint8_t a[AST][MT * kATileBytes];
-  alignas(1024) uint8_t b[BST][NT * kBTileBytes];
-  alignas(1024) uint8_t raw_lo[RST][NT][kLoBytes];   // rows of 16*LO bytes, TMA-swizzled when 64 or 32 bytes long
-  alignas(1024) uint8_t raw_hi[RST][NT][kHiBytes];
-  alignas(128) uint8_t scale[RST][NT][kScaleBytes];
-  alignas(128) uint8_t zero[RST][NT][kScaleBytes];
+  alignas(1024) uint8_t b[BST][NTB * kBTileBytes];
+  alignas(1024) uint8_t raw_lo[RST][NTB][kLoBytes];  // rows of 16*LO bytes, TMA-swizzled when 64 or 32 bytes long
+  alignas(1024) uint8_t raw_hi[RST][NTB][kHiBytes];
+  alignas(128) uint8_t scale[RST][NTB][kScaleBytes];
+  alignas(128) uint8_t zero[RST][NTB][kScaleBytes];
   alignas(8) uint64_t a_full[AST];             // TMA -> MMA (activation tile landed)
   alignas(8) uint64_t a_empty[AST];            // MMA (tcgen05.commit) -> TMA
   alignas(8) uint64_t b_full[BST];             // dequant warps -> MMA (operand tile written)
@@ -119,6 +129,43 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// ---- the pair form (cluster of two CTAs, tcgen05 cta_group::2) ------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// the shared::cluster address of this CTA's shared address `a` in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t cluster_addr(uint32_t a, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrival on a barrier of the partner CTA.  Relaxed: what the arrival publishes (this CTA's operand tile, written for its
+// own tensor core) has been made visible by the proxy fence before it; a release at cluster scope here stalls every
+// dequantising warp on a cluster-wide memory barrier once per stage.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+// activation tile of this CTA, completion counted on the barrier at cluster address `cluster_bar` (the leader's)
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, CUtensorMap const* map, int c0, int c1, uint32_t cluster_bar) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(cluster_bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrival on one barrier (cluster address: this CTA's or the partner's) once the pair's MMAs issued so far have completed
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
 }
 
 template <class SM>
@@ -289,17 +336,22 @@ __device__ __forceinline__ void dequant_col(uint32_t lo_tile, uint32_t hi_tile, 
 template <int MT, int NT, int DEPTH> constexpr int gemm_dq() { return (MT == 2 && NT == 2 && DEPTH == 0) ? QB_GEMM_DQ : 1; }
 
 template <int LO, int HI, bool BF16, int MT, int NT, int DEPTH>
-__global__ void __launch_bounds__(128 + 128 * MT * gemm_dq<MT, NT, DEPTH>(), DEPTH ? 2 : 1)
+__global__ void __launch_bounds__(128 + 128 * MT * gemm_dq<MT, NT, DEPTH>(), DEPTH == 1 ? 2 : 1)
 mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_lo,
                   const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ CUtensorMap map_s,
                   const __grid_constant__ CUtensorMap map_z, GemmArgs g) {
   extern __shared__ uint8_t smem_raw[];
   using SM = GemmSmem<LO, HI, MT, NT, DEPTH>;
   constexpr int AST = SM::AST, BST = SM::BST, RST = SM::RST, kRows = kTM * MT, kCols = kTN * NT;
+  constexpr bool PAIR = DEPTH == 2;                           // one of two CTAs of a cluster: rows 256*rank.. of a 512-row tile,
+  constexpr int NTB = SM::NTB, kColsB = kTN * NTB;            // all 256 accumulator columns, but only half of the weight columns
+  constexpr int kRowsTile = PAIR ? 2 * kRows : kRows;         // rows of the tile a row-tile index names
+  static_assert(!PAIR || (MT == 2 && NT == 2), "the pair form is the 512 x 256 tile");
   constexpr int DQ = gemm_dq<MT, NT, DEPTH>();
   constexpr int kDqWarps = 4 * MT * DQ;                       // the first 4*MT of them also run the epilogue: one per 32 accumulator lanes
-  constexpr int NC = 8 * NT / MT / DQ;                        // 8-element chunks a dequant thread converts per stage
-  static_assert(NC >= 1 && NC * MT * DQ == 8 * NT, "the dequant threads tile a stage's chunks exactly");
+  constexpr int NC = 8 * NTB / MT / DQ;                       // 8-element chunks a dequant thread converts per stage
+  static_assert(NC >= 1 && NC * MT * DQ == 8 * NTB, "the dequant threads tile a stage's chunks exactly");
+  uint32_t const crank = PAIR ? cluster_ctarank() : 0u;
   SM& sm = *reinterpret_cast<SM*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -316,7 +368,7 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         int const x = base + lane;
         int r0 = 0, rows = 0;
         if (x < g.experts) { r0 = g.offsets[x]; rows = g.offsets[x + 1] - r0; }
-        int const cnt = (rows + kRows - 1) / kRows;
+        int const cnt = (rows + kRowsTile - 1) / kRowsTile;
         int incl = cnt;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) { int const u = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += u; }
@@ -328,8 +380,8 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           hit_e = __shfl_sync(0xffffffffu, x, src);
           int const lo_s = __shfl_sync(0xffffffffu, lo, src), r0_s = __shfl_sync(0xffffffffu, r0, src),
                     rows_s = __shfl_sync(0xffffffffu, rows, src);
-          hit_m0 = r0_s + (t - lo_s) * kRows;
-          hit_rows = min(kRows, rows_s - (t - lo_s) * kRows);
+          hit_m0 = r0_s + (t - lo_s) * kRowsTile;
+          hit_rows = min(kRowsTile, rows_s - (t - lo_s) * kRowsTile);
         }
         carry += __shfl_sync(0xffffffffu, incl, 31);
       }
@@ -337,14 +389,20 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     }
     __syncthreads();
     e = tile_of[0]; m0 = tile_of[1]; mrows = tile_of[2];
-    if (e < 0) return;                                        // uniform for the CTA, before any mbarrier or TMEM allocation
+    if (e < 0) return;                                        // uniform for the CTA (and the pair), before any mbarrier or TMEM allocation
   } else {
-    m0 = blockIdx.y * kRows; mrows = min(kRows, g.m_rows - m0);
+    int const t = blockIdx.y;
+    m0 = t * kRowsTile; mrows = min(kRowsTile, g.m_rows - m0);
     if (mrows <= 0) return;
   }
-  int const n0 = blockIdx.x * kCols;
-  int const nt_here = min(NT, (g.n - n0) / kTN);              // a 256-wide tile may hang over the last 128 columns
-  int const mt_here = min(MT, (mrows + kTM - 1) / kTM);       // ... and a ragged row tile over the last 128 rows
+  // Row blocks the MMAs cover: in the pair form block mt is rows 128*mt.. of BOTH CTAs' halves, and the leader's half is
+  // the fuller one, so the count comes from the whole tile's rows.  Then this CTA's own rows (none, for the partner of a
+  // tile of up to 256 rows: it still runs the pipeline, its half of the operand is needed, and stores nothing).
+  int const mt_here = min(MT, (mrows + kTM - 1) / kTM);       // a ragged row tile may end in the first 128 rows
+  if constexpr (PAIR) { m0 += int(crank) * kRows; mrows = max(0, min(kRows, mrows - int(crank) * kRows)); }
+  int const n0 = (PAIR ? int(blockIdx.x >> 1) : int(blockIdx.x)) * kCols;   // the pair's two CTAs are neighbours along x
+  int const nb0 = n0 + int(crank) * kColsB;                   // first weight column this CTA converts (pair form: its half)
+  int const nt_here = PAIR ? NT : min(NT, (g.n - n0) / kTN);  // a 256-wide tile may hang over the last 128 columns
   // split-K: slice z owns a contiguous run of 128-k pieces (pieces are dealt as evenly as they divide); its stages are
   // numbered from 0 for the rings, and offset by ks0 stages / p0 pieces where global k coordinates are formed
   int const pieces = g.k / kRawK, z = blockIdx.z, S = g.splits;
@@ -356,7 +414,7 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < AST; ++s) { mbar_init(&sm.a_full[s], 1); mbar_init(&sm.a_empty[s], 1); }
-    for (int s = 0; s < BST; ++s) { mbar_init(&sm.b_full[s], kDqWarps); mbar_init(&sm.b_empty[s], 1); }
+    for (int s = 0; s < BST; ++s) { mbar_init(&sm.b_full[s], PAIR ? 2 * kDqWarps : kDqWarps); mbar_init(&sm.b_empty[s], 1); }
     for (int s = 0; s < RST; ++s) { mbar_init(&sm.raw_full[s], 1); mbar_init(&sm.raw_empty[s], kDqWarps); }
     mbar_init(&sm.acc_full, 1);
     sm.abort_flag = 0;
@@ -364,18 +422,24 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 2) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(uint32_t(kTN * MT * NT)) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (PAIR) {                                     // the same warp of both CTAs, the same destination offset
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(uint32_t(kTN * MT * NT)) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(uint32_t(kTN * MT * NT)) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  if constexpr (PAIR) cluster_sync_all();                     // the partner's barriers exist before anything arrives on them
   uint32_t const tmem = sm.tmem_base;
 
   if (warp == 0) {
     // ================= TMA producer =================
     if (lane == 0) {
-      unsigned const raw_bytes = unsigned(NT) * (unsigned(kTN * kRawK * LO / 8) + unsigned(kTN * kRawK * HI / 8) +
+      unsigned const raw_bytes = unsigned(NTB) * (unsigned(kTN * kRawK * LO / 8) + unsigned(kTN * kRawK * HI / 8) +
                                                  unsigned(srows * kTN * 2) * (g.has_zero ? 2u : 1u));
       for (int i = 0; i < nks; ++i) {
         int const sa = i % AST;
@@ -385,25 +449,31 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           mbar_expect_tx(&sm.raw_full[r], raw_bytes);
           int const kk = (p0 + j) * kRawK;
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt) {                    // columns past n are out of bounds: zero-filled, still counted
-            tma_load_3d(sm.raw_lo[r][nt], &map_lo, kk * LO / 8, n0 + nt * kTN, e, &sm.raw_full[r]);
-            if constexpr (HI != 0) tma_load_3d(sm.raw_hi[r][nt], &map_hi, kk * HI / 8, n0 + nt * kTN, e, &sm.raw_full[r]);
-            tma_load_3d(sm.scale[r][nt], &map_s, n0 + nt * kTN, kk / gs, e, &sm.raw_full[r]);
-            if (g.has_zero) tma_load_3d(sm.zero[r][nt], &map_z, n0 + nt * kTN, kk / gs, e, &sm.raw_full[r]);
+          for (int nt = 0; nt < NTB; ++nt) {                   // columns past n are out of bounds: zero-filled, still counted
+            tma_load_3d(sm.raw_lo[r][nt], &map_lo, kk * LO / 8, nb0 + nt * kTN, e, &sm.raw_full[r]);
+            if constexpr (HI != 0) tma_load_3d(sm.raw_hi[r][nt], &map_hi, kk * HI / 8, nb0 + nt * kTN, e, &sm.raw_full[r]);
+            tma_load_3d(sm.scale[r][nt], &map_s, nb0 + nt * kTN, kk / gs, e, &sm.raw_full[r]);
+            if (g.has_zero) tma_load_3d(sm.zero[r][nt], &map_z, nb0 + nt * kTN, kk / gs, e, &sm.raw_full[r]);
           }
         }
         if (i >= AST && !gemm_wait(sm, &sm.a_empty[sa], unsigned(i / AST - 1) & 1u, g.status)) break;
 #ifdef QB_GABL_NOA
         if (i >= AST) { mbar_arrive(&sm.a_full[sa]); continue; }
 #endif
-        mbar_expect_tx(&sm.a_full[sa], MT * kATileBytes);
-        tma_load_2d(sm.a[sa], &map_a, (ks0 + i) * kTK, m0, &sm.a_full[sa]);
+        if constexpr (PAIR) {
+          // both CTAs' activation tiles are counted on the LEADER's barrier, which the leader arms for both
+          if (crank == 0) mbar_expect_tx(&sm.a_full[sa], 2 * MT * kATileBytes);
+          tma_load_2d_pair(sm.a[sa], &map_a, (ks0 + i) * kTK, m0, cluster_addr(smem_u32(&sm.a_full[sa]), 0));
+        } else {
+          mbar_expect_tx(&sm.a_full[sa], MT * kATileBytes);
+          tma_load_2d(sm.a[sa], &map_a, (ks0 + i) * kTK, m0, &sm.a_full[sa]);
+        }
       }
     }
   } else if (warp == 1) {
     // ================= MMA issuer =================
-    if (lane == 0) {
-      uint32_t const idesc = umma_idesc(BF16 ? 1 : 0, kTM, kTN * nt_here);
+    if (lane == 0 && crank == 0) {                             // pair form: the leader issues for both CTAs
+      uint32_t const idesc = umma_idesc(BF16 ? 1 : 0, PAIR ? 2 * kTM : kTM, kTN * nt_here);
       bool ok = true;
       for (int i = 0; i < nks && ok; ++i) {
         int const sa = i % AST, sb = i % BST;
@@ -417,19 +487,37 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         for (int kk = 0; kk < kTK / 16; ++kk)
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt)                      // every row block multiplies the same dequantised operand tile
-            if (mt < mt_here)
-              umma_f16(tmem + mt * kCols, umma_desc_sw128(a_addr + mt * kATileBytes + kk * 32), umma_desc_sw128(b_addr + kk * 32),
-                       idesc, (i | kk) ? 1u : 0u);
+            if (mt < mt_here) {
+              if constexpr (PAIR)
+                umma_f16_pair(tmem + mt * kCols, umma_desc_sw128(a_addr + mt * kATileBytes + kk * 32), umma_desc_sw128(b_addr + kk * 32),
+                              idesc, (i | kk) ? 1u : 0u);
+              else
+                umma_f16(tmem + mt * kCols, umma_desc_sw128(a_addr + mt * kATileBytes + kk * 32), umma_desc_sw128(b_addr + kk * 32),
+                         idesc, (i | kk) ? 1u : 0u);
+            }
 #endif
-        umma_commit(&sm.a_empty[sa]);                          // frees the rings' slots once these MMAs have read them
-        umma_commit(&sm.b_empty[sb]);
+        if constexpr (PAIR) {                                  // frees the slots in BOTH CTAs once these MMAs have read them
+          uint32_t const ae = smem_u32(&sm.a_empty[sa]), be = smem_u32(&sm.b_empty[sb]);
+          umma_commit_pair(cluster_addr(ae, 0)); umma_commit_pair(cluster_addr(ae, 1));
+          umma_commit_pair(cluster_addr(be, 0)); umma_commit_pair(cluster_addr(be, 1));
+        } else {
+          umma_commit(&sm.a_empty[sa]);                        // frees the rings' slots once these MMAs have read them
+          umma_commit(&sm.b_empty[sb]);
+        }
       }
-      if (ok) umma_commit(&sm.acc_full);
+      if (ok) {
+        if constexpr (PAIR) {
+          uint32_t const af = smem_u32(&sm.acc_full);
+          umma_commit_pair(cluster_addr(af, 0)); umma_commit_pair(cluster_addr(af, 1));
+        } else {
+          umma_commit(&sm.acc_full);
+        }
+      }
     }
   } else if (warp >= 4) {
     // ================= dequantise (thread = weight column), then epilogue =================
     int const t = threadIdx.x - 128;
-    int const col = t % kCols, part = t / kCols;               // kCols columns x (128*MT / kCols) chunk ranges
+    int const col = t % kColsB, part = t / kColsB;             // the CTA's weight columns x (128*MT*DQ / columns) chunk ranges
     int const nt = col >> 7, cin = col & 127;
     bool const live = nt < nt_here;
     float const coff = float(g.code_offset);
@@ -455,7 +543,8 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes -> visible to the MMA
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(&sm.b_full[sb]);
+        if (PAIR && crank != 0) mbar_arrive_cluster(cluster_addr(smem_u32(&sm.b_full[sb]), 0));   // the leader's barrier counts both CTAs' warps
+        else mbar_arrive(&sm.b_full[sb]);
         if (h == 1) mbar_arrive(&sm.raw_empty[r]);
       }
     }
@@ -513,9 +602,13 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     for (int s = 0; s < RST; ++s) { (void)mbar_wait_bounded(&sm.raw_full[s], 0, nullptr, 0, 100000000ull); (void)mbar_wait_bounded(&sm.raw_full[s], 1, nullptr, 0, 100000000ull); }
   }
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();                     // neither CTA's shared or tensor memory goes while the other may use it
   if (warp == 2) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(uint32_t(kTN * MT * NT)) : "memory");
+    if constexpr (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(uint32_t(kTN * MT * NT)) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(uint32_t(kTN * MT * NT)) : "memory");
   }
 }
 
@@ -656,7 +749,9 @@ int launch_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
   auto kern = mixed_gemm_kernel<LO, HI, BF16, MT, NT, DEPTH>;
   size_t const smem = sizeof(GemmSmem<LO, HI, MT, NT, DEPTH>) + 1024;
   static_assert(sizeof(GemmSmem<LO, HI, MT, NT, DEPTH>) + 1024 <= 232448, "shared memory of one CTA");
-  static_assert(DEPTH == 0 || sizeof(GemmSmem<LO, HI, MT, NT, DEPTH>) + 1024 <= 113 * 1024, "two CTAs of the shallow form share an SM");
+  static_assert(DEPTH != 1 || sizeof(GemmSmem<LO, HI, MT, NT, DEPTH>) + 1024 <= 113 * 1024, "two CTAs of the shallow form share an SM");
+  constexpr bool PAIR = DEPTH == 2;
+  if (PAIR && (d.n % (kTN * NT) != 0 || splits > 1)) return 30;  // the pair form covers whole 256-column tiles, one K slice
   {  // the opt-in to large dynamic shared memory is a per-device attribute of the function
     static std::mutex mu;
     static bool attr_set[kMaxDevices] = {};
@@ -672,9 +767,30 @@ int launch_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
     }
   }
   // row tiles: sum over experts of ceil(rows_e / tile) <= floor(total / tile) + the experts that hold rows
-  int const mtiles = d.experts > 0 ? d.total_rows / (kTM * MT) + std::min(d.experts, d.total_rows)
-                                   : (d.total_rows + kTM * MT - 1) / (kTM * MT);
+  int const tile_rows = kTM * MT * (PAIR ? 2 : 1);
+  int const mtiles = d.experts > 0 ? d.total_rows / tile_rows + std::min(d.experts, d.total_rows)
+                                   : (d.total_rows + tile_rows - 1) / tile_rows;
   if (mtiles > 65535) return 30;
+  if constexpr (PAIR) {                                        // clusters of two CTAs (neighbours along grid x; they split a tile's rows)
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * ((d.n + kTN * NT - 1) / (kTN * NT)), mtiles, 1);
+    cfg.blockDim = dim3(128 + 128 * MT * gemm_dq<MT, NT, DEPTH>());
+    cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    cudaError_t const le = cudaLaunchKernelEx(&cfg, kern, ma, ml, mh, ms, mz, g);
+    if (le != cudaSuccess) {
+      int ncl = -1;
+      cudaError_t const oe = cudaOccupancyMaxActiveClusters(&ncl, kern, &cfg);
+      std::fprintf(stderr, "[quactlize_b200] pair-form GEMM launch failed: %s (grid %u x %u, block %u, smem %zu, active clusters %d / %s)\n",
+                   cudaGetErrorString(le), cfg.gridDim.x, cfg.gridDim.y, cfg.blockDim.x, smem, ncl, cudaGetErrorString(oe));
+      (void)cudaGetLastError();
+      return kRuntimeError;
+    }
+    return 0;
+  }
   kern<<<dim3((d.n + kTN * NT - 1) / (kTN * NT), mtiles, splits), 128 + 128 * MT * gemm_dq<MT, NT, DEPTH>(), smem, stream>>>(ma, ml, mh, ms, mz, g);
   if (splits > 1) {
     int64_t const elems = int64_t(d.total_rows) * d.n;         // n % 128 == 0: whole float4 groups
@@ -699,7 +815,7 @@ int enqueue_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
   int const key = d.lo_bits * 10 + d.hi_bits;
   // 256 x 256 CTA tiles (four accumulators = all 512 TMEM columns) for prefill-sized problems; small ones keep 128 x 128
   int const avg_rows = d.experts > 0 ? d.total_rows / d.experts : d.total_rows;
-  bool const big = d.tile == 256 || (d.tile == 0 && avg_rows >= 192);
+  bool const big = d.tile == 256 || d.tile == 512 || (d.tile == 0 && avg_rows >= 192);
   if (d.shallow && !big) {                        // decode tactic: 128 x 128 tiles, two-deep rings, several CTAs per SM
 #define QB_GEMM_SHALLOW(K, L, H) case K: return d.act_bf16 ? launch_mixed_gemm<L, H, true, 1, 1, 1>(d, stream) : launch_mixed_gemm<L, H, false, 1, 1, 1>(d, stream);
     switch (key) {
@@ -709,6 +825,14 @@ int enqueue_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
     }
 #undef QB_GEMM_SHALLOW
   }
+  // The pair form (512 x 256 tile over a cluster of two CTAs, tcgen05 cta_group::2; each CTA converts half of the weight
+  // columns): int4 planes, whole 256-column tiles, one K slice.  Opt-in (QUACTLIZE_B200_GEMM_PAIR in the environment, read
+  // per call): measured on par with the single-CTA tile on dense problems (64 us both at M = 2048, N = K = 4096) and 9-12 %
+  // behind it on the ragged MoE problems, whose experts pad to 512 rows instead of 256.  Halving the conversion did not
+  // raise the tensor pipe's duty (47 % against 45 %): each SM still serves the operand reads of both tensor cores.
+  bool const pair_on = std::getenv("QUACTLIZE_B200_GEMM_PAIR") != nullptr;
+  if (big && key == 40 && d.n % 256 == 0 && d.splits <= 1 && (d.tile == 512 || (d.tile == 0 && pair_on)))
+    return d.act_bf16 ? launch_mixed_gemm<4, 0, true, 2, 2, 2>(d, stream) : launch_mixed_gemm<4, 0, false, 2, 2, 2>(d, stream);
 #define QB_GEMM_CASE(K, L, H) case K: return d.act_bf16 ? (big ? launch_mixed_gemm<L, H, true, 2, 2>(d, stream) : launch_mixed_gemm<L, H, true, 1, 1>(d, stream)) \
                                                         : (big ? launch_mixed_gemm<L, H, false, 2, 2>(d, stream) : launch_mixed_gemm<L, H, false, 1, 1>(d, stream));
   switch (key) {
