@@ -1,4 +1,4 @@
-"""Command line over the benchmark cases of quactlize_b200.workloads (every BASELINE configuration at full size plus the
+"""Command line over the benchmark cases of quactlize_b200.workloads (every benchmark configuration at full size plus the
 auxiliary ones: fused gate+up, a 264 MB Q4_K matrix, the raw blocks of the other formats, dequantise, the units pre-pass).
 
     python -m quactlize_b200.bench_suite --list

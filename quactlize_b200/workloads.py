@@ -33,7 +33,7 @@ SAMPLE_COLS = 256
 @dataclass
 class Case:
     name: str
-    bound: str                                   # "hbm" or "tensor": which roofline the launch is judged on
+    bound: str                                   # "hbm" or "tensor": which roofline bounds the launch
     weight_bytes: int                            # packed weight bytes one launch reads (the published numerator)
     alg_bytes: int                               # weights + scale channel + activations + outputs of one launch
     flops: float
