@@ -218,6 +218,38 @@ def run_b200(args):
     step_bytes = launches_per_step * WEIGHT_BYTES
     value = world * step_bytes * args.steps / (ms * 1e-3) / 1e9
 
+    # ---- the same step with each layer's gate and up in ONE launch (they share the activation): 64 launches on the same
+    # 96 buffers through the additive two-matrix entry; outputs must equal the per-matrix launches bit for bit
+    fused = None
+    if m == 1 and not args.no_graph:
+        outs_f = [torch.empty_like(o) for o in outs]
+
+        def fused_step():
+            sp = torch.cuda.current_stream(dev).cuda_stream
+            for layer in range(LAYERS):
+                (n, k, wg, _), (_, _, wu, _), (nd, kd, wd, _) = seq[3 * layer], seq[3 * layer + 1], seq[3 * layer + 2]
+                rc = L.quactlize_b200_vecdot_dense2_dev_v1(wg.data_ptr(), n, wu.data_ptr(), n, BLOCK, xs[k].data_ptr(),
+                                                           outs_f[3 * layer].data_ptr(), outs_f[3 * layer + 1].data_ptr(), k // 256, QT, sp)
+                rc = rc or L.quactlize_ppu_vecdot_dense_dev_v1(wd.data_ptr(), BLOCK, xs[kd].data_ptr(), outs_f[3 * layer + 2].data_ptr(),
+                                                               nd, kd // 256, QT, sp)
+                if rc:
+                    raise RuntimeError(f"fused step enqueue failed rc={rc}")
+        fused_step(); torch.cuda.synchronize(dev)
+        same = all(torch.equal(a_, b_) for a_, b_ in zip(outs, outs_f))
+        gf = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gf):
+            fused_step()
+        for _ in range(warm):
+            gf.replay()
+        fms = sorted(timed(gf.replay, args.steps) for _ in range(BATCHES))
+        fm = fms[len(fms) // 2]
+        fgbs = world * step_bytes * args.steps / (fm * 1e-3) / 1e9
+        fused = {"what": "the same step with gate and up of a layer in one launch (quactlize_b200_vecdot_dense2_dev_v1): 64 launches",
+                 "ms_per_step": round(fm / args.steps, 5), "value": round(fgbs, 2), "unit": "GB/s",
+                 "frac": round(fgbs / world / peaks["hbm"], 4), "bit_identical_to_per_matrix_launches": bool(same),
+                 "gpu_launches": BATCHES * args.steps * 2 * LAYERS}
+        del outs_f
+
     # ---- end to end through the host-pointer ABI: pinned host weights, H2D + kernel + D2H per call -----------------
     pin_w = {s: [torch.from_numpy(b).pin_memory() for b in ws] for s, ws in host_w.items()}
     pin_x = {k: xs[k][:1].cpu().pin_memory() for _, k in SHAPES}
@@ -295,6 +327,8 @@ def run_b200(args):
         "gpu_launches": BATCHES * args.steps * launches_per_step, "launch_mode": "eager" if args.no_graph else "cuda_graph",
         "clocks": clocks, "commit": _git_head(),
     }
+    if fused is not None:
+        line["fused_gate_up_step"] = fused
     if ep is not None:
         line["ep_moe"] = ep
         line["ep_moe_cfg5"] = ep5

@@ -82,6 +82,10 @@ int quactlize_ppu_prepass_unit(uint8_t const* units, uint16_t* scale, uint16_t* 
 int quactlize_b200_vecdot_rows_dev_v1(uint8_t const* blocks, int64_t block_bytes, uint16_t const* x, float* out, int m,
                                       int rows, int blocks_per_row, int qtype, int force_generic, void* stream);
 /* additive device-pointer forms of the entries above */
+/* Two raw-block matrices [n_a][bpr] and [n_b][bpr] of one format against ONE fp16 activation row in one launch (a layer's
+ * gate and up projections): out_a fp32 [n_a], out_b fp32 [n_b].  Device pointers, enqueue only; codes as vecdot_dense. */
+int quactlize_b200_vecdot_dense2_dev_v1(uint8_t const* blocks_a, int n_a, uint8_t const* blocks_b, int n_b, int64_t block_bytes,
+                                        uint16_t const* x, float* out_a, float* out_b, int bpr, int qtype, void* stream);
 int quactlize_b200_vecdot_dev_v1(uint8_t const* blocks, int64_t block_bytes, uint16_t const* x, float* out, int rows,
                                  int blocks_per_row, int qtype, void* stream);
 int quactlize_b200_vecdot_moe_dev_v1(uint8_t const* blocks, int64_t block_bytes, uint16_t const* x, int const* offsets,

@@ -147,6 +147,30 @@ def gguf_vecdot_dense(blocks, x, n: int, k: int, qtype: int):
     return out
 
 
+def gguf_vecdot_dense2(blocks_a, blocks_b, x, n_a: int, n_b: int, k: int, qtype: int):
+    """Two dense decode GEMVs that share their activation, in one launch (additive; a layer's gate and up projections):
+    blocks_a [n_a*k/256,type_size], blocks_b [n_b*k/256,type_size], x fp16/fp32 [1,k] -> (fp32 [1,n_a], fp32 [1,n_b]).
+    Device tensors only."""
+    g = _geom(qtype)
+    _u8(blocks_a, "blocks_a", 2)
+    _u8(blocks_b, "blocks_b", 2)
+    _check(x.dim() == 2 and x.shape[0] == 1 and x.shape[1] == k, "x must be fp16/fp32 [1,k]")
+    _check(n_a > 0 and n_b > 0 and k > 0 and k % 256 == 0, "n_a, n_b must be positive and k a positive multiple of 256")
+    bpr = k // 256
+    _check(blocks_a.shape[0] == n_a * bpr and blocks_b.shape[0] == n_b * bpr, "blocks need n*k/256 rows")
+    _check(blocks_a.shape[1] == g.block_bytes and blocks_b.shape[1] == g.block_bytes,
+           f"this format's raw GGUF block is {g.block_bytes} bytes")
+    dev = _same_device(blocks_a, x)
+    _check(dev.type == "cuda" and blocks_b.device == dev, "gguf_vecdot_dense2 takes tensors of one CUDA device")
+    x16 = _f16(x)
+    out_a = torch.empty((1, n_a), dtype=torch.float32, device=dev)
+    out_b = torch.empty((1, n_b), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _rc(_lib.lib().quactlize_b200_vecdot_dense2_dev_v1(_p(blocks_a), n_a, _p(blocks_b), n_b, g.block_bytes, _p(x16), _p(out_a),
+                                                           _p(out_b), bpr, int(qtype), _stream(blocks_a)), "gguf_vecdot_dense2")
+    return out_a, out_b
+
+
 def _offsets_info(row_offsets, experts, total_rows):
     _check(row_offsets.dtype == torch.int32 and row_offsets.dim() == 1 and row_offsets.numel() == experts + 1,
            "row_offsets must be int32 [experts+1]")

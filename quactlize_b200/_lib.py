@@ -31,6 +31,7 @@ SIGNATURES = {
     "quactlize_ppu_prepass": (I, [P, I64, P, P, I, P, P, I, I, I]),
     "quactlize_ppu_prepass_unit": (I, [P, P, P, I, I, I, I, I]),
     "quactlize_b200_vecdot_dev_v1": (I, [P, I64, P, P, I, I, I, P]),
+    "quactlize_b200_vecdot_dense2_dev_v1": (I, [P, I, P, I, I64, P, P, P, I, I, P]),
     "quactlize_b200_vecdot_rows_dev_v1": (I, [P, I64, P, P, I, I, I, I, I, P]),
     "quactlize_b200_vecdot_moe_dev_v1": (I, [P, I64, P, P, P, I, I, I, I, I, I, P]),
     "quactlize_b200_dequantize_dev_v1": (I, [P, I64, P, I, I, P]),

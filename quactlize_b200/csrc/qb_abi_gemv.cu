@@ -51,6 +51,31 @@ extern "C" int quactlize_b200_vecdot_dev_v1(uint8_t const* b, int64_t block_byte
   return rt_check_launch("raw-block row vecdot enqueue") ? 0 : kRuntimeError;
 }
 
+// Two raw-block matrices of the same K against one activation row in ONE launch (a layer's gate and up projections share
+// their input): out_a[n_a] and out_b[n_b].  Q4_K through the single-row kernel with the rows of both matrices split over
+// the CTAs as one; any other format, alignment or shape runs as two launches.  Device pointers, enqueue only.
+extern "C" int quactlize_b200_vecdot_dense2_dev_v1(uint8_t const* blocks_a, int n_a, uint8_t const* blocks_b, int n_b, int64_t block_bytes,
+                                                  uint16_t const* x, float* out_a, float* out_b, int bpr, int qtype, void* stream) {
+  if (!blocks_a || !blocks_b || !x || !out_a || !out_b || n_a <= 0 || n_b <= 0 || bpr <= 0) return 12;
+  if (kq::raw_bytes(qtype) == 0) return 3;
+  if (block_bytes != kq::raw_bytes(qtype)) return 12;
+  rt_clear_error();
+  auto al = [](void const* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  unsigned int* status = rt_device_status_ptr();
+  bool done = false;
+  if (qtype == 12 && status && al(blocks_a) && al(blocks_b) && al(x))
+    done = enqueue_q4k_gemv1_dual(blocks_a, n_a, blocks_b, n_b, reinterpret_cast<__half const*>(x), out_a, out_b, bpr, status,
+                                  static_cast<cudaStream_t>(stream));
+  if (!done) {
+    (void)cudaGetLastError();
+    enqueue_native_gemv(blocks_a, reinterpret_cast<__half const*>(x), out_a, nullptr, n_a, bpr, 1, 1, 1, qtype, false, false,
+                        static_cast<cudaStream_t>(stream));
+    enqueue_native_gemv(blocks_b, reinterpret_cast<__half const*>(x), out_b, nullptr, n_b, bpr, 1, 1, 1, qtype, false, false,
+                        static_cast<cudaStream_t>(stream));
+  }
+  return rt_check_launch("two-matrix raw-block GEMV enqueue") ? 0 : kRuntimeError;
+}
+
 extern "C" int quactlize_ppu_vecdot_dense(uint8_t const* b, int64_t block_bytes, uint16_t const* x, float* out,
                                           int rows, int bpr, int qtype) {
   if (kq::raw_bytes(qtype) == 0) return 3;

@@ -39,6 +39,11 @@ struct Q4Args {
   int S, nbs, RS, iters;     // K segments per row, blocks per segment, row slots per CTA, rows per slot
   int rows_q, rows_r;        // n = gridDim.x*rows_q + rows_r: CTA c owns rows_q (+1 if c < rows_r) consecutive rows
   unsigned int* status;
+  // A second matrix of the same K that shares the activation row (dense only): output rows n_first .. n-1 are its rows
+  // 0 .. n - n_first - 1 and go to out2.  nullptr: one matrix (n_first == n).
+  uint8_t const* blocks2;
+  float* out2;
+  int n_first;
 };
 
 __device__ __forceinline__ uint4 lds128_a(uint32_t addr) {
@@ -202,12 +207,19 @@ __global__ void __launch_bounds__(kQ4Warps * 32, 1) q4k_gemv1_kernel(Q4Args a) {
   // cost the four rounds of the warps that would own four of them while the others own three.  Which warp computes a row
   // does not change the row's arithmetic, so results do not depend on the claiming order.
   static_assert(STAGES == 2, "the claim bookkeeping below keeps two pairs per warp");
-  uint8_t const* seg_base = a.blocks + (size_t(e) * a.n + size_t(row0)) * row_stride + size_t(seg) * a.nbs * 144;
+  size_t const seg_off = size_t(seg) * a.nbs * 144;
+  // the row's segment in memory: rows of the first matrix (of expert e), then, for a two-matrix launch, of the second
+  auto row_src = [&](int grow) -> uint8_t const* {
+    return grow < a.n_first ? a.blocks + (size_t(e) * a.n_first + size_t(grow)) * row_stride + seg_off
+                            : a.blocks2 + size_t(grow - a.n_first) * row_stride + seg_off;
+  };
   auto issue_pair = [&](int pair, uint32_t dst, uint32_t bar) {
-    uint8_t const* src = seg_base + size_t(2 * pair) * row_stride;
+    int const grow = row0 + 2 * pair;
+    uint8_t const* src = row_src(grow);
     bool const two = 2 * pair + 1 < nrows;
+    bool const adjacent = grow + 1 != a.n_first;                 // a pair that straddles the two matrices is two copies
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(two ? 2u * copy_bytes : copy_bytes) : "memory");
-    if (two && contiguous) {
+    if (two && contiguous && adjacent) {
       asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                    ::"r"(dst), "l"(src), "r"(2u * copy_bytes), "r"(bar) : "memory");
     } else {
@@ -215,7 +227,7 @@ __global__ void __launch_bounds__(kQ4Warps * 32, 1) q4k_gemv1_kernel(Q4Args a) {
                    ::"r"(dst), "l"(src), "r"(copy_bytes), "r"(bar) : "memory");
       if (two)
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                     ::"r"(dst + uint32_t(seg_bytes)), "l"(src + row_stride), "r"(copy_bytes), "r"(bar) : "memory");
+                     ::"r"(dst + uint32_t(seg_bytes)), "l"(adjacent ? src + row_stride : row_src(grow + 1)), "r"(copy_bytes), "r"(bar) : "memory");
     }
   };
   int* claim = reinterpret_cast<int*>(red) + 16;                 // [S] next unclaimed pair per K segment (S <= 16)
@@ -366,7 +378,9 @@ __global__ void __launch_bounds__(kQ4Warps * 32, 1) q4k_gemv1_kernel(Q4Args a) {
   for (int r = threadIdx.x; r < nrows; r += T) {
     float s = 0.f;
     for (int sg = 0; sg < a.S; ++sg) s += part[r * a.S + sg];
-    a.out[size_t(arow) * a.n + row0 + r] = s;
+    int const grow = row0 + r;
+    if (grow < a.n_first) a.out[size_t(arow) * a.n_first + grow] = s;
+    else a.out2[size_t(arow) * (a.n - a.n_first) + (grow - a.n_first)] = s;
   }
 }
 
@@ -421,6 +435,7 @@ bool enqueue_q4k_gemv1(uint8_t const* blocks, __half const* x, float* out, int c
   Q4Args a{};
   a.blocks = blocks; a.x = x; a.out = out; a.offsets = offsets;
   a.n = n; a.bpr = bpr; a.max_rows = max_rows;
+  a.blocks2 = nullptr; a.out2 = nullptr; a.n_first = n;
   a.S = p.S; a.nbs = p.nbs; a.RS = p.RS; a.iters = p.iters; a.status = status;
   a.rows_q = n / p.gx; a.rows_r = n % p.gx;
   // Programmatic dependent launch: the next kernel of the stream may start its prologue (barrier set-up and weight
@@ -428,6 +443,29 @@ bool enqueue_q4k_gemv1(uint8_t const* blocks, __half const* x, float* out, int c
   static bool const no_pdl = std::getenv("QUACTLIZE_B200_NO_PDL") != nullptr;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(p.gx, gy); cfg.blockDim = dim3(p.W * 32); cfg.dynamicSmemBytes = p.smem; cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = no_pdl ? 0 : 1;
+  return cudaLaunchKernelEx(&cfg, q4k_gemv1_kernel<kStages1>, a) == cudaSuccess;
+}
+
+// Two Q4_K matrices of the same K against ONE activation row in one launch (a layer's gate and up projections): the CTAs
+// split the n1 + n2 rows evenly as if they were one matrix.  false outside the single-row kernel's envelope.
+bool enqueue_q4k_gemv1_dual(uint8_t const* blocks1, int n1, uint8_t const* blocks2, int n2, __half const* x, float* out1, float* out2,
+                            int bpr, unsigned int* status, cudaStream_t stream) {
+  if (n1 <= 0 || n2 <= 0) return false;
+  Q4Plan1 const& p = q4k_plan1(n1 + n2, bpr, 1);
+  if (!p.ok) return false;
+  Q4Args a{};
+  a.blocks = blocks1; a.x = x; a.out = out1; a.offsets = nullptr;
+  a.n = n1 + n2; a.bpr = bpr; a.max_rows = 1;
+  a.blocks2 = blocks2; a.out2 = out2; a.n_first = n1;
+  a.S = p.S; a.nbs = p.nbs; a.RS = p.RS; a.iters = p.iters; a.status = status;
+  a.rows_q = a.n / p.gx; a.rows_r = a.n % p.gx;
+  static bool const no_pdl = std::getenv("QUACTLIZE_B200_NO_PDL") != nullptr;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(p.gx, 1); cfg.blockDim = dim3(p.W * 32); cfg.dynamicSmemBytes = p.smem; cfg.stream = stream;
   cudaLaunchAttribute at[1];
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;

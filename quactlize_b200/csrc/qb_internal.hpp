@@ -13,6 +13,8 @@ int enqueue_native_gemv(uint8_t const* blocks, __half const* x, float* out, int 
                         bool force_generic, cudaStream_t stream);
 bool enqueue_q4k_gemv1(uint8_t const* blocks, __half const* x, float* out, int const* offsets, int n, int bpr,
                        int experts, int rows, int max_rows, unsigned int* status, cudaStream_t stream);
+bool enqueue_q4k_gemv1_dual(uint8_t const* blocks1, int n1, uint8_t const* blocks2, int n2, __half const* x, float* out1, float* out2,
+                            int bpr, unsigned int* status, cudaStream_t stream);   // two matrices, one activation row, one launch
 bool enqueue_q4k_mma(uint8_t const* blocks, __half const* x, float* out, int const* offsets, int n, int bpr, int experts,
                      int rows, unsigned int* status, cudaStream_t stream);   // tensor-core small-batch form
 bool enqueue_q4k_rows(uint8_t const* blocks, __half const* x, float* out, int n, int bpr, int rows, unsigned int* status,

@@ -112,6 +112,32 @@ def cfg2(m: int, n: int, k: int, dev="cuda:0", qtype: int = 12) -> Case:
     return Case(f"cfg2_{name}_m{m}_{k}to{n}", "hbm", wb, wb + m * k * 2 + m * n * 4, 2.0 * m * n * k, nc, launch, sample, kernel)
 
 
+def gate_up_two_buffers(dev="cuda:0") -> Case:
+    """Gate and up projections of one layer (two separate Q4_K matrices 4096 -> 14336, one activation) in one launch."""
+    n, k, qtype = 14336, 4096, 12
+    bb, bpr = synth.BLOCK_BYTES[qtype], k // 256
+    ga = synth.kquant_blocks(qtype, n * bpr, seed=231)
+    up = synth.kquant_blocks(qtype, n * bpr, seed=232)
+    x = synth.activations(1, k, seed=233)
+    nc = _ncopies(ga.size + up.size)
+    a0, u0 = _dev(ga, dev), _dev(up, dev)
+    copies = [(a0, u0)] + [(a0.clone(), u0.clone()) for _ in range(nc - 1)]
+    xd = _dev(x, dev)
+
+    def launch(i):
+        return qb.gguf_vecdot_dense2(copies[i][0], copies[i][1], xd, n, n, k, qtype)
+
+    def sample():
+        cols = _cols(n, 234)
+        og, ou = launch(0)
+        got = np.concatenate([og.cpu().numpy()[:, cols], ou.cpu().numpy()[:, cols]], axis=1)
+        sub = np.concatenate([ga.reshape(n, bpr, bb)[cols], up.reshape(n, bpr, bb)[cols]]).reshape(-1, bb)
+        return {"kind": "raw", "got": got, "blocks": sub, "x": x, "n": 2 * len(cols), "k": k, "qtype": qtype, "out": "fp32"}
+    wb = ga.size + up.size
+    return Case("q4k_m1_gate_up_two_buffers_4096to14336x2", "hbm", wb, wb + k * 2 + 2 * n * 4, 4.0 * n * k, nc, launch, sample,
+                "q4k_gemv1_kernel")
+
+
 def cfg3(qtype: int, n: int, dev="cuda:0") -> Case:
     k = 4096
     bb = synth.BLOCK_BYTES[qtype]
@@ -340,6 +366,7 @@ def registry() -> Dict[str, Callable[[], Case]]:
     # blocks of the other four formats through the raw-block entry
     r["aux_w4a16_m1_32768x4096"] = (lambda: cfg1(n=32768))      # the plane GEMV on a 67 MB matrix
     r["aux_q4k_m1_gate_up_fused"] = (lambda: cfg2(1, 2 * 14336, 4096))
+    r["aux_q4k_m1_gate_up_two_buffers"] = gate_up_two_buffers    # the same through the two-matrix entry, separate buffers
     r["aux_q4k_m1_stream_264mb"] = (lambda: cfg2(1, 8 * 14336, 4096))
     for qt, nm in ((10, "q2k"), (11, "q3k"), (13, "q5k"), (14, "q6k")):
         r[f"aux_raw_{nm}_m1_4096to14336"] = (lambda qt=qt: cfg2(1, 14336, 4096, qtype=qt))

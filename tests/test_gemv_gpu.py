@@ -145,6 +145,23 @@ def test_kquant_fast_kernel_moe(qt):
     _wait_ok()
 
 
+@pytest.mark.parametrize("qt", [12, 14])
+@pytest.mark.parametrize("n_a,n_b,k", [(14336, 14336, 4096), (97, 53, 4096), (33, 1, 2048), (40, 24, 14336)])
+def test_two_matrices_one_launch(qt, n_a, n_b, k):
+    """gate and up in one launch: both outputs equal what one launch per matrix gives, bit for bit, and the oracle."""
+    ba = synth.kquant_blocks(qt, n_a * k // 256, seed=n_a + qt)
+    bb = synth.kquant_blocks(qt, n_b * k // 256, seed=n_b + qt + 1)
+    x = synth.activations(1, k, seed=9)
+    oa, ob = qb.gguf_vecdot_dense2(_cuda(ba), _cuda(bb), _cuda(x), n_a, n_b, k, qt)
+    sa = qb.gguf_vecdot_dense(_cuda(ba), _cuda(x), n_a, k, qt)
+    sb = qb.gguf_vecdot_dense(_cuda(bb), _cuda(x), n_b, k, qt)
+    assert torch.equal(oa, sa) and torch.equal(ob, sb)
+    cols = np.unique(np.concatenate([[0, n_a - 1], np.random.default_rng(1).integers(0, n_a, 64)]))
+    sub = ba.reshape(n_a, k // 256, -1)[cols].reshape(-1, ba.shape[1])
+    assert kq.max_rel(oa.cpu().numpy()[:, cols], kq.vecdot_dense(sub, x, len(cols), k, qt)) < TOL
+    _wait_ok()
+
+
 def test_q4k_activation_extremes():
     n, k = 64, 1024
     blocks = synth.kquant_blocks(12, n * k // 256, seed=9)
