@@ -407,14 +407,21 @@ int enqueue_plane_gemv(PlaneGemvDesc const& d, cudaStream_t s) {
   if (d.k <= 0 || d.k % 256 || d.n <= 0) return 40;
   // Kernel choice: the tensor-core small-batch kernel when several activation rows can share a weight pass, else the
   // row-thread kernel, else the segment-per-warp kernel below.  QUACTLIZE_B200_PLANE_GEMV = mma | rowthread | segment
-  // forces one of them (for comparisons).
+  // forces one of them (for comparisons); "pair" forces the row-pair kernel of the merged artifact where it applies.
   static int const forced = [] {
     char const* v = std::getenv("QUACTLIZE_B200_PLANE_GEMV");
-    return !v ? 0 : v[0] == 'm' ? 1 : v[0] == 'r' ? 2 : v[0] == 's' ? 3 : 0;
+    return !v ? 0 : v[0] == 'm' ? 1 : v[0] == 'r' ? 2 : v[0] == 's' ? 3 : v[0] == 'p' ? 4 : 0;
   }();
   bool const batch = d.offsets ? d.m_rows >= 2 * std::max(1, d.experts) : d.m_rows >= 2;
   if (forced == 1 || (forced == 0 && batch)) {
     int const rc = enqueue_rowmma_gemv(d, s);
+    if (rc != 40) return rc;
+  }
+  // merged artifact, one activation row per expert at most: the row-pair kernel (with more rows per expert the row-thread
+  // kernel shares a weight tile between up to four of them)
+  int const passes = d.offsets ? d.max_rows : d.m_rows;
+  if (d.scale_mode == 1 && (forced == 4 || (forced == 0 && passes == 1))) {
+    int const rc = enqueue_bc_gemv1(d, s);
     if (rc != 40) return rc;
   }
   if (forced != 3) {

@@ -50,6 +50,7 @@ struct PlaneGemvDesc {
 int enqueue_plane_gemv(PlaneGemvDesc const& d, cudaStream_t stream);   // 0 ok, 40 unsupported shape
 int enqueue_rowthread_gemv(PlaneGemvDesc const& d, cudaStream_t stream);   // row-thread form; 40 = shape not covered by it
 int enqueue_rowmma_gemv(PlaneGemvDesc const& d, cudaStream_t stream);      // tensor-core small-batch form; 40 = not covered
+int enqueue_bc_gemv1(PlaneGemvDesc const& d, cudaStream_t stream);         // planes + packed units, one activation row per weight pass; 40 = not covered
 
 // Tensor-core mixed-input GEMM (dense when experts == 0, else grouped with cumulative offsets).
 struct GemmDesc {

@@ -162,7 +162,7 @@ def cfg3(qtype: int, n: int, dev="cuda:0") -> Case:
     wb = blocks.size                              # planes + units are byte-neutral: exactly the raw block bytes
     nm = {14: "q6k", 13: "q5k", 11: "q3k"}[qtype]
     return Case(f"cfg3_{nm}_m1_{k}to{n}", "hbm", wb, wb + k * 2 + n * 4, 2.0 * n * k, nc, launch, sample,
-                "rowthread_gemv_kernel")
+                "bc_gemv1_kernel")
 
 
 def cfg4_counts(seed: int = 11) -> np.ndarray:

@@ -310,8 +310,25 @@ def test_bc_gemv_dense(qtype, n, k):
     _wait_ok()
 
 
-def test_bc_gemv_moe(qtype):
-    n, k, rows = 256, 1024, [1, 0, 4, 2]
+@pytest.mark.parametrize("n,k", [(256, 9728), (1024, 14336), (4096, 512)])
+def test_bc_gemv_dense_row_pair_segments(qtype, n, k):
+    """K segments per row: 38 superblocks = three segments of 13 (a two-superblock unit straddles a segment boundary),
+    56 = four of 14, and rows of two superblocks; more CTAs than SMs' worth of rows and fewer."""
+    blocks = synth.kquant_blocks(qtype, n * k // 256, seed=qtype * 7 + n % 13)
+    low, high, units = qb.gguf_prepare_fully_quantized_dense(torch.from_numpy(blocks), n, k, qtype)
+    a = synth.activations(1, k, seed=14)
+    rows = np.random.default_rng(3).choice(n, size=min(n, 192), replace=False)
+    rows[:4] = [0, 1, n - 2, n - 1]
+    bb = blocks.shape[1]
+    ref = kq.vecdot_dense(blocks.reshape(n, -1, bb)[rows].reshape(-1, bb), a, len(rows), k, qtype)
+    out = qb.gguf_gemv_bc(_cuda(a), low.to(DEV), high.to(DEV), units.to(DEV), qtype)
+    assert kq.max_rel(out.cpu().numpy()[:, rows], ref) < TOL
+    _wait_ok()
+
+
+@pytest.mark.parametrize("rows", [[1, 0, 4, 2], [1, 0, 1, 1]], ids=["ragged", "one_row_each"])
+def test_bc_gemv_moe(qtype, rows):
+    n, k = 256, 1024
     e = len(rows)
     blocks = synth.kquant_blocks(qtype, e * n * k // 256, seed=qtype * 5)
     low, high, units = qb.gguf_prepare_fully_quantized_grouped(torch.from_numpy(blocks), n, k, qtype, e)
