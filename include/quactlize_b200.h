@@ -360,6 +360,9 @@ int quactlize_b200_device_wait_status(void);
  * up after limit_ns (1 .. 100 000 000).  The kernel returns normally; the next quactlize_b200_device_wait_status()
  * reports 41 once, then 0.  No counterpart in the reference (its waits are unbounded). */
 int quactlize_b200_debug_wait_probe(long long limit_ns, void* stream);
+/* additive, for tests: how many launches of the swapped tensor-core form (weights converted into tensor memory as the A
+ * operand; opt-in through QUACTLIZE_B200_GEMM_SWAP) this process has enqueued.  No counterpart in the reference. */
+long long quactlize_b200_debug_gemm_swap_launches(void);
 
 #ifdef __cplusplus
 }

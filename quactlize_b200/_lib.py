@@ -106,6 +106,7 @@ SIGNATURES = {
     "quactlize_b200_rt_last_status": (I, []),
     "quactlize_b200_device_wait_status": (I, []),
     "quactlize_b200_debug_wait_probe": (I, [C.c_longlong, P]),
+    "quactlize_b200_debug_gemm_swap_launches": (C.c_longlong, []),
     "quactlize_b200_unpack_dev_v1": (I, [P, I64, P, P, P, I, I, P]),
     "quactlize_b200_planes_dequantize_dev_v1": (I, [P, P, P, P, P, I, I, I, I, I, I, I, P]),
 }

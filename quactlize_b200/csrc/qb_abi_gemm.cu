@@ -393,3 +393,5 @@ extern "C" int quactlize_b200_gemm_plane_dev_v1(void const* act, uint8_t const* 
   if (rc) return rc;
   return rt_check_launch("plane GEMM enqueue") ? 0 : kRuntimeError;
 }
+
+extern "C" long long quactlize_b200_debug_gemm_swap_launches(void) { return qb::gemm_swap_launches(); }

@@ -31,6 +31,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
@@ -612,6 +613,298 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   }
 }
 
+// ---- the swapped form: weights as the A operand, converted straight into TENSOR MEMORY -------------------------------------
+//
+// In the kernel above every dequantised weight crosses shared memory twice more than it has to (the converting thread
+// stores it, the tensor core reads it back once per row block).  tcgen05.mma can take its A operand from tensor memory,
+// so here the roles are swapped: D[n][token] = W[n][k] * X[token][k]^T with A = 128 weight rows (one per TMEM lane, two
+// 16-bit elements per 32-bit column) and B = up to 192 activation rows from shared memory.  A converting thread owns ONE
+// weight row: it reads the 64 codes of the row's stage from the raw ring, converts them in registers and writes them
+// with one tcgen05.st (left in flight while the next stage is converted) into a ring of TMEM columns; the dequantised
+// operand never touches shared memory.  The CTA tile is 256 weight rows (two blocks of 128 = two accumulators) x 192
+// tokens: the 512 TMEM columns hold 2 x 192 accumulator columns and a two-deep operand ring of 32 columns per block.
+// The accumulator holds [weight row][token], so the epilogue stores transposed: for one token the 32 lanes of a warp
+// write 32 consecutive outputs.  int4 planes (LO = 4, HI = 0), one K slice; the other formats and split-K use the kernel
+// above.  Results are bit-identical to the kernel above (same conversion arithmetic, same K order).
+//
+// Measured on the 4096 -> 14336 grouped problem (8192 rows): 1.10 ms against 0.97 ms above, so this form is opt-in.  What
+// it showed: with the MMAs compiled out (QB_SWAP_NOMMA) 0.94 ms, with the TMEM stores compiled out (QB_SWAP_NOST)
+// 0.89 ms, deeper activation rings (QB_SWAP_XS = 6) no change, smaller token tiles slower (160: 1.24 ms, 128: 1.44 ms);
+// a first version with one block of 128 rows x 256 tokens, which re-reads the activations once per 128 weight rows, took
+// 1.21 ms while moving 8.4 GB from L2, i.e. 7 TB/s.  Every variant, and the kernel above with its conversion compiled out
+// (0.63 ms, 4.7 GB), tops out at about 26 bytes per clock and SM of L2 -> shared-memory copies: the tile's flops per L2
+// byte set the floor (190-207 here), the rings' depth does not, and the conversion path comes on top of it.
+#ifndef QB_SWAP_TOKENS
+#define QB_SWAP_TOKENS 192
+#endif
+constexpr int kSwapTokens = QB_SWAP_TOKENS;                    // activation rows per CTA tile (the MMAs' N)
+constexpr int kSwapACol = 2 * kSwapTokens;                     // first TMEM column of the operand ring (the accumulators are below)
+struct SwapSmem {
+#ifndef QB_SWAP_XS
+#define QB_SWAP_XS 4
+#endif
+  static constexpr int XS = QB_SWAP_XS, RS = 3;                // activation ring, raw ring
+  static constexpr int TS = (512 - 2 * kSwapTokens) / 64;      // TMEM operand ring per block: what the accumulators leave
+  static_assert(kSwapTokens % 16 == 0 && kSwapTokens <= 192 && TS >= 2, "two accumulators and at least a two-deep operand ring");
+  alignas(1024) uint8_t x[XS][kSwapTokens * kTK * 2];          // 192 tokens x 64 k, K-major, 128-byte swizzle
+  alignas(1024) uint8_t raw_lo[RS][2][kTN * kRawK / 2];        // per block: 128 weight rows x 64 bytes (128 k), TMA-swizzled
+  alignas(128) uint8_t scale[RS][2][kScaleBytes];
+  alignas(128) uint8_t zero[RS][2][kScaleBytes];
+  alignas(8) uint64_t x_full[XS];                              // TMA -> MMA
+  alignas(8) uint64_t x_empty[XS];                             // MMA (tcgen05.commit) -> TMA
+  alignas(8) uint64_t raw_full[RS];                            // TMA -> converting warps
+  alignas(8) uint64_t raw_empty[RS];                           // converting warps -> TMA
+  alignas(8) uint64_t a_full[2][TS];                           // a block's converting warps (tcgen05.st done) -> MMA
+  alignas(8) uint64_t a_empty[2][TS];                          // MMA (tcgen05.commit) -> the block's converting warps
+  alignas(8) uint64_t acc_full;
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(384, 1)
+mixed_gemm_swap_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_lo,
+                       const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_z, GemmArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  using SM = SwapSmem;
+  using P = Pack2<BF16>;
+  constexpr int XS = SM::XS, RS = SM::RS, TS = SM::TS;
+  SM& sm = *reinterpret_cast<SM*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // ---- which tile: blockIdx.x = tile of 256 weight rows, blockIdx.y = tile of 192 tokens (grouped: searched in the counts)
+  int e = 0, m0, mrows;
+  if (g.offsets) {
+    __shared__ int tile_of[4];
+    if (warp == 0) {
+      int const t = blockIdx.y;
+      int carry = 0, hit_e = -1, hit_m0 = 0, hit_rows = 0;
+      for (int base = 0; base < g.experts && hit_e < 0; base += 32) {
+        int const x = base + lane;
+        int r0 = 0, rows = 0;
+        if (x < g.experts) { r0 = g.offsets[x]; rows = g.offsets[x + 1] - r0; }
+        int const cnt = (rows + kSwapTokens - 1) / kSwapTokens;
+        int incl = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { int const u = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += u; }
+        int const lo = carry + incl - cnt;
+        bool const mine = cnt > 0 && t >= lo && t < lo + cnt;
+        unsigned const who = __ballot_sync(0xffffffffu, mine);
+        if (who) {
+          int const src = __ffs(who) - 1;
+          hit_e = __shfl_sync(0xffffffffu, x, src);
+          int const lo_s = __shfl_sync(0xffffffffu, lo, src), r0_s = __shfl_sync(0xffffffffu, r0, src),
+                    rows_s = __shfl_sync(0xffffffffu, rows, src);
+          hit_m0 = r0_s + (t - lo_s) * kSwapTokens;
+          hit_rows = min(kSwapTokens, rows_s - (t - lo_s) * kSwapTokens);
+        }
+        carry += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0) { tile_of[0] = hit_e; tile_of[1] = hit_m0; tile_of[2] = hit_rows; }
+    }
+    __syncthreads();
+    e = tile_of[0]; m0 = tile_of[1]; mrows = tile_of[2];
+    if (e < 0) return;                                        // uniform for the CTA, before any mbarrier or TMEM allocation
+  } else {
+    m0 = int(blockIdx.y) * kSwapTokens; mrows = min(kSwapTokens, g.m_rows - m0);
+    if (mrows <= 0) return;
+  }
+  // a wait of an earlier CTA of this process gave up: do not queue thousands of CTAs behind the same failure
+  if (g.status && *reinterpret_cast<volatile unsigned int*>(g.status) != 0u) return;
+  int const n0 = int(blockIdx.x) * (2 * kTN);
+  int const ncols = max(16, (mrows + 15) & ~15);              // the MMAs' N: tokens of this tile, in sixteens
+  int const nks = g.k / kTK;                                  // 64-k stages (k is a multiple of 128)
+  int const gs = g.group_size;
+  int const srows = gs >= kRawK ? 1 : kRawK / gs;             // scale rows per 128-k piece
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < XS; ++s) { mbar_init(&sm.x_full[s], 1); mbar_init(&sm.x_empty[s], 1); }
+    for (int s = 0; s < RS; ++s) { mbar_init(&sm.raw_full[s], 1); mbar_init(&sm.raw_empty[s], 8); }
+    for (int b = 0; b < 2; ++b)
+      for (int s = 0; s < TS; ++s) { mbar_init(&sm.a_full[b][s], 4); mbar_init(&sm.a_empty[b][s], 1); }
+    mbar_init(&sm.acc_full, 1);
+    sm.abort_flag = 0;
+    mbar_init_fence();
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  uint32_t const tmem = sm.tmem_base;
+
+  if (warp == 0) {
+    // ================= TMA producer =================
+    if (lane == 0) {
+      unsigned const raw_bytes = 2u * (unsigned(kTN * kRawK / 2) + unsigned(srows * kTN * 2) * (g.has_zero ? 2u : 1u));
+      for (int i = 0; i < nks; ++i) {
+        if ((i & 1) == 0) {
+          int const j = i >> 1, r = j % RS;
+          if (j >= RS && !gemm_wait(sm, &sm.raw_empty[r], unsigned(j / RS - 1) & 1u, g.status)) break;
+          mbar_expect_tx(&sm.raw_full[r], raw_bytes);
+          int const kk = j * kRawK;
+#pragma unroll
+          for (int b = 0; b < 2; ++b) {
+            tma_load_3d(sm.raw_lo[r][b], &map_lo, kk / 2, n0 + b * kTN, e, &sm.raw_full[r]);
+            tma_load_3d(sm.scale[r][b], &map_s, n0 + b * kTN, kk / gs, e, &sm.raw_full[r]);
+            if (g.has_zero) tma_load_3d(sm.zero[r][b], &map_z, n0 + b * kTN, kk / gs, e, &sm.raw_full[r]);
+          }
+        }
+        int const sx = i % XS;
+        if (i >= XS && !gemm_wait(sm, &sm.x_empty[sx], unsigned(i / XS - 1) & 1u, g.status)) break;
+        mbar_expect_tx(&sm.x_full[sx], kSwapTokens * kTK * 2);
+        tma_load_2d(sm.x[sx], &map_x, i * kTK, m0, &sm.x_full[sx]);
+      }
+    }
+  } else if (warp == 1) {
+    // ================= MMA issuer =================
+    if (lane == 0) {
+      uint32_t const idesc = umma_idesc(BF16 ? 1 : 0, kTM, ncols);
+      bool ok = true;
+      for (int i = 0; i < nks && ok; ++i) {
+        int const sx = i % XS, sa = i % TS;
+        ok = gemm_wait(sm, &sm.x_full[sx], unsigned(i / XS) & 1u, g.status);
+        uint32_t const x_addr = smem_u32(sm.x[sx]);
+#pragma unroll
+        for (int b = 0; b < 2 && ok; ++b) {
+          ok = gemm_wait(sm, &sm.a_full[b][sa], unsigned(i / TS) & 1u, g.status);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+#ifndef QB_SWAP_NOMMA
+          for (int kk = 0; kk < kTK / 16; ++kk)                // 16 k per instruction = 8 TMEM columns of the operand
+            umma_f16_ts(tmem + uint32_t(b * kSwapTokens), tmem + uint32_t(kSwapACol + (b * TS + sa) * 32 + kk * 8),
+                        umma_desc_sw128(x_addr + kk * 32), idesc, (i | kk) ? 1u : 0u);
+#endif
+          umma_commit(&sm.a_empty[b][sa]);                     // frees the block's operand slot once these MMAs have read it
+        }
+        if (ok) umma_commit(&sm.x_empty[sx]);
+      }
+      if (ok) umma_commit(&sm.acc_full);
+    }
+  } else if (warp >= 4) {
+    // ================= convert (warpgroup = block of 128 weight rows, thread = weight row = TMEM lane), then epilogue =====
+    int const t = threadIdx.x - 128, blk = t >> 7, q = warp & 3, rr = q * 32 + lane;
+    float const coff = float(g.code_offset);
+    int const gsh = 31 - __clz(gs);
+    uint32_t const lane_base = uint32_t(q * 32) << 16;
+    // The store of stage i into tensor memory is left in flight while stage i+1 is loaded and converted: its completion
+    // is awaited (and the stage handed to the MMA warp) just before the next store is issued.
+    bool ok = true;
+    int pending = -1;                                          // operand slot whose tcgen05.st has been issued but not yet published
+    for (int i = 0; i < nks && ok; ++i) {
+      int const sa = i % TS, j = i >> 1, r = j % RS, h = i & 1;
+      if (h == 0) ok = gemm_wait(sm, &sm.raw_full[r], unsigned(j / RS) & 1u, g.status);
+      if (!ok) break;
+      int const kofs = h * 64;                                 // this stage's 64 codes inside the 128-k piece
+      uint32_t lw[8];
+      load_raw<32, 64>(smem_u32(sm.raw_lo[r][blk]), uint32_t(rr * 64 + kofs / 2), lw);
+      uint32_t o[32];
+      int gprev = -1;
+      typename P::T2 s2, z2;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        int const grow = gs >= kRawK ? 0 : ((kofs + 8 * c) >> gsh);
+        if (grow != gprev) {
+          float const s = g_ldsh(smem_u32(sm.scale[r][blk]) + uint32_t((grow * kTN + rr) * 2));
+          float const z = (g.has_zero ? g_ldsh(smem_u32(sm.zero[r][blk]) + uint32_t((grow * kTN + rr) * 2)) : 0.f) + coff * s;
+          s2 = P::from_f(s, s); z2 = P::from_f(z, z);
+          gprev = grow;
+        }
+        uint32_t const w = lw[c], w4 = w >> 4;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj)                          // byte jj: (low nibble, high nibble) = elements 2jj, 2jj+1
+          o[4 * c + jj] = P::affine((__byte_perm(w, w4, 0x4400u + 0x1111u * jj) & 0x000F000Fu) | P::kMagic, s2, z2);
+      }
+      __syncwarp();                                            // every lane has read its codes and scales of this piece
+      if (lane == 0 && h == 1) mbar_arrive(&sm.raw_empty[r]);
+      if (pending >= 0) {                                      // publish the previous stage
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.a_full[blk][pending]);
+      }
+      if (i >= TS) ok = gemm_wait(sm, &sm.a_empty[blk][sa], unsigned(i / TS - 1) & 1u, g.status);
+      if (!ok) { pending = -1; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      uint32_t const taddr = tmem + lane_base + uint32_t(kSwapACol + (blk * TS + sa) * 32);
+#ifndef QB_SWAP_NOST
+      asm volatile(
+          "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+          "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+          ::"r"(taddr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]), "r"(o[8]),
+            "r"(o[9]), "r"(o[10]), "r"(o[11]), "r"(o[12]), "r"(o[13]), "r"(o[14]), "r"(o[15]), "r"(o[16]), "r"(o[17]),
+            "r"(o[18]), "r"(o[19]), "r"(o[20]), "r"(o[21]), "r"(o[22]), "r"(o[23]), "r"(o[24]), "r"(o[25]), "r"(o[26]),
+            "r"(o[27]), "r"(o[28]), "r"(o[29]), "r"(o[30]), "r"(o[31]) : "memory");
+#else
+      asm volatile("" ::"r"(taddr), "r"(o[0] ^ o[7] ^ o[13] ^ o[31]) : "memory");
+#endif
+      pending = sa;
+    }
+    if (pending >= 0) {
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.a_full[blk][pending]);
+    }
+    // epilogue: TMEM lane rr of accumulator blk = weight row n0 + 128*blk + rr; 32 tokens at a time
+    if (ok) ok = gemm_wait(sm, &sm.acc_full, 0, g.status);
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+      for (int c = 0; c < mrows; c += 32) {
+        uint32_t v[32];
+        uint32_t const taddr = tmem + lane_base + uint32_t(blk * kSwapTokens + c);
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+            "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+              "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+              "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+              "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+            : "r"(taddr) : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int u = 0; u < 32; ++u) {
+          if (c + u < mrows) {                                  // uniform for the warp
+            float const f = __uint_as_float(v[u]);
+            uint16_t bits;
+            if constexpr (BF16) { __nv_bfloat16 const hh = __float2bfloat16_rn(f); bits = *reinterpret_cast<uint16_t const*>(&hh); }
+            else { __half const hh = __float2half_rn(f); bits = *reinterpret_cast<uint16_t const*>(&hh); }
+            // a row map sends every output row to its own destination (peer memory is written, never read)
+            uint16_t* dst = g.out_rows ? reinterpret_cast<uint16_t*>(g.out_rows[m0 + c + u]) + n0 + blk * kTN + rr
+                                       : reinterpret_cast<uint16_t*>(g.out) + size_t(m0 + c + u) * g.n + n0 + blk * kTN + rr;
+            *dst = bits;
+          }
+        }
+      }
+    }
+  }
+  // ---- teardown: everyone meets here (all waits are bounded), then the allocating warp frees the TMEM columns
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (sm.abort_flag && threadIdx.x == 0) {
+    // drain copies that may still be in flight so they do not land in shared memory handed to another CTA
+    for (int s = 0; s < XS; ++s) { (void)mbar_wait_bounded(&sm.x_full[s], 0, nullptr, 0, 100000000ull); (void)mbar_wait_bounded(&sm.x_full[s], 1, nullptr, 0, 100000000ull); }
+    for (int s = 0; s < RS; ++s) { (void)mbar_wait_bounded(&sm.raw_full[s], 0, nullptr, 0, 100000000ull); (void)mbar_wait_bounded(&sm.raw_full[s], 1, nullptr, 0, 100000000ull); }
+  }
+  __syncthreads();
+  if (warp == 2) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+  }
+}
+
 // Light reduce of the split-K partial planes: out[r][c] = sum_z partial[z][r][c], converted to the output type.  A thread
 // owns four consecutive columns; slices are summed in slice order, so the result does not depend on scheduling.
 template <bool BF16>
@@ -672,11 +965,65 @@ inline CUtensorMapSwizzle plane_swizzle(int row_bytes) {
   return row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : (row_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
+// The four maps over a weight artifact depend only on its pointers and shape: a model's weights are launched again and
+// again, so they are encoded once and kept (per plane-width instantiation; the map of the activations is encoded per launch).
+template <int LO, int HI>
+int weight_maps(GemmDesc const& d, int E, CUtensorMap& ml, CUtensorMap& mh, CUtensorMap& ms, CUtensorMap& mz) {
+  int const gs = d.group_size;
+  int const srows = gs >= kRawK ? 1 : kRawK / gs;
+  struct WKey {
+    void const *lo, *hi, *sc, *ze; int n, k, e, gs;
+    bool operator<(WKey const& o) const {
+      return std::tie(lo, hi, sc, ze, n, k, e, gs) < std::tie(o.lo, o.hi, o.sc, o.ze, o.n, o.k, o.e, o.gs);
+    }
+  };
+  struct WMaps { CUtensorMap ml, mh, ms, mz; };
+  static std::map<WKey, WMaps> cache;
+  static std::mutex cmu;
+  WKey const key{d.low, HI ? d.high : nullptr, d.scale, d.zero, d.n, d.k, E, gs};
+  std::lock_guard<std::mutex> lock(cmu);
+  auto it = cache.find(key);
+  if (it == cache.end()) {
+    WMaps w{};
+    {
+      cuuint64_t const rb = cuuint64_t(d.k) * LO / 8;
+      cuuint64_t dims[3] = {rb, cuuint64_t(d.n), cuuint64_t(E)};
+      cuuint64_t str[2] = {rb, rb * d.n};
+      cuuint32_t box[3] = {cuuint32_t(kRawK * LO / 8), cuuint32_t(kTN), 1};
+      if (!make_map(&w.ml, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.low, dims, str, box, plane_swizzle(16 * LO))) return kRuntimeError;
+    }
+    if constexpr (HI != 0) {
+      cuuint64_t const rb = cuuint64_t(d.k) * HI / 8;
+      cuuint64_t dims[3] = {rb, cuuint64_t(d.n), cuuint64_t(E)};
+      cuuint64_t str[2] = {rb, rb * d.n};
+      cuuint32_t box[3] = {cuuint32_t(kRawK * HI / 8), cuuint32_t(kTN), 1};
+      if (!make_map(&w.mh, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.high, dims, str, box, plane_swizzle(16 * HI))) return kRuntimeError;
+    } else {
+      w.mh = w.ml;
+    }
+    {
+      cuuint64_t const kg = cuuint64_t(d.k / gs);
+      cuuint64_t dims[3] = {cuuint64_t(d.n), kg, cuuint64_t(E)};
+      cuuint64_t str[2] = {cuuint64_t(d.n) * 2, cuuint64_t(d.n) * 2 * kg};
+      cuuint32_t box[3] = {cuuint32_t(kTN), cuuint32_t(srows), 1};
+      if (!make_map(&w.ms, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, d.scale, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
+      if (d.zero) {
+        if (!make_map(&w.mz, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, d.zero, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
+      } else {
+        w.mz = w.ms;
+      }
+    }
+    if (cache.size() >= 8192) cache.clear();                  // bounded: far more artifacts than a model has
+    it = cache.emplace(key, w).first;
+  }
+  ml = it->second.ml; mh = it->second.mh; ms = it->second.ms; mz = it->second.mz;
+  return 0;
+}
+
 template <int LO, int HI, bool BF16, int MT, int NT, int DEPTH = 0>
 int launch_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
   int const E = d.experts > 0 ? d.experts : 1;
   int const gs = d.group_size;
-  int const srows = gs >= kRawK ? 1 : kRawK / gs;
   CUtensorMap ma, ml, mh, ms, mz;
   {
     cuuint64_t dims[2] = {cuuint64_t(d.k), cuuint64_t(d.total_rows)};
@@ -685,56 +1032,7 @@ int launch_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
     if (!make_map(&ma, BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, d.act, dims, str, box,
                   CU_TENSOR_MAP_SWIZZLE_128B)) return kRuntimeError;
   }
-  // The four maps over the weight artifact depend only on its pointers and shape: a model's weights are launched again and
-  // again, so they are encoded once and kept (per instantiation; the map of the activations is encoded per launch).
-  {
-    struct WKey {
-      void const *lo, *hi, *sc, *ze; int n, k, e, gs;
-      bool operator<(WKey const& o) const {
-        return std::tie(lo, hi, sc, ze, n, k, e, gs) < std::tie(o.lo, o.hi, o.sc, o.ze, o.n, o.k, o.e, o.gs);
-      }
-    };
-    struct WMaps { CUtensorMap ml, mh, ms, mz; };
-    static std::map<WKey, WMaps> cache;
-    static std::mutex cmu;
-    WKey const key{d.low, HI ? d.high : nullptr, d.scale, d.zero, d.n, d.k, E, gs};
-    std::lock_guard<std::mutex> lock(cmu);
-    auto it = cache.find(key);
-    if (it == cache.end()) {
-      WMaps w{};
-      {
-        cuuint64_t const rb = cuuint64_t(d.k) * LO / 8;
-        cuuint64_t dims[3] = {rb, cuuint64_t(d.n), cuuint64_t(E)};
-        cuuint64_t str[2] = {rb, rb * d.n};
-        cuuint32_t box[3] = {cuuint32_t(kRawK * LO / 8), cuuint32_t(kTN), 1};
-        if (!make_map(&w.ml, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.low, dims, str, box, plane_swizzle(16 * LO))) return kRuntimeError;
-      }
-      if constexpr (HI != 0) {
-        cuuint64_t const rb = cuuint64_t(d.k) * HI / 8;
-        cuuint64_t dims[3] = {rb, cuuint64_t(d.n), cuuint64_t(E)};
-        cuuint64_t str[2] = {rb, rb * d.n};
-        cuuint32_t box[3] = {cuuint32_t(kRawK * HI / 8), cuuint32_t(kTN), 1};
-        if (!make_map(&w.mh, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.high, dims, str, box, plane_swizzle(16 * HI))) return kRuntimeError;
-      } else {
-        w.mh = w.ml;
-      }
-      {
-        cuuint64_t const kg = cuuint64_t(d.k / gs);
-        cuuint64_t dims[3] = {cuuint64_t(d.n), kg, cuuint64_t(E)};
-        cuuint64_t str[2] = {cuuint64_t(d.n) * 2, cuuint64_t(d.n) * 2 * kg};
-        cuuint32_t box[3] = {cuuint32_t(kTN), cuuint32_t(srows), 1};
-        if (!make_map(&w.ms, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, d.scale, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
-        if (d.zero) {
-          if (!make_map(&w.mz, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, d.zero, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return kRuntimeError;
-        } else {
-          w.mz = w.ms;
-        }
-      }
-      if (cache.size() >= 8192) cache.clear();                  // bounded: far more artifacts than a model has
-      it = cache.emplace(key, w).first;
-    }
-    ml = it->second.ml; mh = it->second.mh; ms = it->second.ms; mz = it->second.mz;
-  }
+  if (int const rc = weight_maps<LO, HI>(d, E, ml, mh, ms, mz)) return rc;
   GemmArgs g{};
   g.offsets = d.experts > 0 ? d.offsets : nullptr;
   g.out = d.out; g.m_rows = d.total_rows; g.n = d.n; g.k = d.k; g.experts = E; g.group_size = gs;
@@ -799,12 +1097,61 @@ int launch_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
   return 0;
 }
 
+std::atomic<long long> g_swap_launches{0};
+
+// The swapped form (int4 planes, one K slice): see mixed_gemm_swap_kernel.
+template <bool BF16>
+int launch_mixed_gemm_swap(GemmDesc const& d, cudaStream_t stream) {
+  int const E = d.experts > 0 ? d.experts : 1;
+  CUtensorMap mx, ml, mh, ms, mz;
+  {
+    cuuint64_t dims[2] = {cuuint64_t(d.k), cuuint64_t(d.total_rows)};
+    cuuint64_t str[1] = {cuuint64_t(d.k) * 2};
+    cuuint32_t box[2] = {cuuint32_t(kTK), cuuint32_t(kSwapTokens)};
+    if (!make_map(&mx, BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, d.act, dims, str, box,
+                  CU_TENSOR_MAP_SWIZZLE_128B)) return kRuntimeError;
+  }
+  if (int const rc = weight_maps<4, 0>(d, E, ml, mh, ms, mz)) return rc;
+  GemmArgs g{};
+  g.offsets = d.experts > 0 ? d.offsets : nullptr;
+  g.out = d.out; g.m_rows = d.total_rows; g.n = d.n; g.k = d.k; g.experts = E; g.group_size = d.group_size;
+  g.code_offset = d.code_offset; g.has_zero = d.zero ? 1 : 0;
+  g.splits = 1; g.partial = nullptr; g.out_rows = d.out_rows;
+  g.status = rt_device_status_ptr();
+  if (!g.status) return kRuntimeError;
+  auto kern = mixed_gemm_swap_kernel<BF16>;
+  size_t const smem = sizeof(SwapSmem) + 1024;
+  static_assert(sizeof(SwapSmem) + 1024 <= 232448, "shared memory of one CTA");
+  {
+    static std::mutex mu;
+    static bool attr_set[kMaxDevices] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { (void)cudaGetLastError(); return kRuntimeError; }
+    std::lock_guard<std::mutex> lock(mu);
+    if (!attr_set[dev]) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return kRuntimeError;
+      }
+      attr_set[dev] = true;
+    }
+  }
+  int const mtiles = d.experts > 0 ? d.total_rows / kSwapTokens + std::min(d.experts, d.total_rows)
+                                   : (d.total_rows + kSwapTokens - 1) / kSwapTokens;
+  if (mtiles > 65535) return 30;
+  kern<<<dim3(d.n / (2 * kTN), mtiles, 1), 384, smem, stream>>>(mx, ml, ms, mz, g);
+  g_swap_launches.fetch_add(1, std::memory_order_relaxed);
+  return 0;
+}
+
 }  // namespace
 
 bool tma_make_map(CUtensorMap* m, CUtensorMapDataType dt, int rank, void const* base, cuuint64_t const* dims,
                   cuuint64_t const* strides_bytes, cuuint32_t const* box, CUtensorMapSwizzle sw) {
   return make_map(m, dt, rank, base, dims, strides_bytes, box, sw);
 }
+
+long long gemm_swap_launches() { return g_swap_launches.load(std::memory_order_relaxed); }
 
 int enqueue_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
   if (!d.act || !d.low || !d.scale || (!d.out && !d.out_rows) || d.total_rows <= 0 || d.n <= 0 || d.n % kTN || d.k <= 0 || d.k % 256 ||
@@ -815,7 +1162,7 @@ int enqueue_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
   int const key = d.lo_bits * 10 + d.hi_bits;
   // 256 x 256 CTA tiles (four accumulators = all 512 TMEM columns) for prefill-sized problems; small ones keep 128 x 128
   int const avg_rows = d.experts > 0 ? d.total_rows / d.experts : d.total_rows;
-  bool const big = d.tile == 256 || d.tile == 512 || (d.tile == 0 && avg_rows >= 192);
+  bool const big = d.tile == 256 || d.tile == 512 || d.tile == 1024 || (d.tile == 0 && avg_rows >= 192);
   if (d.shallow && !big) {                        // decode tactic: 128 x 128 tiles, two-deep rings, several CTAs per SM
 #define QB_GEMM_SHALLOW(K, L, H) case K: return d.act_bf16 ? launch_mixed_gemm<L, H, true, 1, 1, 1>(d, stream) : launch_mixed_gemm<L, H, false, 1, 1, 1>(d, stream);
     switch (key) {
@@ -830,6 +1177,13 @@ int enqueue_mixed_gemm(GemmDesc const& d, cudaStream_t stream) {
   // per call): measured on par with the single-CTA tile on dense problems (64 us both at M = 2048, N = K = 4096) and 9-12 %
   // behind it on the ragged MoE problems, whose experts pad to 512 rows instead of 256.  Halving the conversion did not
   // raise the tensor pipe's duty (47 % against 45 %): each SM still serves the operand reads of both tensor cores.
+  // The swapped form (weights as the A operand, converted into tensor memory): int4 planes, whole 256-row weight tiles,
+  // one K slice.  Opt-in (QUACTLIZE_B200_GEMM_SWAP in the environment, read per call, or tile = 1024): it is slower than
+  // the tiles below on the problems measured (see mixed_gemm_swap_kernel).
+  char const* const swap_env = std::getenv("QUACTLIZE_B200_GEMM_SWAP");   // set: prefill-sized problems; "all": every size
+  bool const swap_on = swap_env != nullptr && (big || swap_env[0] == 'a');
+  if (key == 40 && d.splits <= 1 && !d.shallow && d.n % (2 * kTN) == 0 && (d.tile == 1024 || (d.tile == 0 && swap_on)))
+    return d.act_bf16 ? launch_mixed_gemm_swap<true>(d, stream) : launch_mixed_gemm_swap<false>(d, stream);
   bool const pair_on = std::getenv("QUACTLIZE_B200_GEMM_PAIR") != nullptr;
   if (big && key == 40 && d.n % 256 == 0 && d.splits <= 1 && (d.tile == 512 || (d.tile == 0 && pair_on)))
     return d.act_bf16 ? launch_mixed_gemm<4, 0, true, 2, 2, 2>(d, stream) : launch_mixed_gemm<4, 0, false, 2, 2, 2>(d, stream);

@@ -72,5 +72,6 @@ struct GemmDesc {
 // pairs that hold rows (an upper bound is fine).  1 when the plain launch already gives every SM a tile.
 int splitk_auto(int row_tiles, int n, int k);
 int enqueue_mixed_gemm(GemmDesc const& d, cudaStream_t stream);    // 0 ok, 30/33 refused, 41 runtime
+long long gemm_swap_launches();                                    // launches of the swapped (TMEM-operand) form so far
 
 }  // namespace qb

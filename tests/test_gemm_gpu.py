@@ -209,3 +209,35 @@ def test_one_process_drives_two_devices():
         with torch.cuda.device(dev):
             torch.cuda.synchronize()
             assert _lib.lib().quactlize_b200_device_wait_status() == 0
+
+
+@pytest.mark.parametrize("case", [
+    dict(m=256, n=256, k=256, gs=128, dt="bf16"), dict(m=192, n=256, k=512, gs=64, dt="fp16"),
+    dict(m=333, n=512, k=2048, gs=32, dt="fp16", zero=False), dict(m=512, n=256, k=512, gs=16, dt="bf16"),
+    dict(m=900, n=256, k=1024, gs=128, dt="bf16", offs=[0, 300, 300, 810, 900]),
+    dict(m=40, n=256, k=256, gs=128, dt="bf16", offs=[0, 17, 40])], ids=lambda c: f"m{c['m']}n{c['n']}k{c['k']}g{c['gs']}")
+def test_swapped_form_is_bit_identical(case, monkeypatch):
+    """The swapped form (weights converted into tensor memory as the A operand; opt-in through the environment, read per
+    call) against the default kernel: same conversion arithmetic, same K order, so the outputs must be equal bit for bit;
+    dense and ragged grouped, every group size, with and without a zero plane."""
+    rng = np.random.default_rng(case["m"] + case["n"] + case["k"])
+    offs = case.get("offs")
+    e = 1 if offs is None else len(offs) - 1
+    m, n, k, gs = case["m"], case["n"], case["k"], case["gs"]
+    dt = torch.bfloat16 if case["dt"] == "bf16" else torch.float16
+    low = torch.from_numpy(rng.integers(0, 256, size=(e, n, k // 2), dtype=np.uint8)).to(DEV)
+    scale = torch.from_numpy((np.abs(rng.normal(0, 0.02, size=(e, k // gs, n))) / 7).astype(np.float16)).to(DEV)
+    zero = (-8.0 * scale.float()).half() if case.get("zero", True) else None
+    a = torch.from_numpy(rng.normal(0, 1, size=(m, k)).astype(np.float32)).to(DEV).to(dt)
+    off = None if offs is None else torch.tensor(offs, dtype=torch.int32, device=DEV)
+    L = _lib.lib()
+    monkeypatch.delenv("QUACTLIZE_B200_GEMM_SWAP", raising=False)
+    before = L.quactlize_b200_debug_gemm_swap_launches()
+    ref = qb.gemm_plane(a, low, None, scale, zero, 4, 0, gs, row_offsets=off)
+    assert L.quactlize_b200_debug_gemm_swap_launches() == before          # the default kernel ran
+    monkeypatch.setenv("QUACTLIZE_B200_GEMM_SWAP", "all")
+    got = qb.gemm_plane(a, low, None, scale, zero, 4, 0, gs, row_offsets=off)
+    assert L.quactlize_b200_debug_gemm_swap_launches() == before + 1      # ... and now the swapped one
+    torch.cuda.synchronize()
+    assert torch.equal(got, ref)
+    assert L.quactlize_b200_device_wait_status() == 0
