@@ -99,3 +99,34 @@ def test_grouped_gemm_with_empty_groups_only_and_single_row_groups():
             ref = kq.planes_matmul(a, low, None, scale, zero, bits, 0, gs, off)
             assert kq.max_rel(out.float().cpu().numpy(), ref) < 3e-3
     _wait_ok()
+
+
+@pytest.mark.parametrize("qt", [11, 13, 14])
+@pytest.mark.parametrize("k", [16384, 32768])
+def test_merged_gemv_long_rows(qt, k):
+    """K = 16384 is what the merged artifact's row-pair kernel still holds (four segments of sixteen superblocks); longer
+    rows go to the row-thread kernel."""
+    n = 256
+    blocks = synth.kquant_blocks(qt, n * k // 256, seed=k % 83 + qt)
+    low, high, units = qb.gguf_prepare_fully_quantized_dense(torch.from_numpy(blocks), n, k, qt)
+    a = synth.activations(1, k, seed=9)
+    out = qb.gguf_gemv_bc(_cuda(a), low.to(DEV), high.to(DEV), units.to(DEV), qt)
+    assert kq.max_rel(out.cpu().numpy(), kq.vecdot_dense(blocks, a, n, k, qt)) < 4e-3
+    _wait_ok()
+
+
+@pytest.mark.parametrize("qt", [10, 14])
+def test_merged_gemv_with_unaligned_units(qt):
+    """Packed units that start 4 bytes off a 16-byte boundary: the row-pair kernel's 8-byte unit pieces would be misaligned,
+    so another kernel takes the launch."""
+    n, k = 256, 2048
+    blocks = synth.kquant_blocks(qt, n * k // 256, seed=51 + qt)
+    low, high, units = qb.gguf_prepare_fully_quantized_dense(torch.from_numpy(blocks), n, k, qt)
+    raw = torch.zeros(units.numel() + 64, dtype=torch.uint8, device=DEV)
+    raw[4:4 + units.numel()] = units.to(DEV).reshape(-1)
+    u_un = raw[4:4 + units.numel()].view(units.shape)
+    assert u_un.data_ptr() % 16 == 4
+    a = synth.activations(1, k, seed=10)
+    out = qb.gguf_gemv_bc(_cuda(a), low.to(DEV), high.to(DEV), u_un, qt)
+    assert kq.max_rel(out.cpu().numpy(), kq.vecdot_dense(blocks, a, n, k, qt)) < 4e-3
+    _wait_ok()
