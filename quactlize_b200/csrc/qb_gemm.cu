@@ -632,8 +632,9 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 // 0.89 ms, deeper activation rings (QB_SWAP_XS = 6) no change, smaller token tiles slower (160: 1.24 ms, 128: 1.44 ms);
 // a first version with one block of 128 rows x 256 tokens, which re-reads the activations once per 128 weight rows, took
 // 1.21 ms while moving 8.4 GB from L2, i.e. 7 TB/s.  Every variant, and the kernel above with its conversion compiled out
-// (0.63 ms, 4.7 GB), tops out at about 26 bytes per clock and SM of L2 -> shared-memory copies: the tile's flops per L2
-// byte set the floor (190-207 here), the rings' depth does not, and the conversion path comes on top of it.
+// (0.63 ms, 4.7 GB), tops out at about 26 bytes per clock and SM of tensor copies into shared memory -- about 4 cycles
+// per box row of at most 128 bytes (388 rows per stage above: 1 570 cycles; 324 here: 1 300-1 490): the rows a tile needs
+// per flop set the floor, the rings' depth does not, and the conversion path comes on top of it.
 #ifndef QB_SWAP_TOKENS
 #define QB_SWAP_TOKENS 192
 #endif
