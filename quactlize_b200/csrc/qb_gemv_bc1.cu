@@ -282,6 +282,7 @@ __global__ void __launch_bounds__(kBcWarps * 32, 1) bc_gemv1_kernel(BcArgs a) {
   constexpr int PPG = (256 / G) / 8;                               // 16-byte activation pieces per group: 2 or 4
   constexpr int OPC = GM::kOct, CPS = GM::kCps, GPC = GM::kGpc, SLOTS = GM::kSlots;
   constexpr int HCB = 16 * F::kHi / F::kLo;                        // high-plane bytes per chunk
+  static_assert((P == 1 ? 16 : 9) * UD2 <= 96, "a segment's unit pieces fit three per lane");
   extern __shared__ __align__(128) uint8_t smem[];
   int const T = blockDim.x, W = T >> 5, warp = __shfl_sync(0xffffffffu, int(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   int const seg = warp % a.S, rslot = warp / a.S;
