@@ -192,3 +192,12 @@ def test_pack_unit_reference_form_matches_golden(qtype):
     if geo.has_min:
         with pytest.raises(RuntimeError):
             qb.gguf_pack_unit(sblk, d, None, qtype)
+
+
+def test_variant_builds_need_a_name_and_a_macro_the_sources_mention():
+    """The ablation builds (`python -m quactlize_b200.build --variant NAME --define MACRO`) refuse what cannot work before
+    any compiler runs: a name that is no identifier, no macro, a macro no source mentions."""
+    from quactlize_b200 import build as qbuild
+    for name, defines in (("no-dash", ["QB_SWAP_NOST"]), ("ok", []), ("ok", ["QB_NO_SUCH_SWITCH"])):
+        with pytest.raises(ValueError):
+            qbuild.build_variant(name, defines)
